@@ -1,0 +1,258 @@
+/*
+ * saetta_b200.h -- C ABI of the B200 attention path.
+ *
+ * One shared library, plain pointers and sizes only.  Every entry point
+ * returns a saetta_status; saetta_last_error() gives the message of the last
+ * failure on the calling thread.  Nothing unwinds across this boundary.
+ *
+ * Each block names the interface of the reference project (Rust, paths inside
+ * that project) that it stands in for.  Geometry is the reference's: head
+ * dimension 256, 8 query heads per kv head, quantisation groups of 64.
+ *
+ * Conventions shared by all entry points
+ *   - pointers named *_dev are device pointers on the object's device;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); work is enqueued, never synchronised, unless stated;
+ *   - the per-token inputs (position, kv_len) are read ON THE DEVICE from a
+ *     saetta_token_params the caller updates between replays, so a recorded
+ *     CUDA graph of these calls serves every position, as the reference's
+ *     recorded Plan does (src/plan.rs:1-35);
+ *   - handles are not thread-safe; distinct handles on distinct streams may
+ *     run concurrently.
+ */
+#ifndef SAETTA_B200_H
+#define SAETTA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum saetta_status {
+    SAETTA_OK = 0,
+    SAETTA_ERR_BAD_ARG = 1,   /* null pointer, unknown enum value */
+    SAETTA_ERR_BAD_SHAPE = 2, /* what the reference asserts: head_dim != 256, heads != 8*kv_heads, m > rows ... */
+    SAETTA_ERR_NO_MEM = 3,
+    SAETTA_ERR_CUDA = 4,
+    SAETTA_ERR_TIMEOUT = 5, /* a bounded device-side wait gave up (see saetta_device_status) */
+    SAETTA_ERR_UNSUPPORTED = 6
+} saetta_status;
+
+const char *saetta_last_error(void);
+/* Library version string and the SM architecture the kernels were built for. */
+const char *saetta_version(void);
+
+/* src/plan.rs:17-35 `TokenParams`; kernels read it from device memory. */
+typedef struct saetta_token_params {
+    uint32_t token;
+    uint32_t position;
+    uint32_t kv_len; /* position + 1 */
+    uint32_t pad;
+} saetta_token_params;
+
+/* src/attention_prefill.rs:5-14 `FlashParams`. */
+typedef struct saetta_flash_params {
+    uint32_t heads;
+    uint32_t kv_heads;
+    uint32_t pos;    /* position of the chunk's first token; token i sees keys 0 ..= pos + i */
+    uint32_t tokens;
+    float scale;
+} saetta_flash_params;
+
+/* Storage type of 16-bit tensors (the reference stores binary16; the tensor-core
+ * prefill also takes bfloat16). */
+typedef enum saetta_dtype { SAETTA_F16 = 0, SAETTA_BF16 = 1 } saetta_dtype;
+
+/* ------------------------------------------------------------------ QuantRows
+ * src/kv_quant.rs:158-283 `QuantRows`: the codes, scales and biases of one cache
+ * side (keys or values).  Layout (kernels/kv_quant.metal:1-6): group
+ * G = token * per_token + g, data u32 [groups][2*bits], scales/biases binary16
+ * [groups]; code i of a group sits at bit i*bits of word i*bits/32.
+ */
+typedef struct saetta_quant_rows saetta_quant_rows;
+
+/* QuantRows::new(gpu, bits, values, capacity): owns its three buffers. */
+int saetta_quant_rows_create(int device, int bits, size_t values, size_t capacity,
+                             saetta_quant_rows **out);
+/* The same object over buffers the caller owns (a `View` of each). */
+int saetta_quant_rows_wrap(int device, int bits, size_t values, size_t capacity, void *data_dev,
+                           void *scales_dev, void *biases_dev, saetta_quant_rows **out);
+void saetta_quant_rows_destroy(saetta_quant_rows *rows);
+int saetta_quant_rows_buffers(const saetta_quant_rows *rows, void **data_dev, void **scales_dev,
+                              void **biases_dev);
+/* QuantRows::record / record_at: quantise one token's `values` f32 at x_dev into
+ * the slot at params_dev->position. */
+int saetta_quant_rows_record_at(saetta_quant_rows *rows, const float *x_dev,
+                                const saetta_token_params *params_dev, void *stream);
+/* QuantRows::encode: `tokens` rows of x_dev into the slots from `pos`. */
+int saetta_quant_rows_encode(saetta_quant_rows *rows, const float *x_dev, size_t pos,
+                             size_t tokens, void *stream);
+/* QuantRows::encode_dequantize: tokens 0..tokens as 16-bit values (s*q + z, a
+ * multiply then an add in f32, then one rounding) into out_dev. */
+int saetta_quant_rows_encode_dequantize(const saetta_quant_rows *rows, void *out_dev,
+                                        int dtype, size_t tokens, void *stream);
+
+/* Host-side kv_quant::quantize / dequantize (src/kv_quant.rs:54-105), bit for bit
+ * what the kernels write; for callers that prepare a cache on the CPU. */
+int saetta_quantize_host(const float *x, size_t n, int bits, uint32_t *data, uint16_t *scales,
+                         uint16_t *biases);
+int saetta_dequantize_host(const uint32_t *data, const uint16_t *scales, const uint16_t *biases,
+                           size_t groups, int bits, float *out);
+
+/* ------------------------------------------------------------------ GpuKvCache
+ * src/gpu_layers.rs:179-293 `GpuKvCache`.  bits 16 / 8 / 4 as `KvBits`; bits 32
+ * (f32 rows, no counterpart in the reference) exists so the f32 configuration
+ * can run on the device.  Capacity is rounded up to SAETTA_KV_ALIGN.  Token p
+ * lives in row p of every buffer.
+ */
+#define SAETTA_KV_ALIGN 128
+typedef struct saetta_kv_cache saetta_kv_cache;
+
+int saetta_kv_cache_create(int device, int bits, size_t heads, size_t kv_heads, size_t head_dim,
+                           size_t capacity, saetta_kv_cache **out);
+void saetta_kv_cache_destroy(saetta_kv_cache *cache);
+size_t saetta_kv_cache_capacity(const saetta_kv_cache *cache);
+int saetta_kv_cache_bits(const saetta_kv_cache *cache);
+/* GpuKvCache::buffers(): keys, values, then k.scales, k.biases, v.scales, v.biases
+ * for a quantised cache; row_bytes[i] is the size of one token's row. Returns
+ * the number of buffers (2 or 6) in *count. */
+int saetta_kv_cache_buffers(const saetta_kv_cache *cache, void *buffers_dev[6],
+                            size_t row_bytes[6], int *count);
+/* The two QuantRows of a quantised cache (borrowed; NULL for 16/32 bits). */
+int saetta_kv_cache_quant(const saetta_kv_cache *cache, saetta_quant_rows **keys,
+                          saetta_quant_rows **values);
+/* GpuKvCache::resize: new buffers, every old row that fits copied over; blocks
+ * until the copy is done.  Ops recorded with the old buffers must be recorded again. */
+int saetta_kv_cache_resize(saetta_kv_cache *cache, size_t capacity, void *stream);
+/* The store sites (src/gpu_layers.rs:373-411, 483-522, src/prefill.rs:1656-1666):
+ * write `rows` rows of k and v (f32 [rows][kv_heads*head_dim], already normed
+ * and roped) at params_dev->position + r  /  at pos + r.  A 16-bit cache
+ * narrows (the reference's to_half), a quantised one quantises. */
+int saetta_kv_cache_store(saetta_kv_cache *cache, const float *k_dev, const float *v_dev,
+                          const saetta_token_params *params_dev, size_t rows, void *stream);
+int saetta_kv_cache_store_at(saetta_kv_cache *cache, const float *k_dev, const float *v_dev,
+                             size_t pos, size_t tokens, void *stream);
+/* dtype of a 16-bit cache's rows (SAETTA_F16 unless set otherwise before use). */
+int saetta_kv_cache_set_dtype(saetta_kv_cache *cache, int dtype);
+
+/* ------------------------------------------------------------------ RowBackup
+ * src/gpu_cache.rs:192-286 `RowBackup`: rows from..from+n of every buffer of
+ * every cache copied aside and put back by byte ranges.
+ */
+typedef struct saetta_row_backup saetta_row_backup;
+int saetta_row_backup_create(saetta_row_backup **out);
+void saetta_row_backup_destroy(saetta_row_backup *b);
+int saetta_row_backup_save(saetta_row_backup *b, saetta_kv_cache *const *caches, size_t n_caches,
+                           size_t from, size_t n, void *stream);
+int saetta_row_backup_restore(saetta_row_backup *b, saetta_kv_cache *const *caches,
+                              size_t n_caches, void *stream);
+void saetta_row_backup_clear(saetta_row_backup *b);
+uint64_t saetta_row_backup_bytes(const saetta_row_backup *b);
+
+/* ------------------------------------------------------------------ DecodeAttention / AttentionRows
+ * src/attention.rs:19-171 `DecodeAttention` and src/rows.rs:307-494
+ * `AttentionRows`: out = softmax(q K^T / 16) V * sigmoid(gate) for m rows over
+ * the cache; row r sees params_dev->kv_len + r keys.  One object holds the
+ * split-KV scratch for one capacity; layers that run one after the other share
+ * it.  q [m][heads][256] f32, q_and_gate [m][heads][512] f32 with the gate of
+ * head h at h*512+256, out [m][heads][256] f32.
+ */
+#define SAETTA_MAX_ROWS 8 /* src/rows.rs:9 */
+typedef struct saetta_decode saetta_decode;
+
+/* DecodeAttention::new(gpu, heads, kv_heads, head_dim, capacity) when rows == 1,
+ * AttentionRows::new(gpu, heads, kv_heads, capacity, rows) otherwise. */
+int saetta_decode_create(int device, size_t heads, size_t kv_heads, size_t head_dim,
+                         size_t capacity, size_t rows, saetta_decode **out);
+void saetta_decode_destroy(saetta_decode *op);
+/* DecodeAttention::record / AttentionRows::record: a 16-bit (dtype) or f32
+ * (dtype = -1) cache [capacity][kv_heads][256]. */
+int saetta_decode_record(saetta_decode *op, size_t m, const float *q_dev, const void *keys_dev,
+                         const void *values_dev, int dtype, const float *q_and_gate_dev,
+                         float *out_dev, const saetta_token_params *params_dev, void *stream);
+/* DecodeAttention::record_quant / AttentionRows::record_quant. */
+int saetta_decode_record_quant(saetta_decode *op, size_t m, const float *q_dev,
+                               const saetta_quant_rows *keys, const saetta_quant_rows *values,
+                               const float *q_and_gate_dev, float *out_dev,
+                               const saetta_token_params *params_dev, void *stream);
+/* Either of the two, picked by the cache's bits. */
+int saetta_decode_record_cache(saetta_decode *op, size_t m, const float *q_dev,
+                               const saetta_kv_cache *cache, const float *q_and_gate_dev,
+                               float *out_dev, const saetta_token_params *params_dev,
+                               void *stream);
+/* Number of split-KV parts the op launches (its grid), and the device status
+ * word of its bounded waits: 0 when no wait ever gave up.  Synchronises `stream`. */
+int saetta_decode_splits(const saetta_decode *op);
+int saetta_decode_device_status(saetta_decode *op, void *stream, uint32_t *status);
+
+/* Batched decode, one row per sequence (no counterpart in the reference, which
+ * serves one sequence): sequence i reads caches[i] up to kv_lens_dev[i] keys,
+ * q [n][heads][256], q_and_gate [n][heads][512], out [n][heads][256].  All
+ * caches share bits, and the op's capacity bounds every kv_len. */
+typedef struct saetta_decode_batch saetta_decode_batch;
+int saetta_decode_batch_create(int device, size_t heads, size_t kv_heads, size_t head_dim,
+                               size_t max_seqs, size_t max_total_tokens,
+                               saetta_decode_batch **out);
+void saetta_decode_batch_destroy(saetta_decode_batch *op);
+int saetta_decode_batch_record(saetta_decode_batch *op, size_t n,
+                               saetta_kv_cache *const *caches, const uint32_t *kv_lens_host,
+                               const float *q_dev, const float *q_and_gate_dev, float *out_dev,
+                               void *stream);
+
+/* ------------------------------------------------------------------ split-KV across GPUs
+ * No counterpart in the reference (one GPU).  Each rank holds a disjoint set of
+ * KV rows and produces, per (row, head), the partial (m, l, O) of
+ * kernels/attention.metal:367-409's merge: part [m][heads][SAETTA_PART_STRIDE]
+ * f32 = 256 unnormalised outputs, then the running max (in log2 units) and the
+ * sum.  After the ranks' parts are gathered into [ranks][m][heads][stride] (an
+ * NCCL all-gather on the caller's side), merge applies the gate.
+ */
+#define SAETTA_PART_STRIDE 264
+/* row_step 1: row r sees params_dev->kv_len + r keys (the shard that holds the
+ * new rows); 0: every row sees kv_len keys (the other shards). */
+int saetta_decode_partial_cache(saetta_decode *op, size_t m, const float *q_dev,
+                                const saetta_kv_cache *cache, float *part_dev, uint32_t row_step,
+                                const saetta_token_params *params_dev, void *stream);
+int saetta_merge_partials(int device, const float *parts_dev, size_t ranks, size_t rows,
+                          size_t heads, const float *q_and_gate_dev, float *out_dev, void *stream);
+
+/* ------------------------------------------------------------------ prefill
+ * src/attention_prefill.rs:39-72 `encode` and src/attention_gemm.rs:93-363
+ * `AttGemm`: causal attention of a chunk of p.tokens query tokens at p.pos over
+ * keys 0 .. p.pos + i, gate fused.  q 16-bit [tokens][heads][256], keys/values
+ * the 16-bit cache from position 0 with the chunk's rows already written,
+ * q_and_gate f32 [tokens][heads][512], out f32 [tokens][heads][256].
+ */
+typedef struct saetta_att_gemm saetta_att_gemm;
+/* AttGemm::new(gpu, chunk, kv_heads). */
+int saetta_att_gemm_create(int device, size_t chunk, size_t kv_heads, saetta_att_gemm **out);
+void saetta_att_gemm_destroy(saetta_att_gemm *op);
+/* Grows the 16-bit staging copy a quantised cache is read through to `tokens`
+ * tokens now, so that later encodes allocate nothing. */
+int saetta_att_gemm_reserve(saetta_att_gemm *op, size_t tokens);
+/* AttGemm::encode: with keys_q/values_q non-NULL the cache is read from those
+ * 8/4-bit rows (through a 16-bit copy, as the reference's kv_stage reads it)
+ * and keys_dev/values_dev are ignored. */
+int saetta_att_gemm_encode(saetta_att_gemm *op, const void *q_dev, int dtype, const void *keys_dev,
+                           const void *values_dev, const saetta_quant_rows *keys_q,
+                           const saetta_quant_rows *values_q, const float *q_and_gate_dev,
+                           float *out_dev, saetta_flash_params p, void *stream);
+/* attention_prefill::encode: the same computation with no object (16-bit cache only). */
+int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *keys_dev,
+                          const void *values_dev, const float *q_and_gate_dev, float *out_dev,
+                          saetta_flash_params p, void *stream);
+/* As saetta_att_gemm_encode, but keys [lo, hi) only and the result left as the
+ * partial (m, l, O) of SAETTA_PART_STRIDE floats per (token, head) for the
+ * cross-GPU merge; hi is clipped per token by causality. */
+int saetta_att_gemm_partial(saetta_att_gemm *op, const void *q_dev, int dtype,
+                            const void *keys_dev, const void *values_dev,
+                            const saetta_quant_rows *keys_q, const saetta_quant_rows *values_q,
+                            float *part_dev, saetta_flash_params p, size_t key_lo, size_t key_hi,
+                            void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAETTA_B200_H */

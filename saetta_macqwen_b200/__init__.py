@@ -1,0 +1,410 @@
+"""saetta attention path for B200: ctypes binding of libsaetta_b200.so.
+
+The product is the shared library (CUDA C++ behind the C ABI of
+include/saetta_b200.h).  This module only loads it and mirrors, name for name,
+the reference's Rust operator structs so tests and benchmarks read like the
+reference's own (paths inside the reference project):
+
+    QuantRows         src/kv_quant.rs:158-283
+    GpuKvCache        src/gpu_layers.rs:179-293
+    RowBackup         src/gpu_cache.rs:192-286
+    DecodeAttention   src/attention.rs:19-171
+    AttentionRows     src/rows.rs:307-494
+    AttGemm           src/attention_gemm.rs:93-363
+    TokenParams       src/plan.rs:17-35
+    FlashParams       src/attention_prefill.rs:5-14
+
+There is no CPU or PyTorch fallback: without the built library every call
+raises.  Device memory is whatever the caller hands in as raw device pointers
+(ints) or objects with ``data_ptr()`` (torch tensors).
+"""
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsaetta_b200.so")
+
+F16, BF16, F32 = 0, 1, -1
+KV_ALIGN = 128
+MAX_ROWS = 8
+PART_STRIDE = 264
+OK, BAD_ARG, BAD_SHAPE, NO_MEM, CUDA, TIMEOUT, UNSUPPORTED = range(7)
+
+
+class SaettaError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"saetta status {code}: {message}")
+        self.code = code
+
+
+class TokenParams(C.Structure):
+    """src/plan.rs:17-35."""
+    _fields_ = [("token", C.c_uint32), ("position", C.c_uint32), ("kv_len", C.c_uint32), ("pad", C.c_uint32)]
+
+    @classmethod
+    def new(cls, token, position):
+        return cls(token, position, position + 1, 0)
+
+
+class FlashParams(C.Structure):
+    """src/attention_prefill.rs:5-14."""
+    _fields_ = [("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("pos", C.c_uint32), ("tokens", C.c_uint32),
+                ("scale", C.c_float)]
+
+
+def build(verbose=False):
+    """Compiles the library in-tree with nvcc for sm_100a (make in csrc/)."""
+    cmd = ["make", "-C", os.path.join(_HERE, "csrc"), "-j8"]
+    subprocess.check_call(cmd, stdout=None if verbose else subprocess.DEVNULL)
+    return LIB_PATH
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol include/saetta_b200.h declares.
+_P, _Z, _I, _U32, _U64 = C.c_void_p, C.c_size_t, C.c_int, C.c_uint32, C.c_uint64
+_PP = C.POINTER(C.c_void_p)
+SYMBOLS = {
+    "saetta_last_error": (C.c_char_p, []),
+    "saetta_version": (C.c_char_p, []),
+    "saetta_quant_rows_create": (_I, [_I, _I, _Z, _Z, _PP]),
+    "saetta_quant_rows_wrap": (_I, [_I, _I, _Z, _Z, _P, _P, _P, _PP]),
+    "saetta_quant_rows_destroy": (None, [_P]),
+    "saetta_quant_rows_buffers": (_I, [_P, _PP, _PP, _PP]),
+    "saetta_quant_rows_record_at": (_I, [_P, _P, _P, _P]),
+    "saetta_quant_rows_encode": (_I, [_P, _P, _Z, _Z, _P]),
+    "saetta_quant_rows_encode_dequantize": (_I, [_P, _P, _I, _Z, _P]),
+    "saetta_quantize_host": (_I, [_P, _Z, _I, _P, _P, _P]),
+    "saetta_dequantize_host": (_I, [_P, _P, _P, _Z, _I, _P]),
+    "saetta_kv_cache_create": (_I, [_I, _I, _Z, _Z, _Z, _Z, _PP]),
+    "saetta_kv_cache_destroy": (None, [_P]),
+    "saetta_kv_cache_capacity": (_Z, [_P]),
+    "saetta_kv_cache_bits": (_I, [_P]),
+    "saetta_kv_cache_buffers": (_I, [_P, _PP, C.POINTER(_Z), C.POINTER(_I)]),
+    "saetta_kv_cache_quant": (_I, [_P, _PP, _PP]),
+    "saetta_kv_cache_resize": (_I, [_P, _Z, _P]),
+    "saetta_kv_cache_store": (_I, [_P, _P, _P, _P, _Z, _P]),
+    "saetta_kv_cache_store_at": (_I, [_P, _P, _P, _Z, _Z, _P]),
+    "saetta_kv_cache_set_dtype": (_I, [_P, _I]),
+    "saetta_row_backup_create": (_I, [_PP]),
+    "saetta_row_backup_destroy": (None, [_P]),
+    "saetta_row_backup_save": (_I, [_P, _PP, _Z, _Z, _Z, _P]),
+    "saetta_row_backup_restore": (_I, [_P, _PP, _Z, _P]),
+    "saetta_row_backup_clear": (None, [_P]),
+    "saetta_row_backup_bytes": (_U64, [_P]),
+    "saetta_decode_create": (_I, [_I, _Z, _Z, _Z, _Z, _Z, _PP]),
+    "saetta_decode_destroy": (None, [_P]),
+    "saetta_decode_record": (_I, [_P, _Z, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "saetta_decode_record_quant": (_I, [_P, _Z, _P, _P, _P, _P, _P, _P, _P]),
+    "saetta_decode_record_cache": (_I, [_P, _Z, _P, _P, _P, _P, _P, _P]),
+    "saetta_decode_splits": (_I, [_P]),
+    "saetta_decode_device_status": (_I, [_P, _P, C.POINTER(_U32)]),
+    "saetta_decode_batch_create": (_I, [_I, _Z, _Z, _Z, _Z, _Z, _PP]),
+    "saetta_decode_batch_destroy": (None, [_P]),
+    "saetta_decode_batch_record": (_I, [_P, _Z, _PP, C.POINTER(_U32), _P, _P, _P, _P]),
+    "saetta_decode_partial_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P]),
+    "saetta_merge_partials": (_I, [_I, _P, _Z, _Z, _Z, _P, _P, _P]),
+    "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
+    "saetta_att_gemm_destroy": (None, [_P]),
+    "saetta_att_gemm_reserve": (_I, [_P, _Z]),
+    "saetta_att_gemm_encode": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, FlashParams, _P]),
+    "saetta_att_gemm_partial": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, FlashParams, _Z, _Z, _P]),
+    "saetta_prefill_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, FlashParams, _P]),
+}
+
+
+def lib():
+    """The loaded library; raises if it has not been built (no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise SaettaError(CUDA, f"{LIB_PATH} is missing: build it with saetta_macqwen_b200.build() "
+                                    "(nvcc, sm_100a); there is no CPU fallback")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            f = getattr(l, name)
+            f.restype, f.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+def _check(rc):
+    if rc:
+        raise SaettaError(rc, lib().saetta_last_error().decode())
+
+
+def ptr(x):
+    """Device (or host) address of a torch tensor, numpy array, ctypes object or int."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    return C.addressof(x)
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+class QuantRows:
+    """src/kv_quant.rs:158-283."""
+
+    def __init__(self, device, bits, values, capacity, _handle=None, _borrowed=False):
+        self.bits, self.per_token, self.capacity = bits, values // 64, capacity
+        self._borrowed = _borrowed
+        if _handle is None:
+            h = C.c_void_p()
+            _check(lib().saetta_quant_rows_create(device, bits, values, capacity, C.byref(h)))
+            _handle = h
+        self.h = _handle
+
+    @classmethod
+    def wrap(cls, device, bits, values, capacity, data, scales, biases):
+        h = C.c_void_p()
+        _check(lib().saetta_quant_rows_wrap(device, bits, values, capacity, ptr(data), ptr(scales), ptr(biases),
+                                            C.byref(h)))
+        r = cls(device, bits, values, capacity, _handle=h)
+        r._keep = (data, scales, biases)
+        return r
+
+    def buffers(self):
+        d, s, z = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        _check(lib().saetta_quant_rows_buffers(self.h, C.byref(d), C.byref(s), C.byref(z)))
+        return d.value, s.value, z.value
+
+    def record_at(self, x, params, stream=None):
+        """record / record_at: one row at params.position (params on the device)."""
+        _check(lib().saetta_quant_rows_record_at(self.h, ptr(x), ptr(params), _stream(stream)))
+
+    record = record_at
+
+    def encode(self, x, pos, tokens, stream=None):
+        _check(lib().saetta_quant_rows_encode(self.h, ptr(x), pos, tokens, _stream(stream)))
+
+    def encode_dequantize(self, out, tokens, dtype=F16, stream=None):
+        _check(lib().saetta_quant_rows_encode_dequantize(self.h, ptr(out), dtype, tokens, _stream(stream)))
+
+    def __del__(self):
+        if getattr(self, "h", None) and not self._borrowed and _lib is not None:
+            _lib.saetta_quant_rows_destroy(self.h)
+            self.h = None
+
+
+class GpuKvCache:
+    """src/gpu_layers.rs:179-293; bits 16/8/4 (and 32 for the f32 configuration)."""
+
+    def __init__(self, device, bits, capacity, heads=16, kv_heads=2, head_dim=256, dtype=F16):
+        h = C.c_void_p()
+        _check(lib().saetta_kv_cache_create(device, bits, heads, kv_heads, head_dim, capacity, C.byref(h)))
+        self.h, self.bits, self.device = h, bits, device
+        self.heads, self.kv_heads, self.head_dim = heads, kv_heads, head_dim
+        if bits == 16:
+            _check(lib().saetta_kv_cache_set_dtype(h, dtype))
+
+    @classmethod
+    def with_bits(cls, device, capacity, bits, **kw):
+        return cls(device, bits, capacity, **kw)
+
+    @property
+    def capacity(self):
+        return lib().saetta_kv_cache_capacity(self.h)
+
+    def buffers(self):
+        """[(device pointer, row bytes)] in the order of GpuKvCache::buffers."""
+        b, rb, n = (C.c_void_p * 6)(), (C.c_size_t * 6)(), C.c_int()
+        _check(lib().saetta_kv_cache_buffers(self.h, b, rb, C.byref(n)))
+        return [(b[i], rb[i]) for i in range(n.value)]
+
+    def quant(self):
+        k, v = C.c_void_p(), C.c_void_p()
+        _check(lib().saetta_kv_cache_quant(self.h, C.byref(k), C.byref(v)))
+        if not k.value:
+            return None
+        values = self.kv_heads * self.head_dim
+        return (QuantRows(self.device, self.bits, values, self.capacity, _handle=k, _borrowed=True),
+                QuantRows(self.device, self.bits, values, self.capacity, _handle=v, _borrowed=True))
+
+    def resize(self, capacity, stream=None):
+        _check(lib().saetta_kv_cache_resize(self.h, capacity, _stream(stream)))
+
+    def store(self, k, v, params, rows=1, stream=None):
+        """The decode/verify store site: rows at params.position + r."""
+        _check(lib().saetta_kv_cache_store(self.h, ptr(k), ptr(v), ptr(params), rows, _stream(stream)))
+
+    def store_at(self, k, v, pos, tokens, stream=None):
+        """The prefill store site: tokens rows at pos."""
+        _check(lib().saetta_kv_cache_store_at(self.h, ptr(k), ptr(v), pos, tokens, _stream(stream)))
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_kv_cache_destroy(self.h)
+            self.h = None
+
+
+class RowBackup:
+    """src/gpu_cache.rs:192-286."""
+
+    def __init__(self):
+        h = C.c_void_p()
+        _check(lib().saetta_row_backup_create(C.byref(h)))
+        self.h = h
+
+    @staticmethod
+    def _arr(caches):
+        return (C.c_void_p * len(caches))(*[c.h for c in caches])
+
+    def save(self, caches, start, n, stream=None):
+        _check(lib().saetta_row_backup_save(self.h, self._arr(caches), len(caches), start, n, _stream(stream)))
+
+    def restore(self, caches, stream=None):
+        _check(lib().saetta_row_backup_restore(self.h, self._arr(caches), len(caches), _stream(stream)))
+
+    def clear(self):
+        lib().saetta_row_backup_clear(self.h)
+
+    def bytes(self):
+        return lib().saetta_row_backup_bytes(self.h)
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_row_backup_destroy(self.h)
+            self.h = None
+
+
+class AttentionRows:
+    """src/rows.rs:307-494; with rows == 1 it is src/attention.rs:19-171 DecodeAttention."""
+
+    def __init__(self, device, heads, kv_heads, capacity, rows, head_dim=256):
+        h = C.c_void_p()
+        _check(lib().saetta_decode_create(device, heads, kv_heads, head_dim, capacity, rows, C.byref(h)))
+        self.h, self.rows = h, rows
+
+    @property
+    def splits(self):
+        return lib().saetta_decode_splits(self.h)
+
+    def record(self, m, q, keys, values, q_and_gate, out, params, dtype=F16, stream=None):
+        _check(lib().saetta_decode_record(self.h, m, ptr(q), ptr(keys), ptr(values), dtype, ptr(q_and_gate),
+                                          ptr(out), ptr(params), _stream(stream)))
+
+    def record_quant(self, m, q, keys, values, q_and_gate, out, params, stream=None):
+        _check(lib().saetta_decode_record_quant(self.h, m, ptr(q), keys.h, values.h, ptr(q_and_gate), ptr(out),
+                                                ptr(params), _stream(stream)))
+
+    def record_cache(self, m, q, cache, q_and_gate, out, params, stream=None):
+        _check(lib().saetta_decode_record_cache(self.h, m, ptr(q), cache.h, ptr(q_and_gate), ptr(out), ptr(params),
+                                                _stream(stream)))
+
+    def partial_cache(self, m, q, cache, part, params, row_step=1, stream=None):
+        _check(lib().saetta_decode_partial_cache(self.h, m, ptr(q), cache.h, ptr(part), row_step, ptr(params),
+                                                 _stream(stream)))
+
+    def device_status(self, stream=None):
+        s = C.c_uint32()
+        _check(lib().saetta_decode_device_status(self.h, _stream(stream), C.byref(s)))
+        return s.value
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_decode_destroy(self.h)
+            self.h = None
+
+
+class DecodeAttention(AttentionRows):
+    """src/attention.rs:19-171."""
+
+    def __init__(self, device, heads, kv_heads, head_dim, capacity):
+        super().__init__(device, heads, kv_heads, capacity, 1, head_dim=head_dim)
+
+    def record(self, q, keys, values, q_and_gate, out, params, dtype=F16, stream=None):
+        super().record(1, q, keys, values, q_and_gate, out, params, dtype=dtype, stream=stream)
+
+    def record_quant(self, q, keys, values, q_and_gate, out, params, stream=None):
+        super().record_quant(1, q, keys, values, q_and_gate, out, params, stream=stream)
+
+
+class DecodeBatch:
+    """One decode row for each of many sequences with ragged lengths (no reference counterpart)."""
+
+    def __init__(self, device, max_seqs, heads=16, kv_heads=2, head_dim=256):
+        h = C.c_void_p()
+        _check(lib().saetta_decode_batch_create(device, heads, kv_heads, head_dim, max_seqs, 0, C.byref(h)))
+        self.h = h
+
+    def record(self, caches, kv_lens, q, q_and_gate, out, stream=None):
+        n = len(caches)
+        arr = (C.c_void_p * n)(*[c.h for c in caches])
+        lens = (C.c_uint32 * n)(*[int(x) for x in kv_lens])
+        _check(lib().saetta_decode_batch_record(self.h, n, arr, lens, ptr(q), ptr(q_and_gate), ptr(out),
+                                                _stream(stream)))
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_decode_batch_destroy(self.h)
+            self.h = None
+
+
+def merge_partials(device, parts, ranks, rows, heads, q_and_gate, out, stream=None):
+    """LSE merge of [ranks][rows][heads][PART_STRIDE] partials, then the gate."""
+    _check(lib().saetta_merge_partials(device, ptr(parts), ranks, rows, heads, ptr(q_and_gate), ptr(out),
+                                       _stream(stream)))
+
+
+class AttGemm:
+    """src/attention_gemm.rs:93-363."""
+
+    def __init__(self, device, chunk, kv_heads):
+        h = C.c_void_p()
+        _check(lib().saetta_att_gemm_create(device, chunk, kv_heads, C.byref(h)))
+        self.h = h
+
+    def reserve(self, tokens):
+        _check(lib().saetta_att_gemm_reserve(self.h, tokens))
+
+    def encode(self, q, keys, values, quant, q_and_gate, out, p, dtype=BF16, stream=None):
+        kq, vq = (quant[0].h, quant[1].h) if quant else (None, None)
+        _check(lib().saetta_att_gemm_encode(self.h, ptr(q), dtype, ptr(keys), ptr(values), kq, vq, ptr(q_and_gate),
+                                            ptr(out), p, _stream(stream)))
+
+    def partial(self, q, keys, values, quant, part, p, key_lo, key_hi, dtype=BF16, stream=None):
+        kq, vq = (quant[0].h, quant[1].h) if quant else (None, None)
+        _check(lib().saetta_att_gemm_partial(self.h, ptr(q), dtype, ptr(keys), ptr(values), kq, vq, ptr(part), p,
+                                             key_lo, key_hi, _stream(stream)))
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_att_gemm_destroy(self.h)
+            self.h = None
+
+
+def prefill_encode(device, q, keys, values, q_and_gate, out, p, dtype=BF16, stream=None):
+    """src/attention_prefill.rs:39-72 `encode`."""
+    _check(lib().saetta_prefill_encode(device, ptr(q), dtype, ptr(keys), ptr(values), ptr(q_and_gate), ptr(out), p,
+                                       _stream(stream)))
+
+
+def quantize_host(x, bits):
+    """saetta_quantize_host on a numpy f32 array: (data, scales, biases)."""
+    import numpy as np
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    g = x.size // 64
+    data, s, z = np.empty(g * 2 * bits, np.uint32), np.empty(g, np.uint16), np.empty(g, np.uint16)
+    _check(lib().saetta_quantize_host(ptr(x), x.size, bits, ptr(data), ptr(s), ptr(z)))
+    return data, s, z
+
+
+def dequantize_host(data, scales, biases, bits):
+    import numpy as np
+    data = np.ascontiguousarray(data, np.uint32)
+    s, z = np.ascontiguousarray(scales, np.uint16), np.ascontiguousarray(biases, np.uint16)
+    out = np.empty(s.size * 64, np.float32)
+    _check(lib().saetta_dequantize_host(ptr(data), ptr(s), ptr(z), s.size, bits, ptr(out)))
+    return out

@@ -1,0 +1,850 @@
+// The C ABI (include/saetta_b200.h): argument checks, object lifetimes, and the
+// choice of kernel.  Every misuse the reference answers with assert!/panic!
+// (src/attention.rs:49-57, src/rows.rs:390,459, src/kv_quant.rs:57,168) comes
+// back as a status code here, before anything is launched.
+#include <cstdio>
+#include <cstring>
+#include <algorithm>
+#include <cmath>
+#include <new>
+
+#include "host.hpp"
+
+namespace saetta {
+
+static thread_local std::string g_error;
+
+void set_error(const std::string &msg) { g_error = msg; }
+int fail(int code, const std::string &msg) {
+    g_error = msg;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char *what) {
+    g_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return e == cudaErrorMemoryAllocation ? SAETTA_ERR_NO_MEM : SAETTA_ERR_CUDA;
+}
+
+int sm_count(int device) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) return 148;
+    return n;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int alloc_zero(void **p, size_t bytes) {
+    SAETTA_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+    SAETTA_CUDA(cudaMemset(*p, 0, bytes ? bytes : 16));
+    return SAETTA_OK;
+}
+
+static KvView view_of(const saetta_quant_rows *k, const saetta_quant_rows *v) {
+    KvView kv;
+    kv.bits = k->bits;
+    kv.k = k->data, kv.v = v->data;
+    kv.ks = k->scales, kv.kz = k->biases, kv.vs = v->scales, kv.vz = v->biases;
+    kv.kv_heads = uint32_t(k->per_token / kGroupsPerHead);
+    return kv;
+}
+
+// One-time per-device raise of the kernels' dynamic shared-memory limits.
+static int configure_device(int device) {
+    static bool done[64] = {};
+    if (device >= 0 && device < 64 && done[device]) return SAETTA_OK;
+    int rc = decode_quant_configure(device);
+    if (!rc) rc = decode_exact_configure(device);
+    if (!rc) rc = prefill_configure(device);
+    if (!rc && device >= 0 && device < 64) done[device] = true;
+    return rc;
+}
+
+} // namespace saetta
+
+using namespace saetta;
+
+extern "C" {
+
+const char *saetta_last_error(void) { return g_error.c_str(); }
+const char *saetta_version(void) { return "saetta_b200 0.1 (sm_100a)"; }
+
+// ------------------------------------------------------------------ QuantRows
+
+static int quant_rows_check(int bits, size_t values) {
+    if (bits != 8 && bits != 4) return fail(SAETTA_ERR_BAD_SHAPE, "QuantRows: bits must be 8 or 4 (a half cache has no codes)");
+    if (!values || values % kGroup) return fail(SAETTA_ERR_BAD_SHAPE, "QuantRows: values must be a multiple of 64");
+    return SAETTA_OK;
+}
+
+int saetta_quant_rows_create(int device, int bits, size_t values, size_t capacity, saetta_quant_rows **out) {
+    if (!out) return fail(SAETTA_ERR_BAD_ARG, "QuantRows::new: out is null");
+    if (int rc = quant_rows_check(bits, values)) return rc;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "QuantRows::new: cannot select the device");
+    auto *r = new (std::nothrow) saetta_quant_rows();
+    if (!r) return fail(SAETTA_ERR_NO_MEM, "QuantRows::new: host allocation");
+    r->device = device, r->bits = bits, r->per_token = values / kGroup, r->capacity = capacity, r->owns = true;
+    const size_t groups = r->per_token * capacity;
+    int rc = alloc_zero(&r->data, groups * 2 * size_t(bits) * 4);
+    if (!rc) rc = alloc_zero(&r->scales, groups * 2);
+    if (!rc) rc = alloc_zero(&r->biases, groups * 2);
+    if (rc) {
+        saetta_quant_rows_destroy(r);
+        return rc;
+    }
+    *out = r;
+    return SAETTA_OK;
+}
+
+int saetta_quant_rows_wrap(int device, int bits, size_t values, size_t capacity, void *data_dev, void *scales_dev,
+                           void *biases_dev, saetta_quant_rows **out) {
+    if (!out || !data_dev || !scales_dev || !biases_dev) return fail(SAETTA_ERR_BAD_ARG, "QuantRows wrap: null pointer");
+    if (int rc = quant_rows_check(bits, values)) return rc;
+    if (!aligned16(data_dev) || !aligned16(scales_dev) || !aligned16(biases_dev))
+        return fail(SAETTA_ERR_BAD_ARG, "QuantRows wrap: buffers must be 16-byte aligned");
+    auto *r = new (std::nothrow) saetta_quant_rows();
+    if (!r) return fail(SAETTA_ERR_NO_MEM, "QuantRows wrap: host allocation");
+    r->device = device, r->bits = bits, r->per_token = values / kGroup, r->capacity = capacity;
+    r->data = data_dev, r->scales = scales_dev, r->biases = biases_dev, r->owns = false;
+    *out = r;
+    return SAETTA_OK;
+}
+
+void saetta_quant_rows_destroy(saetta_quant_rows *r) {
+    if (!r) return;
+    if (r->owns) {
+        DeviceGuard guard(r->device);
+        cudaFree(r->data);
+        cudaFree(r->scales);
+        cudaFree(r->biases);
+    }
+    delete r;
+}
+
+int saetta_quant_rows_buffers(const saetta_quant_rows *r, void **data_dev, void **scales_dev, void **biases_dev) {
+    if (!r) return fail(SAETTA_ERR_BAD_ARG, "QuantRows: null handle");
+    if (data_dev) *data_dev = r->data;
+    if (scales_dev) *scales_dev = r->scales;
+    if (biases_dev) *biases_dev = r->biases;
+    return SAETTA_OK;
+}
+
+int saetta_quant_rows_record_at(saetta_quant_rows *r, const float *x_dev, const saetta_token_params *params_dev,
+                                void *stream) {
+    if (!r || !x_dev || !params_dev) return fail(SAETTA_ERR_BAD_ARG, "QuantRows::record: null pointer");
+    if (!aligned16(x_dev)) return fail(SAETTA_ERR_BAD_ARG, "QuantRows::record: x must be 16-byte aligned");
+    DeviceGuard guard(r->device);
+    return launch_kv_quantize(r->bits, uint32_t(r->per_token), x_dev, r, nullptr, nullptr, 1, 0, params_dev,
+                              (cudaStream_t)stream);
+}
+
+int saetta_quant_rows_encode(saetta_quant_rows *r, const float *x_dev, size_t pos, size_t tokens, void *stream) {
+    if (!r || (!x_dev && tokens)) return fail(SAETTA_ERR_BAD_ARG, "QuantRows::encode: null pointer");
+    if (pos + tokens > r->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "QuantRows::encode: pos + tokens exceeds the capacity");
+    if (!aligned16(x_dev)) return fail(SAETTA_ERR_BAD_ARG, "QuantRows::encode: x must be 16-byte aligned");
+    DeviceGuard guard(r->device);
+    return launch_kv_quantize(r->bits, uint32_t(r->per_token), x_dev, r, nullptr, nullptr, tokens, pos, nullptr,
+                              (cudaStream_t)stream);
+}
+
+int saetta_quant_rows_encode_dequantize(const saetta_quant_rows *r, void *out_dev, int dtype, size_t tokens,
+                                        void *stream) {
+    if (!r || (!out_dev && tokens)) return fail(SAETTA_ERR_BAD_ARG, "QuantRows::encode_dequantize: null pointer");
+    if (dtype != SAETTA_F16 && dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "encode_dequantize: dtype");
+    if (tokens > r->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "encode_dequantize: tokens exceeds the capacity");
+    if (!aligned16(out_dev)) return fail(SAETTA_ERR_BAD_ARG, "encode_dequantize: out must be 16-byte aligned");
+    DeviceGuard guard(r->device);
+    return launch_kv_dequantize(r, out_dev, dtype, tokens, (cudaStream_t)stream);
+}
+
+// Host restatement of the kernels' arithmetic (src/kv_quant.rs:54-105); the
+// narrowing to binary16 is the hardware-equivalent round-to-nearest-even.
+static uint16_t host_f16(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    const uint32_t sign = (x >> 16) & 0x8000u, exp = (x >> 23) & 0xffu;
+    uint32_t man = x & 0x7fffffu;
+    if (exp == 0xff) return uint16_t(sign | 0x7c00u | (man ? 0x200u | (man >> 13) : 0));
+    const int e = int(exp) - 112;
+    if (e >= 31) return uint16_t(sign | 0x7c00u);
+    if (e <= 0) {
+        if (e < -10) return uint16_t(sign);
+        man |= 0x800000u;
+        const uint32_t shift = uint32_t(14 - e);
+        uint32_t h = man >> shift;
+        const uint32_t rem = man & ((1u << shift) - 1), mid = 1u << (shift - 1);
+        if (rem > mid || (rem == mid && (h & 1))) h++;
+        return uint16_t(sign | h);
+    }
+    uint32_t h = (uint32_t(e) << 10) | (man >> 13);
+    const uint32_t rem = man & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (h & 1))) h++;
+    return uint16_t(sign | h);
+}
+static float host_f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t(h) & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (!man) {
+            bits = sign;
+        } else {
+            float v = float(man) * 5.9604644775390625e-08f;
+            memcpy(&bits, &v, 4);
+            bits |= sign;
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+int saetta_quantize_host(const float *x, size_t n, int bits, uint32_t *data, uint16_t *scales, uint16_t *biases) {
+    if (!x || !data || !scales || !biases) return fail(SAETTA_ERR_BAD_ARG, "quantize: null pointer");
+    if ((bits != 8 && bits != 4) || n % kGroup) return fail(SAETTA_ERR_BAD_SHAPE, "quantize: bits 8 or 4, length a multiple of 64");
+    const float levels = float((1u << bits) - 1);
+    const size_t per_word = 32 / size_t(bits);
+    size_t w = 0;
+    for (size_t g = 0; g < n / kGroup; g++) {
+        const float *grp = x + g * kGroup;
+        float lo = INFINITY, hi = -INFINITY;
+        for (int i = 0; i < kGroup; i++) lo = fminf(lo, grp[i]), hi = fmaxf(hi, grp[i]);
+        const volatile float range = hi - lo;
+        const volatile float sd = range / levels;
+        const uint16_t s = host_f16(sd), z = host_f16(lo);
+        const float sf = host_f16_to_f32(s), zf = host_f16_to_f32(z);
+        const volatile float inv = sf > 0.0f ? 1.0f / sf : 0.0f;
+        for (size_t k = 0; k < size_t(kGroup); k += per_word) {
+            uint32_t word = 0;
+            for (size_t i = 0; i < per_word; i++) {
+                const volatile float d = grp[k + i] - zf;
+                const volatile float t = d * inv;
+                float r = rintf(t);
+                if (r != r) r = 0.0f;
+                r = r < 0.0f ? 0.0f : (r > levels ? levels : r);
+                word |= uint32_t(r) << (i * size_t(bits));
+            }
+            data[w++] = word;
+        }
+        scales[g] = s, biases[g] = z;
+    }
+    return SAETTA_OK;
+}
+
+int saetta_dequantize_host(const uint32_t *data, const uint16_t *scales, const uint16_t *biases, size_t groups,
+                           int bits, float *out) {
+    if (!data || !scales || !biases || !out) return fail(SAETTA_ERR_BAD_ARG, "dequantize: null pointer");
+    if (bits != 8 && bits != 4) return fail(SAETTA_ERR_BAD_SHAPE, "dequantize: bits 8 or 4");
+    const uint32_t mask = (1u << bits) - 1;
+    const size_t per_word = 32 / size_t(bits), words = 2 * size_t(bits);
+    size_t o = 0;
+    for (size_t g = 0; g < groups; g++) {
+        const float s = host_f16_to_f32(scales[g]), z = host_f16_to_f32(biases[g]);
+        for (size_t k = 0; k < words; k++)
+            for (size_t i = 0; i < per_word; i++) {
+                const volatile float p = s * float((data[g * words + k] >> (i * size_t(bits))) & mask);
+                out[o++] = p + z;
+            }
+    }
+    return SAETTA_OK;
+}
+
+// ------------------------------------------------------------------ GpuKvCache
+
+static int kv_cache_alloc(saetta_kv_cache *c, size_t capacity) {
+    c->capacity = capacity;
+    if (c->bits == 8 || c->bits == 4) {
+        saetta_quant_rows *sides[2] = {&c->k, &c->v};
+        for (auto *r : sides) {
+            *r = saetta_quant_rows();
+            r->device = c->device, r->bits = c->bits, r->per_token = c->row_values() / kGroup, r->capacity = capacity;
+            const size_t groups = r->per_token * capacity;
+            if (int rc = alloc_zero(&r->data, groups * 2 * size_t(c->bits) * 4)) return rc;
+            if (int rc = alloc_zero(&r->scales, groups * 2)) return rc;
+            if (int rc = alloc_zero(&r->biases, groups * 2)) return rc;
+        }
+        c->keys = c->k.data, c->values = c->v.data;
+        return SAETTA_OK;
+    }
+    if (int rc = alloc_zero(&c->keys, capacity * c->plain_row_bytes())) return rc;
+    return alloc_zero(&c->values, capacity * c->plain_row_bytes());
+}
+
+static void kv_cache_free(saetta_kv_cache *c) {
+    if (c->bits == 8 || c->bits == 4) {
+        for (auto *r : {&c->k, &c->v}) {
+            cudaFree(r->data), cudaFree(r->scales), cudaFree(r->biases);
+            r->data = r->scales = r->biases = nullptr;
+        }
+    } else {
+        cudaFree(c->keys), cudaFree(c->values);
+    }
+    c->keys = c->values = nullptr;
+}
+
+static size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int saetta_kv_cache_create(int device, int bits, size_t heads, size_t kv_heads, size_t head_dim, size_t capacity,
+                           saetta_kv_cache **out) {
+    if (!out) return fail(SAETTA_ERR_BAD_ARG, "GpuKvCache::new: out is null");
+    if (bits != 32 && bits != 16 && bits != 8 && bits != 4) return fail(SAETTA_ERR_BAD_SHAPE, "GpuKvCache: bits must be 32, 16, 8 or 4");
+    if (head_dim != size_t(kDim)) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention is written for head dim 256");
+    if (!kv_heads || heads != kv_heads * kHeadsPerKv) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention needs 8 q heads per kv head");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "GpuKvCache::new: cannot select the device");
+    auto *c = new (std::nothrow) saetta_kv_cache();
+    if (!c) return fail(SAETTA_ERR_NO_MEM, "GpuKvCache::new: host allocation");
+    c->device = device, c->bits = bits, c->heads = heads, c->kv_heads = kv_heads, c->head_dim = head_dim;
+    if (int rc = kv_cache_alloc(c, round_up(capacity ? capacity : 1, SAETTA_KV_ALIGN))) {
+        kv_cache_free(c);
+        delete c;
+        return rc;
+    }
+    *out = c;
+    return SAETTA_OK;
+}
+
+void saetta_kv_cache_destroy(saetta_kv_cache *c) {
+    if (!c) return;
+    DeviceGuard guard(c->device);
+    kv_cache_free(c);
+    delete c;
+}
+
+size_t saetta_kv_cache_capacity(const saetta_kv_cache *c) { return c ? c->capacity : 0; }
+int saetta_kv_cache_bits(const saetta_kv_cache *c) { return c ? c->bits : 0; }
+
+int saetta_kv_cache_set_dtype(saetta_kv_cache *c, int dtype) {
+    if (!c) return fail(SAETTA_ERR_BAD_ARG, "GpuKvCache: null handle");
+    if (dtype != SAETTA_F16 && dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "GpuKvCache: dtype");
+    c->dtype = dtype;
+    return SAETTA_OK;
+}
+
+int saetta_kv_cache_buffers(const saetta_kv_cache *c, void *buffers_dev[6], size_t row_bytes[6], int *count) {
+    if (!c || !buffers_dev || !row_bytes || !count) return fail(SAETTA_ERR_BAD_ARG, "GpuKvCache::buffers: null pointer");
+    if (c->bits == 8 || c->bits == 4) {
+        void *b[6] = {c->keys, c->values, c->k.scales, c->k.biases, c->v.scales, c->v.biases};
+        const size_t d = c->k.data_row_bytes(), p = c->k.param_row_bytes();
+        const size_t rb[6] = {d, d, p, p, p, p};
+        for (int i = 0; i < 6; i++) buffers_dev[i] = b[i], row_bytes[i] = rb[i];
+        *count = 6;
+    } else {
+        buffers_dev[0] = c->keys, buffers_dev[1] = c->values;
+        row_bytes[0] = row_bytes[1] = c->plain_row_bytes();
+        *count = 2;
+    }
+    return SAETTA_OK;
+}
+
+int saetta_kv_cache_quant(const saetta_kv_cache *c, saetta_quant_rows **keys, saetta_quant_rows **values) {
+    if (!c) return fail(SAETTA_ERR_BAD_ARG, "GpuKvCache: null handle");
+    const bool q = c->bits == 8 || c->bits == 4;
+    if (keys) *keys = q ? const_cast<saetta_quant_rows *>(&c->k) : nullptr;
+    if (values) *values = q ? const_cast<saetta_quant_rows *>(&c->v) : nullptr;
+    return SAETTA_OK;
+}
+
+int saetta_kv_cache_resize(saetta_kv_cache *c, size_t capacity, void *stream) {
+    if (!c) return fail(SAETTA_ERR_BAD_ARG, "GpuKvCache::resize: null handle");
+    DeviceGuard guard(c->device);
+    capacity = round_up(capacity ? capacity : 1, SAETTA_KV_ALIGN);
+    saetta_kv_cache old = *c; // keeps the old pointers
+    void *ob[6];
+    size_t rb[6];
+    int n = 0;
+    saetta_kv_cache_buffers(&old, ob, rb, &n);
+    if (int rc = kv_cache_alloc(c, capacity)) {
+        kv_cache_free(c);
+        *c = old;
+        return rc;
+    }
+    void *nb[6];
+    size_t rb2[6];
+    saetta_kv_cache_buffers(c, nb, rb2, &n);
+    const size_t rows = old.capacity < capacity ? old.capacity : capacity;
+    auto st = (cudaStream_t)stream;
+    for (int i = 0; i < n; i++) SAETTA_CUDA(cudaMemcpyAsync(nb[i], ob[i], rows * rb[i], cudaMemcpyDeviceToDevice, st));
+    SAETTA_CUDA(cudaStreamSynchronize(st));
+    kv_cache_free(&old);
+    return SAETTA_OK;
+}
+
+static int kv_store(saetta_kv_cache *c, const float *k, const float *v, size_t pos, const saetta_token_params *params,
+                    size_t rows, cudaStream_t st) {
+    if (!aligned16(k) || !aligned16(v)) return fail(SAETTA_ERR_BAD_ARG, "kv store: k and v must be 16-byte aligned");
+    DeviceGuard guard(c->device);
+    if (c->bits == 8 || c->bits == 4)
+        return launch_kv_quantize(c->bits, uint32_t(c->k.per_token), k, &c->k, v, &c->v, rows, pos, params, st);
+    const int mode = c->bits == 32 ? 2 : (c->dtype == SAETTA_BF16 ? 1 : 0);
+    return launch_kv_store_plain(mode, k, v, c->keys, c->values, c->row_values(), rows, pos, params, st);
+}
+
+int saetta_kv_cache_store(saetta_kv_cache *c, const float *k_dev, const float *v_dev, const saetta_token_params *params_dev,
+                          size_t rows, void *stream) {
+    if (!c || !k_dev || !v_dev || !params_dev) return fail(SAETTA_ERR_BAD_ARG, "kv store: null pointer");
+    if (rows > SAETTA_MAX_ROWS) return fail(SAETTA_ERR_BAD_SHAPE, "kv store: more rows than MAX_ROWS");
+    return kv_store(c, k_dev, v_dev, 0, params_dev, rows, (cudaStream_t)stream);
+}
+
+int saetta_kv_cache_store_at(saetta_kv_cache *c, const float *k_dev, const float *v_dev, size_t pos, size_t tokens,
+                             void *stream) {
+    if (!c || ((!k_dev || !v_dev) && tokens)) return fail(SAETTA_ERR_BAD_ARG, "kv store: null pointer");
+    if (pos + tokens > c->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "kv store: pos + tokens exceeds the capacity");
+    return kv_store(c, k_dev, v_dev, pos, nullptr, tokens, (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------ RowBackup
+
+int saetta_row_backup_create(saetta_row_backup **out) {
+    if (!out) return fail(SAETTA_ERR_BAD_ARG, "RowBackup::new: out is null");
+    *out = new (std::nothrow) saetta_row_backup();
+    return *out ? SAETTA_OK : fail(SAETTA_ERR_NO_MEM, "RowBackup::new: host allocation");
+}
+
+void saetta_row_backup_clear(saetta_row_backup *b) {
+    if (!b) return;
+    if (b->held) {
+        DeviceGuard guard(b->device);
+        for (auto &p : b->parts) cudaFree(p.copy);
+    }
+    b->parts.clear();
+    b->held = false;
+}
+
+void saetta_row_backup_destroy(saetta_row_backup *b) {
+    saetta_row_backup_clear(b);
+    delete b;
+}
+
+uint64_t saetta_row_backup_bytes(const saetta_row_backup *b) {
+    uint64_t total = 0;
+    if (b && b->held)
+        for (auto &p : b->parts) total += uint64_t(p.row_bytes) * b->n;
+    return total;
+}
+
+int saetta_row_backup_save(saetta_row_backup *b, saetta_kv_cache *const *caches, size_t n_caches, size_t from, size_t n,
+                           void *stream) {
+    if (!b || (!caches && n_caches)) return fail(SAETTA_ERR_BAD_ARG, "RowBackup::save: null pointer");
+    saetta_row_backup_clear(b);
+    if (!n || !n_caches) return SAETTA_OK;
+    for (size_t i = 0; i < n_caches; i++)
+        if (!caches[i] || from + n > caches[i]->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "RowBackup::save: rows outside the cache");
+    b->device = caches[0]->device;
+    DeviceGuard guard(b->device);
+    b->from = from, b->n = n, b->held = true;
+    for (size_t i = 0; i < n_caches; i++) {
+        void *bufs[6];
+        size_t rb[6];
+        int cnt = 0;
+        saetta_kv_cache_buffers(caches[i], bufs, rb, &cnt);
+        for (int j = 0; j < cnt; j++) {
+            void *copy = nullptr;
+            cudaError_t e = cudaMalloc(&copy, n * rb[j]);
+            if (e != cudaSuccess) {
+                saetta_row_backup_clear(b);
+                return cuda_fail(e, "RowBackup::save: cudaMalloc");
+            }
+            b->parts.push_back({copy, rb[j]});
+            SAETTA_CUDA(cudaMemcpyAsync(copy, (const char *)bufs[j] + from * rb[j], n * rb[j], cudaMemcpyDeviceToDevice,
+                                        (cudaStream_t)stream));
+        }
+    }
+    return SAETTA_OK;
+}
+
+int saetta_row_backup_restore(saetta_row_backup *b, saetta_kv_cache *const *caches, size_t n_caches, void *stream) {
+    if (!b) return fail(SAETTA_ERR_BAD_ARG, "RowBackup::restore: null handle");
+    if (!b->held) return SAETTA_OK;
+    DeviceGuard guard(b->device);
+    size_t k = 0;
+    for (size_t i = 0; i < n_caches; i++) {
+        void *bufs[6];
+        size_t rb[6];
+        int cnt = 0;
+        saetta_kv_cache_buffers(caches[i], bufs, rb, &cnt);
+        for (int j = 0; j < cnt; j++, k++) {
+            if (k >= b->parts.size() || b->parts[k].row_bytes != rb[j] || b->from + b->n > caches[i]->capacity)
+                return fail(SAETTA_ERR_BAD_SHAPE, "RowBackup::restore: caches differ from the ones saved");
+            SAETTA_CUDA(cudaMemcpyAsync((char *)bufs[j] + b->from * rb[j], b->parts[k].copy, b->n * rb[j],
+                                        cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+        }
+    }
+    // The copies are freed once the stream has used them.
+    SAETTA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    saetta_row_backup_clear(b);
+    return SAETTA_OK;
+}
+
+// ------------------------------------------------------------------ DecodeAttention / AttentionRows
+
+int saetta_decode_create(int device, size_t heads, size_t kv_heads, size_t head_dim, size_t capacity, size_t rows,
+                         saetta_decode **out) {
+    if (!out) return fail(SAETTA_ERR_BAD_ARG, "DecodeAttention::new: out is null");
+    if (head_dim != size_t(kDim)) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention is written for head dim 256");
+    if (!kv_heads || heads != kv_heads * kHeadsPerKv) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention needs 8 q heads per kv head");
+    if (!rows || rows > SAETTA_MAX_ROWS) return fail(SAETTA_ERR_BAD_SHAPE, "AttentionRows: rows must be 1..8");
+    if (!capacity) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: capacity is 0");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "DecodeAttention::new: cannot select the device");
+    if (int rc = configure_device(device)) return rc;
+    auto *op = new (std::nothrow) saetta_decode();
+    if (!op) return fail(SAETTA_ERR_NO_MEM, "DecodeAttention::new: host allocation");
+    op->device = device, op->heads = heads, op->kv_heads = kv_heads, op->capacity = capacity, op->rows = rows;
+    const size_t tiles = (capacity + 31) / 32;
+    const size_t sms = size_t(sm_count(device));
+    op->splits = int(tiles < sms ? tiles : sms);
+    const size_t per_row = std::max(decode_quant_part_floats(kv_heads), heads * size_t(kPartStride));
+    int rc = alloc_zero((void **)&op->parts, size_t(op->splits) * rows * per_row * sizeof(float));
+    if (!rc) rc = alloc_zero((void **)&op->status, 16);
+    if (rc) {
+        saetta_decode_destroy(op);
+        return rc;
+    }
+    *out = op;
+    return SAETTA_OK;
+}
+
+void saetta_decode_destroy(saetta_decode *op) {
+    if (!op) return;
+    DeviceGuard guard(op->device);
+    cudaFree(op->parts);
+    cudaFree(op->status);
+    delete op;
+}
+
+int saetta_decode_splits(const saetta_decode *op) { return op ? op->splits : 0; }
+
+int saetta_decode_device_status(saetta_decode *op, void *stream, uint32_t *status) {
+    if (!op || !status) return fail(SAETTA_ERR_BAD_ARG, "device_status: null pointer");
+    DeviceGuard guard(op->device);
+    SAETTA_CUDA(cudaMemcpyAsync(status, op->status, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SAETTA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (*status) return fail(SAETTA_ERR_TIMEOUT, "a bounded device-side wait gave up");
+    return SAETTA_OK;
+}
+
+static int decode_check(const saetta_decode *op, size_t m, const void *q, const void *out, const void *params) {
+    if (!op || !q || !out || !params) return fail(SAETTA_ERR_BAD_ARG, "decode attention: null pointer");
+    if (!m || m > op->rows) return fail(SAETTA_ERR_BAD_SHAPE, "AttentionRows::record: m exceeds the rows the op was made for");
+    if (!aligned16(q)) return fail(SAETTA_ERR_BAD_ARG, "decode attention: q must be 16-byte aligned");
+    return SAETTA_OK;
+}
+
+static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView &kv, size_t kv_capacity,
+                      const float *q_and_gate, float *out, float *part_out, uint32_t row_step,
+                      const saetta_token_params *params, cudaStream_t st) {
+    if (kv.kv_heads != op->kv_heads) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache and op disagree on kv heads");
+    if (kv_capacity > op->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache larger than the op's capacity");
+    if (kv_capacity % 32) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache capacity must be a multiple of 32");
+    DeviceGuard guard(op->device);
+    const uint32_t heads = uint32_t(op->heads);
+    if (kv.bits == 8 || kv.bits == 4) {
+        if (kv.kv_heads != 2) return fail(SAETTA_ERR_UNSUPPORTED, "quantised decode attention is built for 2 kv heads");
+        if (int rc = launch_decode_quant(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
+                                         uint32_t(kv_capacity), params, st))
+            return rc;
+        return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
+                                 part_out, st);
+    }
+    if (int rc = launch_decode_exact(kv, q, op->parts, uint32_t(m), row_step, op->splits, uint32_t(kv_capacity), params, st))
+        return rc;
+    return launch_merge_logical(op->parts, uint32_t(op->splits), uint32_t(m), heads, q_and_gate, out, part_out, st);
+}
+
+int saetta_decode_record(saetta_decode *op, size_t m, const float *q_dev, const void *keys_dev, const void *values_dev,
+                         int dtype, const float *q_and_gate_dev, float *out_dev, const saetta_token_params *params_dev,
+                         void *stream) {
+    if (int rc = decode_check(op, m, q_dev, out_dev, params_dev)) return rc;
+    if (!keys_dev || !values_dev || !q_and_gate_dev) return fail(SAETTA_ERR_BAD_ARG, "DecodeAttention::record: null pointer");
+    if (dtype != -1 && dtype != SAETTA_F16 && dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "DecodeAttention::record: dtype");
+    KvView kv;
+    kv.bits = dtype == -1 ? 32 : 16, kv.dtype = dtype == -1 ? SAETTA_F16 : dtype;
+    kv.k = keys_dev, kv.v = values_dev, kv.kv_heads = uint32_t(op->kv_heads);
+    return decode_run(op, m, q_dev, kv, op->capacity / 32 * 32, q_and_gate_dev, out_dev, nullptr, 1, params_dev, (cudaStream_t)stream);
+}
+
+int saetta_decode_record_quant(saetta_decode *op, size_t m, const float *q_dev, const saetta_quant_rows *keys,
+                               const saetta_quant_rows *values, const float *q_and_gate_dev, float *out_dev,
+                               const saetta_token_params *params_dev, void *stream) {
+    if (int rc = decode_check(op, m, q_dev, out_dev, params_dev)) return rc;
+    if (!keys || !values || !q_and_gate_dev) return fail(SAETTA_ERR_BAD_ARG, "DecodeAttention::record_quant: null pointer");
+    if (keys->bits != values->bits || keys->per_token != values->per_token || keys->capacity != values->capacity)
+        return fail(SAETTA_ERR_BAD_SHAPE, "record_quant: keys and values differ in format");
+    return decode_run(op, m, q_dev, view_of(keys, values), keys->capacity, q_and_gate_dev, out_dev, nullptr, 1, params_dev,
+                      (cudaStream_t)stream);
+}
+
+static KvView view_of_cache(const saetta_kv_cache *c) {
+    if (c->bits == 8 || c->bits == 4) return view_of(&c->k, &c->v);
+    KvView kv;
+    kv.bits = c->bits, kv.dtype = c->dtype, kv.k = c->keys, kv.v = c->values, kv.kv_heads = uint32_t(c->kv_heads);
+    return kv;
+}
+
+int saetta_decode_record_cache(saetta_decode *op, size_t m, const float *q_dev, const saetta_kv_cache *cache,
+                               const float *q_and_gate_dev, float *out_dev, const saetta_token_params *params_dev,
+                               void *stream) {
+    if (int rc = decode_check(op, m, q_dev, out_dev, params_dev)) return rc;
+    if (!cache || !q_and_gate_dev) return fail(SAETTA_ERR_BAD_ARG, "decode attention: null pointer");
+    return decode_run(op, m, q_dev, view_of_cache(cache), cache->capacity, q_and_gate_dev, out_dev, nullptr, 1, params_dev,
+                      (cudaStream_t)stream);
+}
+
+int saetta_decode_partial_cache(saetta_decode *op, size_t m, const float *q_dev, const saetta_kv_cache *cache,
+                                float *part_dev, uint32_t row_step, const saetta_token_params *params_dev, void *stream) {
+    if (int rc = decode_check(op, m, q_dev, part_dev, params_dev)) return rc;
+    if (!cache) return fail(SAETTA_ERR_BAD_ARG, "decode attention: null pointer");
+    if (row_step > 1) return fail(SAETTA_ERR_BAD_ARG, "decode partial: row_step is 0 or 1");
+    return decode_run(op, m, q_dev, view_of_cache(cache), cache->capacity, nullptr, nullptr, part_dev, row_step, params_dev,
+                      (cudaStream_t)stream);
+}
+
+int saetta_merge_partials(int device, const float *parts_dev, size_t ranks, size_t rows, size_t heads,
+                          const float *q_and_gate_dev, float *out_dev, void *stream) {
+    if (!parts_dev || !q_and_gate_dev || !out_dev) return fail(SAETTA_ERR_BAD_ARG, "merge_partials: null pointer");
+    if (!ranks || !rows || !heads) return fail(SAETTA_ERR_BAD_SHAPE, "merge_partials: empty shape");
+    DeviceGuard guard(device);
+    return launch_merge_logical(parts_dev, uint32_t(ranks), uint32_t(rows), uint32_t(heads), q_and_gate_dev, out_dev,
+                                nullptr, (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------ batched decode
+
+struct BatchTable { // host mirror of what the kernels read
+    std::vector<Segment> segs;
+    std::vector<uint32_t> cta_first, seq_first;
+};
+
+int saetta_decode_batch_create(int device, size_t heads, size_t kv_heads, size_t head_dim, size_t max_seqs,
+                               size_t max_total_tokens, saetta_decode_batch **out) {
+    if (!out) return fail(SAETTA_ERR_BAD_ARG, "decode batch: out is null");
+    if (head_dim != size_t(kDim) || kv_heads != 2 || heads != 16)
+        return fail(SAETTA_ERR_BAD_SHAPE, "batched decode attention is built for 16 q / 2 kv heads of 256");
+    if (!max_seqs) return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: max_seqs is 0");
+    (void)max_total_tokens;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "decode batch: cannot select the device");
+    if (int rc = configure_device(device)) return rc;
+    auto *op = new (std::nothrow) saetta_decode_batch();
+    if (!op) return fail(SAETTA_ERR_NO_MEM, "decode batch: host allocation");
+    op->device = device, op->heads = heads, op->kv_heads = kv_heads, op->max_seqs = max_seqs;
+    op->ctas = sm_count(device);
+    op->max_parts = max_seqs + size_t(op->ctas); // a sequence adds one part per CTA boundary inside it
+    op->table_bytes = op->max_parts * sizeof(Segment) + (size_t(op->ctas) + 1 + max_seqs + 1) * 4;
+    int rc = alloc_zero((void **)&op->parts, op->max_parts * decode_quant_part_floats(kv_heads) * sizeof(float));
+    if (!rc) rc = alloc_zero(&op->table_dev, op->table_bytes);
+    if (!rc) rc = alloc_zero((void **)&op->status, 16);
+    if (!rc) {
+        cudaError_t e = cudaMallocHost(&op->table_host, op->table_bytes);
+        if (e != cudaSuccess) rc = cuda_fail(e, "cudaMallocHost");
+    }
+    if (!rc) {
+        cudaEvent_t ev;
+        cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e != cudaSuccess) rc = cuda_fail(e, "cudaEventCreate");
+        else op->table_event = ev;
+    }
+    if (rc) {
+        saetta_decode_batch_destroy(op);
+        return rc;
+    }
+    *out = op;
+    return SAETTA_OK;
+}
+
+void saetta_decode_batch_destroy(saetta_decode_batch *op) {
+    if (!op) return;
+    DeviceGuard guard(op->device);
+    cudaFree(op->parts);
+    cudaFree(op->table_dev);
+    cudaFree(op->status);
+    if (op->table_host) cudaFreeHost(op->table_host);
+    if (op->table_event) cudaEventDestroy((cudaEvent_t)op->table_event);
+    delete op;
+}
+
+int saetta_decode_batch_record(saetta_decode_batch *op, size_t n, saetta_kv_cache *const *caches,
+                               const uint32_t *kv_lens_host, const float *q_dev, const float *q_and_gate_dev,
+                               float *out_dev, void *stream) {
+    if (!op || !caches || !kv_lens_host || !q_dev || !q_and_gate_dev || !out_dev)
+        return fail(SAETTA_ERR_BAD_ARG, "decode batch: null pointer");
+    if (!n || n > op->max_seqs) return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: more sequences than the op was made for");
+    const int bits = caches[0] ? caches[0]->bits : 0;
+    if (bits != 8 && bits != 4) return fail(SAETTA_ERR_UNSUPPORTED, "decode batch: caches must be 8- or 4-bit");
+    uint64_t total_tiles = 0;
+    for (size_t i = 0; i < n; i++) {
+        if (!caches[i] || caches[i]->bits != bits || caches[i]->kv_heads != 2)
+            return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: caches differ in format");
+        if (!kv_lens_host[i] || kv_lens_host[i] > caches[i]->capacity)
+            return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: kv_len outside the cache");
+        total_tiles += (kv_lens_host[i] + 31) / 32;
+    }
+    DeviceGuard guard(op->device);
+    // The pinned table is reused: wait until the previous call's copy has read it.
+    if (op->table_event) SAETTA_CUDA(cudaEventSynchronize((cudaEvent_t)op->table_event));
+    // Cut the concatenated tile sequence into equal CTA shares; a share that
+    // crosses a sequence boundary becomes several segments.
+    auto *segs = reinterpret_cast<Segment *>(op->table_host);
+    auto *cta_first = reinterpret_cast<uint32_t *>(segs + op->max_parts);
+    auto *seq_first = cta_first + op->ctas + 1;
+    const uint32_t ctas = uint32_t(op->ctas);
+    uint32_t nseg = 0;
+    {
+        // segments in (sequence, tile) order; parts are numbered in the same order,
+        // so a sequence's parts are contiguous.
+        size_t seq = 0;
+        uint64_t seq_base = 0; // global index of the sequence's first tile
+        uint64_t seq_tiles = (kv_lens_host[0] + 31) / 32;
+        seq_first[0] = 0;
+        for (uint32_t c = 0; c < ctas; c++) {
+            cta_first[c] = nseg;
+            uint64_t lo = total_tiles * c / ctas, hi = total_tiles * (c + 1) / ctas;
+            while (lo < hi) {
+                while (lo >= seq_base + seq_tiles) {
+                    seq_base += seq_tiles;
+                    seq++;
+                    seq_tiles = (kv_lens_host[seq] + 31) / 32;
+                    seq_first[seq] = nseg;
+                }
+                const uint64_t end = hi < seq_base + seq_tiles ? hi : seq_base + seq_tiles;
+                Segment s{};
+                const saetta_kv_cache *kc = caches[seq];
+                s.k = kc->k.data, s.v = kc->v.data, s.ks = kc->k.scales, s.kz = kc->k.biases;
+                s.vs = kc->v.scales, s.vz = kc->v.biases;
+                s.tile_begin = uint32_t(lo - seq_base), s.tile_end = uint32_t(end - seq_base);
+                s.kv_len = kv_lens_host[seq], s.part = nseg, s.seq = uint32_t(seq);
+                if (nseg >= op->max_parts) return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: part table overflow");
+                segs[nseg++] = s;
+                lo = end;
+            }
+        }
+        cta_first[ctas] = nseg;
+        for (size_t s2 = seq + 1; s2 <= n; s2++) seq_first[s2] = nseg;
+    }
+    auto st = (cudaStream_t)stream;
+    SAETTA_CUDA(cudaMemcpyAsync(op->table_dev, op->table_host, op->table_bytes, cudaMemcpyHostToDevice, st));
+    SAETTA_CUDA(cudaEventRecord((cudaEvent_t)op->table_event, st));
+    auto *segs_dev = reinterpret_cast<const Segment *>(op->table_dev);
+    auto *cta_first_dev = reinterpret_cast<const uint32_t *>(segs_dev + op->max_parts);
+    auto *seq_first_dev = cta_first_dev + op->ctas + 1;
+    if (int rc = launch_decode_quant_batched(bits, segs_dev, cta_first_dev, op->ctas, q_dev, op->parts, op->status, st))
+        return rc;
+    return launch_merge_frag(op->parts, nseg, seq_first_dev, uint32_t(n), 2, q_and_gate_dev, out_dev, nullptr, st);
+}
+
+// ------------------------------------------------------------------ prefill
+
+int saetta_att_gemm_create(int device, size_t chunk, size_t kv_heads, saetta_att_gemm **out) {
+    if (!out) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::new: out is null");
+    if (!chunk || !kv_heads) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::new: empty shape");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "AttGemm::new: cannot select the device");
+    if (int rc = configure_device(device)) return rc;
+    auto *op = new (std::nothrow) saetta_att_gemm();
+    if (!op) return fail(SAETTA_ERR_NO_MEM, "AttGemm::new: host allocation");
+    op->device = device, op->chunk = chunk, op->kv_heads = kv_heads;
+    if (int rc = alloc_zero((void **)&op->status, 16)) {
+        delete op;
+        return rc;
+    }
+    *out = op;
+    return SAETTA_OK;
+}
+
+void saetta_att_gemm_destroy(saetta_att_gemm *op) {
+    if (!op) return;
+    DeviceGuard guard(op->device);
+    cudaFree(op->stage_k);
+    cudaFree(op->stage_v);
+    cudaFree(op->status);
+    delete op;
+}
+
+int saetta_att_gemm_reserve(saetta_att_gemm *op, size_t tokens) {
+    if (!op) return fail(SAETTA_ERR_BAD_ARG, "AttGemm: null handle");
+    if (tokens <= op->stage_tokens) return SAETTA_OK;
+    DeviceGuard guard(op->device);
+    tokens = round_up(tokens, 1024);
+    cudaFree(op->stage_k), cudaFree(op->stage_v);
+    op->stage_k = op->stage_v = nullptr, op->stage_tokens = 0;
+    const size_t bytes = tokens * op->kv_heads * kDim * 2;
+    if (int rc = alloc_zero(&op->stage_k, bytes)) return rc;
+    if (int rc = alloc_zero(&op->stage_v, bytes)) return rc;
+    op->stage_tokens = tokens;
+    return SAETTA_OK;
+}
+
+static int prefill_check(const void *q, int dtype, const saetta_flash_params &p) {
+    if (!q) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q is null");
+    if (dtype != SAETTA_F16 && dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: dtype");
+    if (!p.kv_heads || p.heads != p.kv_heads * kHeadsPerKv) return fail(SAETTA_ERR_BAD_SHAPE, "needs 8 q heads per kv head");
+    if (!aligned16(q)) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q must be 16-byte aligned");
+    return SAETTA_OK;
+}
+
+static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const void *keys, const void *values,
+                        const saetta_quant_rows *kq, const saetta_quant_rows *vq, const float *q_and_gate, float *out,
+                        float *part, saetta_flash_params p, size_t key_lo, size_t key_hi, cudaStream_t st) {
+    if (int rc = prefill_check(q, dtype, p)) return rc;
+    if (!p.tokens) return SAETTA_OK;
+    if (p.kv_heads != op->kv_heads) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: kv heads differ from the op's");
+    DeviceGuard guard(op->device);
+    const size_t end = size_t(p.pos) + p.tokens;
+    if (key_hi > end) key_hi = end;
+    if (kq || vq) {
+        if (!kq || !vq || kq->bits != vq->bits) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: quant needs both sides");
+        if (end > kq->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: pos + tokens exceeds the capacity");
+        if (kq->per_token != p.kv_heads * size_t(kGroupsPerHead)) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: quant rows of another shape");
+        if (int rc = saetta_att_gemm_reserve(op, key_hi)) return rc;
+        // The quantised cache is read through a 16-bit copy, as the reference's
+        // kv_stage reads it (src/kv_quant.rs:121-126 semantics).
+        if (int rc = launch_kv_dequantize(kq, op->stage_k, dtype, key_hi, st)) return rc;
+        if (int rc = launch_kv_dequantize(vq, op->stage_v, dtype, key_hi, st)) return rc;
+        keys = op->stage_k, values = op->stage_v;
+    }
+    if (!keys || !values) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: keys or values null");
+    PrefillArgs a{q, keys, values, dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
+                  uint32_t(key_lo), uint32_t(key_hi), p.scale};
+    return launch_prefill(a, op->status, st);
+}
+
+int saetta_att_gemm_encode(saetta_att_gemm *op, const void *q_dev, int dtype, const void *keys_dev, const void *values_dev,
+                           const saetta_quant_rows *keys_q, const saetta_quant_rows *values_q, const float *q_and_gate_dev,
+                           float *out_dev, saetta_flash_params p, void *stream) {
+    if (!op || !q_and_gate_dev || !out_dev) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: null pointer");
+    if (p.tokens > op->chunk) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: more tokens than the chunk the op was made for");
+    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, q_and_gate_dev, out_dev, nullptr, p, 0,
+                        size_t(p.pos) + p.tokens, (cudaStream_t)stream);
+}
+
+int saetta_att_gemm_partial(saetta_att_gemm *op, const void *q_dev, int dtype, const void *keys_dev, const void *values_dev,
+                            const saetta_quant_rows *keys_q, const saetta_quant_rows *values_q, float *part_dev,
+                            saetta_flash_params p, size_t key_lo, size_t key_hi, void *stream) {
+    if (!op || !part_dev) return fail(SAETTA_ERR_BAD_ARG, "AttGemm partial: null pointer");
+    if (key_lo > key_hi) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm partial: key_lo > key_hi");
+    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, nullptr, nullptr, part_dev, p, key_lo,
+                        key_hi, (cudaStream_t)stream);
+}
+
+int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *keys_dev, const void *values_dev,
+                          const float *q_and_gate_dev, float *out_dev, saetta_flash_params p, void *stream) {
+    if (!keys_dev || !values_dev || !q_and_gate_dev || !out_dev) return fail(SAETTA_ERR_BAD_ARG, "prefill encode: null pointer");
+    if (int rc = prefill_check(q_dev, dtype, p)) return rc;
+    if (!p.tokens) return SAETTA_OK;
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "prefill encode: cannot select the device");
+    if (int rc = configure_device(device)) return rc;
+    static uint32_t *status[64] = {};
+    if (device < 0 || device >= 64) return fail(SAETTA_ERR_BAD_ARG, "prefill encode: device");
+    if (!status[device])
+        if (int rc = alloc_zero((void **)&status[device], 16)) return rc;
+    PrefillArgs a{q_dev, keys_dev, values_dev, dtype, q_and_gate_dev, out_dev, nullptr, p.heads, p.kv_heads, p.pos,
+                  p.tokens, 0, p.pos + p.tokens, p.scale};
+    return launch_prefill(a, status[device], (cudaStream_t)stream);
+}
+
+} // extern "C"

@@ -1,0 +1,553 @@
+// Split-KV decode / MTP-verify attention over the 8- and 4-bit KV cache.
+//
+// Stands in for attention_partial_mma_q<8|4> (kernels/attention.metal:242-360)
+// and attention_partial_rows<8|4> (kernels/attention_rows.metal:108-292) of the
+// reference; the merge over parts is in merge.cu.  The design is this file's
+// own and is shaped by HBM bandwidth:
+//
+//  * One persistent CTA per SM owns a contiguous range of 32-token tiles.  A
+//    producer warp streams each tile -- key codes, value codes and the four
+//    scale/bias arrays, six contiguous spans covering BOTH kv heads -- into a
+//    ring of shared-memory stages with bulk (TMA engine) copies signalled on
+//    mbarriers, so every cache byte crosses HBM once and many tiles are in
+//    flight per SM.
+//  * Eight consumer warps each own one (kv head, query row) pair and a share of
+//    the 16-token sub-tiles.  Codes go from shared memory to registers with
+//    128/64-bit loads and are turned into binary16 MMA fragments with byte
+//    permutes (code c becomes the half 1024+c, minus 1024: exact).  The eight
+//    query heads of a kv head are the N dimension of mma.sync m16n8k16, so a
+//    code is dequantised once for all of them.
+//  * Scores are accumulated per 64-value group and only then multiplied by the
+//    group's scale: x = s*c + z is applied exactly as s*(q.c) + z*sum(q), in f32.
+//    The query is split into two halves (hi + lo) so it keeps f32 precision.
+//  * Online softmax per warp with shuffles; the running maximum is only moved
+//    when it grows by more than 2^8 (the accumulators stay in range and are
+//    rarely rescaled).  P goes to the P.V product through movmatrix, multiplied
+//    by the value scales; the value biases ride along as one more MMA.
+//  * Every wait on an mbarrier is bounded; a wait that gives up sets a bit in
+//    the status word, raises the CTA's abort flag and the CTA drains and leaves.
+#include "host.hpp"
+
+namespace saetta {
+
+constexpr int kTile = 32;     // tokens per stage
+constexpr int kSub = 16;      // tokens per MMA sub-tile
+constexpr int kWarps = 8;     // consumer warps
+constexpr int kThreads = (kWarps + 1) * 32;
+constexpr int kKv = 2;        // kv heads covered by one stage
+constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in fragment order
+constexpr int kPartKv = kFragFloats + 16; // + m[8], l[8]
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescale = 8.0f; // move the running maximum when it grows by more than 2^8
+
+template <int BITS>
+struct Stage {
+    static constexpr int kCodeRow = kKv * kDim * BITS / 8; // bytes of codes per token, both kv heads
+    static constexpr int kCodes = kTile * kCodeRow;
+    static constexpr int kParamRow = kKv * kGroupsPerHead * 2; // 16 bytes per token
+    static constexpr int kParams = kTile * kParamRow;
+    static constexpr int kK = 0, kV = kCodes, kKs = 2 * kCodes, kKz = kKs + kParams,
+                         kVs = kKz + kParams, kVz = kVs + kParams;
+    static constexpr int kBytes = 2 * kCodes + 4 * kParams;
+    static constexpr int kStages = BITS == 8 ? 5 : 8;
+};
+
+constexpr int kMergeBytes = 2 * kKv * kFragFloats * 4; // up to two rows per pass merge through smem
+constexpr int kMlFloats = kWarps * 4;                  // per warp: m[2] l[2] of its lane quad... see merge
+template <int BITS>
+constexpr int smem_bytes() {
+    return Stage<BITS>::kStages * Stage<BITS>::kBytes + kMergeBytes + kWarps * 8 * 2 * 4 +
+           2 * Stage<BITS>::kStages * 8 + 16;
+}
+
+struct DecodeArgs {
+    Segment seg;               // the one segment of a single-sequence launch (tiles filled on device)
+    const Segment *segs;       // batched: descriptors, else null
+    const uint32_t *cta_first; // batched: CTA c runs segs[cta_first[c] .. cta_first[c+1])
+    const float *q;            // [rows][16][256]
+    float *parts;              // [part][rows][kv][kPartKv]
+    uint32_t *status;
+    const saetta_token_params *params;
+    uint32_t m;        // query rows
+    uint32_t row_step; // row r sees kv_len + r*row_step keys
+    uint32_t capacity;
+};
+
+__device__ __forceinline__ uint32_t lop_and_or(uint32_t w, uint32_t mask, uint32_t magic) {
+    return (w & mask) | magic;
+}
+
+// The dimension (within the thread's 16 of a group) that the B fragment of
+// k-step j, register `reg`, element e pairs with; must mirror how the key codes
+// are cut into A fragments below.
+template <int BITS>
+__device__ __forceinline__ constexpr int q_dim(int j, int reg, int e) {
+    if (BITS == 8) return 4 * j + 2 * reg + e;          // bytes 4j..4j+3 of the 16
+    return 8 * (j >> 1) + 2 * (j & 1) + reg + 4 * e;    // nibbles {n, n+4} of word j/2
+}
+
+template <int BITS, int ROWS>
+__global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeArgs a) {
+    using St = Stage<BITS>;
+    constexpr int NS = St::kStages;
+    constexpr int NSLOT = kWarps / (kKv * ROWS); // warps sharing one (kv, row)
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *stages = smem;
+    float *merge = reinterpret_cast<float *>(smem + NS * St::kBytes);
+    float *ml = merge + kMergeBytes / 4; // [warp][8 heads][m, l]
+    uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 16);
+    uint64_t *empty = full + NS;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + NS);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // The segments this CTA runs.
+    uint32_t seg_lo = 0, seg_hi = 1;
+    if (a.segs) {
+        seg_lo = a.cta_first[blockIdx.x];
+        seg_hi = a.cta_first[blockIdx.x + 1];
+    }
+    const uint32_t row0 = blockIdx.y * ROWS; // first query row of this pass
+
+    auto load_segment = [&](uint32_t si) -> Segment {
+        if (a.segs) return a.segs[si];
+        Segment s = a.seg;
+        const uint32_t kv_len = a.params->kv_len;
+        uint32_t longest = kv_len + (a.m - 1) * a.row_step;
+        longest = min(longest, a.capacity);
+        const uint32_t tiles = (longest + kTile - 1) / kTile;
+        s.tile_begin = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
+        s.tile_end = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
+        s.kv_len = kv_len;
+        s.part = blockIdx.x;
+        s.seq = 0;
+        return s;
+    };
+
+    if (warp == kWarps) {
+        // ---------------------------------------------------------------- producer
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t si = seg_lo; si < seg_hi && ok; si++) {
+            const Segment s = load_segment(si);
+            for (uint32_t t = s.tile_begin; t < s.tile_end; t++, it++) {
+                const uint32_t st = it % NS, round = it / NS;
+                if (!mbar_wait(&empty[st], (round & 1) ^ 1, abort_flag)) {
+                    if (lane == 0) {
+                        atomicOr(a.status, kStatusEmptyTimeout);
+                        *abort_flag = 1;
+                    }
+                    ok = false;
+                    break;
+                }
+                if (lane == 0) {
+                    uint8_t *dst = stages + st * St::kBytes;
+                    mbar_expect_tx(&full[st], St::kBytes);
+                    const size_t tok = size_t(t) * kTile;
+                    bulk_g2s(dst + St::kK, (const uint8_t *)s.k + tok * St::kCodeRow, St::kCodes, &full[st]);
+                    bulk_g2s(dst + St::kV, (const uint8_t *)s.v + tok * St::kCodeRow, St::kCodes, &full[st]);
+                    bulk_g2s(dst + St::kKs, (const uint8_t *)s.ks + tok * St::kParamRow, St::kParams, &full[st]);
+                    bulk_g2s(dst + St::kKz, (const uint8_t *)s.kz + tok * St::kParamRow, St::kParams, &full[st]);
+                    bulk_g2s(dst + St::kVs, (const uint8_t *)s.vs + tok * St::kParamRow, St::kParams, &full[st]);
+                    bulk_g2s(dst + St::kVz, (const uint8_t *)s.vz + tok * St::kParamRow, St::kParams, &full[st]);
+                }
+                __syncwarp();
+            }
+        }
+        // Leave only once every copy this warp issued has landed (bounded): the
+        // shared memory must not be handed to another CTA with copies in flight.
+        const uint32_t issued = it;
+        for (uint32_t k = issued > NS ? issued - NS : 0; k < issued; k++)
+            mbar_wait(&full[k % NS], (k / NS) & 1, abort_flag, 2000000u);
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    const int kv = warp & 1;
+    const int row_in_pass = (warp >> 1) % ROWS;
+    const int slot = (warp >> 1) / ROWS;
+    const uint32_t row = row0 + row_in_pass;
+    const bool row_live = row < a.m;
+    const int g = lane >> 2, i = lane & 3;
+    constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
+
+    uint32_t it = 0;
+    bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
+    for (uint32_t si = seg_lo; si < seg_hi; si++) {
+        const Segment s = load_segment(si);
+        const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
+
+        // Query fragments of head kv*8+g: 16 dims per group, scaled by log2(e)/16,
+        // split into two halves; and the group sums for the bias term.
+        uint32_t qh[4][8], ql[4][8];
+        uint32_t qsb = 0; // B fragment of the group sums (hi for i<2, lo for i>=2)
+        {
+            float qs[4];
+            const float *qp = a.q + ((size_t(s.seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
+#pragma unroll
+            for (int G = 0; G < 4; G++) {
+                float x[16];
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const float4 v = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
+                    x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
+                }
+                float hi[16], lo[16], sum = 0.f;
+#pragma unroll
+                for (int d = 0; d < 16; d++) {
+                    x[d] *= kLog2e * 0.0625f;
+                    hi[d] = __half2float(__float2half_rn(x[d]));
+                    lo[d] = x[d] - hi[d];
+                    sum += x[d];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const int d0 = q_dim<BITS>(j, r, 0), d1 = q_dim<BITS>(j, r, 1);
+                        qh[G][2 * j + r] = pack_half2(hi[d0], hi[d1]);
+                        ql[G][2 * j + r] = pack_half2(lo[d0], lo[d1]);
+                    }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                qs[G] = sum;
+            }
+            const int p = (i & 1) * 2; // groups 2(i&1), 2(i&1)+1
+            const float s0 = p ? qs[2] : qs[0], s1 = p ? qs[3] : qs[1];
+            const float h0 = __half2float(__float2half_rn(s0)), h1 = __half2float(__float2half_rn(s1));
+            qsb = i < 2 ? pack_half2(h0, h1) : pack_half2(s0 - h0, s1 - h1);
+        }
+
+        float O[16][4];
+        float Ob[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < 16; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
+        float Mref[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+        for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
+            const uint32_t st = it % NS, round = it / NS;
+            if (!mbar_wait(&full[st], round & 1, abort_flag)) {
+                if (lane == 0) {
+                    atomicOr(a.status, kStatusFullTimeout);
+                    *abort_flag = 1;
+                }
+                alive = false;
+                break;
+            }
+            const uint8_t *sg = stages + st * St::kBytes;
+#pragma unroll 1
+            for (int sub = 0; sub < kTile / kSub; sub++) {
+                const uint32_t q_idx = 2 * (t - s.tile_begin) + sub;
+                const uint32_t tok0 = t * kTile + sub * kSub; // first token of the sub-tile
+                if (!row_live || (q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_row) continue;
+                const bool partial = tok0 + kSub > n_row;
+                const int lt = sub * kSub; // token offset inside the stage
+
+                // ------------------------------------------------ scores S^T[token][head]
+                float S[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
+                const uint2 sKa = *reinterpret_cast<const uint2 *>(sg + St::kKs + (lt + g) * St::kParamRow + kv * 8);
+                const uint2 sKb = *reinterpret_cast<const uint2 *>(sg + St::kKs + (lt + g + 8) * St::kParamRow + kv * 8);
+#pragma unroll
+                for (int G = 0; G < 4; G++) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (BITS == 8) {
+                        const uint4 ra = *reinterpret_cast<const uint4 *>(kc + (lt + g) * St::kCodeRow + G * 64 + i * 16);
+                        const uint4 rb = *reinterpret_cast<const uint4 *>(kc + (lt + g + 8) * St::kCodeRow + G * 64 + i * 16);
+                        const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t a0 = hsub2_u32(prmt(wa[j], kMagic, 0x4140), k1024);
+                            const uint32_t a1 = hsub2_u32(prmt(wb[j], kMagic, 0x4140), k1024);
+                            const uint32_t a2 = hsub2_u32(prmt(wa[j], kMagic, 0x4342), k1024);
+                            const uint32_t a3 = hsub2_u32(prmt(wb[j], kMagic, 0x4342), k1024);
+                            mma_f16(acc, a0, a1, a2, a3, qh[G][2 * j], qh[G][2 * j + 1]);
+                            mma_f16(acc, a0, a1, a2, a3, ql[G][2 * j], ql[G][2 * j + 1]);
+                        }
+                    } else {
+                        const uint2 ra = *reinterpret_cast<const uint2 *>(kc + (lt + g) * St::kCodeRow + G * 32 + i * 8);
+                        const uint2 rb = *reinterpret_cast<const uint2 *>(kc + (lt + g + 8) * St::kCodeRow + G * 32 + i * 8);
+                        const uint32_t wa[2] = {ra.x, ra.y}, wb[2] = {rb.x, rb.y};
+#pragma unroll
+                        for (int w = 0; w < 2; w++) {
+#pragma unroll
+                            for (int hlf = 0; hlf < 2; hlf++) {
+                                const uint32_t xa = wa[w] >> (8 * hlf), xb = wb[w] >> (8 * hlf);
+                                const uint32_t a0 = hsub2_u32(lop_and_or(xa, 0x000f000fu, k1024), k1024);
+                                const uint32_t a1 = hsub2_u32(lop_and_or(xb, 0x000f000fu, k1024), k1024);
+                                const uint32_t a2 = hsub2_u32(lop_and_or(xa, 0x00f000f0u, k64), k64);
+                                const uint32_t a3 = hsub2_u32(lop_and_or(xb, 0x00f000f0u, k64), k64);
+                                const int j = 2 * w + hlf;
+                                mma_f16(acc, a0, a1, a2, a3, qh[G][2 * j], qh[G][2 * j + 1]);
+                                mma_f16(acc, a0, a1, a2, a3, ql[G][2 * j], ql[G][2 * j + 1]);
+                            }
+                        }
+                    }
+                    const uint32_t pa = G < 2 ? sKa.x : sKa.y, pb = G < 2 ? sKb.x : sKb.y;
+                    const float sa = half_bits_to_float((pa >> (16 * (G & 1))) & 0xffffu);
+                    const float sb = half_bits_to_float((pb >> (16 * (G & 1))) & 0xffffu);
+                    S[0] = fmaf(sa, acc[0], S[0]);
+                    S[1] = fmaf(sa, acc[1], S[1]);
+                    S[2] = fmaf(sb, acc[2], S[2]);
+                    S[3] = fmaf(sb, acc[3], S[3]);
+                }
+                {   // bias term: sum_G z[token][G] * qsum[head][G]; k-slots 0..3 pair with the
+                    // high halves of the sums, 4..7 with the low halves.
+                    const uint32_t za = *reinterpret_cast<const uint32_t *>(sg + St::kKz + (lt + g) * St::kParamRow + kv * 8 + (i & 1) * 4);
+                    const uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + (lt + g + 8) * St::kParamRow + kv * 8 + (i & 1) * 4);
+                    mma_f16(S, za, zb, 0u, 0u, qsb, 0u);
+                }
+                if (partial) {
+                    if (tok0 + g >= n_row) S[0] = S[1] = -INFINITY;
+                    if (tok0 + g + 8 >= n_row) S[2] = S[3] = -INFINITY;
+                }
+
+                // ------------------------------------------------ online softmax (log2 units)
+                float mx0 = fmaxf(S[0], S[2]), mx1 = fmaxf(S[1], S[3]);
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+                }
+                const bool need0 = mx0 > Mref[0] + kRescale, need1 = mx1 > Mref[1] + kRescale;
+                if (__any_sync(0xffffffffu, need0 || need1)) {
+                    const float n0 = need0 ? mx0 : Mref[0], n1 = need1 ? mx1 : Mref[1];
+                    const float f0 = need0 ? exp2f(Mref[0] - n0) : 1.f, f1 = need1 ? exp2f(Mref[1] - n1) : 1.f;
+#pragma unroll
+                    for (int e = 0; e < 16; e++) {
+                        O[e][0] *= f0, O[e][1] *= f1, O[e][2] *= f0, O[e][3] *= f1;
+                    }
+                    Ob[0] *= f0, Ob[1] *= f1, Ob[2] *= f0, Ob[3] *= f1;
+                    l[0] *= f0, l[1] *= f1;
+                    Mref[0] = n0, Mref[1] = n1;
+                }
+                const float p0 = exp2f(S[0] - Mref[0]), p1 = exp2f(S[1] - Mref[1]);
+                const float p2 = exp2f(S[2] - Mref[0]), p3 = exp2f(S[3] - Mref[1]);
+                l[0] += p0 + p2;
+                l[1] += p1 + p3;
+
+                // ------------------------------------------------ P (x value scales) as B fragments
+                uint2 sVa = *reinterpret_cast<const uint2 *>(sg + St::kVs + (lt + g) * St::kParamRow + kv * 8);
+                uint2 sVb = *reinterpret_cast<const uint2 *>(sg + St::kVs + (lt + g + 8) * St::kParamRow + kv * 8);
+                if (partial) { // stale rows may hold anything: keep them out of 0 * x
+                    if (tok0 + g >= n_row) sVa = make_uint2(0u, 0u);
+                    if (tok0 + g + 8 >= n_row) sVb = make_uint2(0u, 0u);
+                }
+                uint32_t pbf[4][2];
+#pragma unroll
+                for (int G = 0; G < 4; G++) {
+                    const uint32_t pa = G < 2 ? sVa.x : sVa.y, pb = G < 2 ? sVb.x : sVb.y;
+                    const float sa = half_bits_to_float((pa >> (16 * (G & 1))) & 0xffffu);
+                    const float sb = half_bits_to_float((pb >> (16 * (G & 1))) & 0xffffu);
+                    pbf[G][0] = movmatrix_trans(pack_half2(p0 * sa, p1 * sa));
+                    pbf[G][1] = movmatrix_trans(pack_half2(p2 * sb, p3 * sb));
+                }
+                const uint32_t pu0 = movmatrix_trans(pack_half2(p0, p1));
+                const uint32_t pu1 = movmatrix_trans(pack_half2(p2, p3));
+
+                // ------------------------------------------------ O^T[dim][head] += V^T P^T
+                const int T0 = lt + 2 * i, T1 = T0 + 1, T2 = T0 + 8, T3 = T0 + 9;
+                {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] z[t][G]
+                    const uint8_t *vz = sg + St::kVz + kv * 8 + (g & 3) * 2;
+                    uint32_t z0 = *reinterpret_cast<const uint16_t *>(vz + T0 * St::kParamRow);
+                    uint32_t z1 = *reinterpret_cast<const uint16_t *>(vz + T1 * St::kParamRow);
+                    uint32_t z2 = *reinterpret_cast<const uint16_t *>(vz + T2 * St::kParamRow);
+                    uint32_t z3 = *reinterpret_cast<const uint16_t *>(vz + T3 * St::kParamRow);
+                    if (partial) {
+                        if (tok0 + 2 * i >= n_row) z0 = 0;
+                        if (tok0 + 2 * i + 1 >= n_row) z1 = 0;
+                        if (tok0 + 2 * i + 8 >= n_row) z2 = 0;
+                        if (tok0 + 2 * i + 9 >= n_row) z3 = 0;
+                    }
+                    const uint32_t a0 = g < 4 ? (z0 | z1 << 16) : 0u, a2 = g < 4 ? (z2 | z3 << 16) : 0u;
+                    mma_f16(Ob, a0, 0u, a2, 0u, pu0, pu1);
+                }
+                const uint8_t *vc = sg + St::kV + kv * (kDim * BITS / 8);
+#pragma unroll
+                for (int G = 0; G < 4; G++) {
+                    if (BITS == 8) {
+                        const uint2 t0 = *reinterpret_cast<const uint2 *>(vc + T0 * St::kCodeRow + G * 64 + g * 8);
+                        const uint2 t1 = *reinterpret_cast<const uint2 *>(vc + T1 * St::kCodeRow + G * 64 + g * 8);
+                        const uint2 t2 = *reinterpret_cast<const uint2 *>(vc + T2 * St::kCodeRow + G * 64 + g * 8);
+                        const uint2 t3 = *reinterpret_cast<const uint2 *>(vc + T3 * St::kCodeRow + G * 64 + g * 8);
+                        // [T0.b0 T1.b0 T0.b1 T1.b1] and [T0.b2 T1.b2 T0.b3 T1.b3], per dim row and token pair
+                        const uint32_t x01[2] = {prmt(t0.x, t1.x, 0x5140), prmt(t0.x, t1.x, 0x7362)};
+                        const uint32_t u01[2] = {prmt(t0.y, t1.y, 0x5140), prmt(t0.y, t1.y, 0x7362)};
+                        const uint32_t x23[2] = {prmt(t2.x, t3.x, 0x5140), prmt(t2.x, t3.x, 0x7362)};
+                        const uint32_t u23[2] = {prmt(t2.y, t3.y, 0x5140), prmt(t2.y, t3.y, 0x7362)};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const uint32_t sel = (e & 1) ? 0x4342u : 0x4140u;
+                            const uint32_t a0 = hsub2_u32(prmt(x01[e >> 1], kMagic, sel), k1024);
+                            const uint32_t a1 = hsub2_u32(prmt(u01[e >> 1], kMagic, sel), k1024);
+                            const uint32_t a2 = hsub2_u32(prmt(x23[e >> 1], kMagic, sel), k1024);
+                            const uint32_t a3 = hsub2_u32(prmt(u23[e >> 1], kMagic, sel), k1024);
+                            mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+                        }
+                    } else {
+                        const uint32_t t0 = *reinterpret_cast<const uint32_t *>(vc + T0 * St::kCodeRow + G * 32 + g * 4);
+                        const uint32_t t1 = *reinterpret_cast<const uint32_t *>(vc + T1 * St::kCodeRow + G * 32 + g * 4);
+                        const uint32_t t2 = *reinterpret_cast<const uint32_t *>(vc + T2 * St::kCodeRow + G * 32 + g * 4);
+                        const uint32_t t3 = *reinterpret_cast<const uint32_t *>(vc + T3 * St::kCodeRow + G * 32 + g * 4);
+                        // low half-word: T0's nibbles 0..3 (dim row g), high: T1's; .y side: nibbles 4..7 (row g+8)
+                        const uint32_t x01 = prmt(t0, t1, 0x5410), u01 = prmt(t0, t1, 0x7632);
+                        const uint32_t x23 = prmt(t2, t3, 0x5410), u23 = prmt(t2, t3, 0x7632);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int sh = 8 * (e >> 1);
+                            const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
+                            const uint32_t a0 = hsub2_u32(lop_and_or(x01 >> sh, mask, mg), mg);
+                            const uint32_t a1 = hsub2_u32(lop_and_or(u01 >> sh, mask, mg), mg);
+                            const uint32_t a2 = hsub2_u32(lop_and_or(x23 >> sh, mask, mg), mg);
+                            const uint32_t a3 = hsub2_u32(lop_and_or(u23 >> sh, mask, mg), mg);
+                            mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);
+        }
+
+        // ---------------------------------------------------------------- end of segment
+        // l over the eight lanes that share the heads; value-bias rows into O.
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l[0] += __shfl_xor_sync(0xffffffffu, l[0], off);
+            l[1] += __shfl_xor_sync(0xffffffffu, l[1], off);
+        }
+#pragma unroll
+        for (int G = 0; G < 4; G++) {
+            const float b0 = __shfl_sync(0xffffffffu, Ob[0], 4 * G + i);
+            const float b1 = __shfl_sync(0xffffffffu, Ob[1], 4 * G + i);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                O[4 * G + e][0] += b0, O[4 * G + e][1] += b1;
+                O[4 * G + e][2] += b0, O[4 * G + e][3] += b1;
+            }
+        }
+        float *dst = a.parts + ((size_t(s.part) * a.m + row) * kKv + kv) * kPartKv;
+        if (NSLOT == 1) {
+            if (row_live) {
+#pragma unroll
+                for (int e = 0; e < 16; e++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) dst[(4 * e + c) * 32 + lane] = O[e][c];
+                if (g == 0) {
+                    dst[kFragFloats + 2 * i] = Mref[0], dst[kFragFloats + 2 * i + 1] = Mref[1];
+                    dst[kFragFloats + 8 + 2 * i] = l[0], dst[kFragFloats + 8 + 2 * i + 1] = l[1];
+                }
+            }
+        } else {
+            // Warps that share a (kv, row) agree on one maximum, scale, and add up
+            // in a fixed order through shared memory (deterministic).
+            if (g == 0) {
+                ml[warp * 16 + 2 * i] = Mref[0], ml[warp * 16 + 2 * i + 1] = Mref[1];
+                ml[warp * 16 + 8 + 2 * i] = l[0], ml[warp * 16 + 8 + 2 * i + 1] = l[1];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            float Mc[2] = {-INFINITY, -INFINITY}, lc[2] = {0.f, 0.f};
+#pragma unroll
+            for (int sl = 0; sl < NSLOT; sl++) {
+                const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
+                Mc[0] = fmaxf(Mc[0], ml[w * 16 + 2 * i]);
+                Mc[1] = fmaxf(Mc[1], ml[w * 16 + 2 * i + 1]);
+            }
+#pragma unroll
+            for (int sl = 0; sl < NSLOT; sl++) {
+                const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
+                const float m0 = ml[w * 16 + 2 * i], m1 = ml[w * 16 + 2 * i + 1];
+                lc[0] += m0 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i] * exp2f(m0 - Mc[0]);
+                lc[1] += m1 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i + 1] * exp2f(m1 - Mc[1]);
+            }
+            const float f0 = Mref[0] == -INFINITY ? 0.f : exp2f(Mref[0] - Mc[0]);
+            const float f1 = Mref[1] == -INFINITY ? 0.f : exp2f(Mref[1] - Mc[1]);
+            float *buf = merge + (row_in_pass * kKv + kv) * kFragFloats;
+#pragma unroll 1
+            for (int sl = 0; sl < NSLOT; sl++) {
+                if (sl == slot) {
+#pragma unroll
+                    for (int e = 0; e < 16; e++)
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const float v = O[e][c] * ((c & 1) ? f1 : f0);
+                            float *p = buf + (4 * e + c) * 32 + lane;
+                            *p = sl ? *p + v : v;
+                        }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            }
+            if (row_live) {
+                constexpr int per = 64 / NSLOT;
+#pragma unroll
+                for (int r = 0; r < per; r++) dst[(slot * per + r) * 32 + lane] = buf[(slot * per + r) * 32 + lane];
+                if (slot == 0 && g == 0) {
+                    dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
+                    dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // merge buffers free again
+        }
+    }
+}
+
+template <int BITS, int ROWS>
+static int launch_one(const DecodeArgs &a, dim3 grid, cudaStream_t stream) {
+    decode_quant_kernel<BITS, ROWS><<<grid, kThreads, smem_bytes<BITS>(), stream>>>(a);
+    SAETTA_CUDA(cudaGetLastError());
+    return SAETTA_OK;
+}
+
+template <int BITS>
+static int launch_rows(const DecodeArgs &a, int ctas, cudaStream_t stream) {
+    if (a.m == 1) return launch_one<BITS, 1>(a, dim3(ctas, 1), stream);
+    if (a.m == 2) return launch_one<BITS, 2>(a, dim3(ctas, 1), stream);
+    return launch_one<BITS, 4>(a, dim3(ctas, (a.m + 3) / 4), stream);
+}
+
+int decode_quant_configure(int device) {
+    (void)device;
+#define SAETTA_SET(BITS, ROWS)                                                               \
+    SAETTA_CUDA(cudaFuncSetAttribute(decode_quant_kernel<BITS, ROWS>,                        \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<BITS>()))
+    SAETTA_SET(8, 1);
+    SAETTA_SET(8, 2);
+    SAETTA_SET(8, 4);
+    SAETTA_SET(4, 1);
+    SAETTA_SET(4, 2);
+    SAETTA_SET(4, 4);
+#undef SAETTA_SET
+    return SAETTA_OK;
+}
+
+int launch_decode_quant(const KvView &kv, const float *q, float *parts, uint32_t *status,
+                        uint32_t m, uint32_t row_step, int splits, uint32_t capacity,
+                        const saetta_token_params *params, cudaStream_t stream) {
+    DecodeArgs a{};
+    a.seg.k = kv.k, a.seg.v = kv.v, a.seg.ks = kv.ks, a.seg.kz = kv.kz, a.seg.vs = kv.vs, a.seg.vz = kv.vz;
+    a.segs = nullptr, a.cta_first = nullptr;
+    a.q = q, a.parts = parts, a.status = status, a.params = params;
+    a.m = m, a.row_step = row_step, a.capacity = capacity;
+    return kv.bits == 8 ? launch_rows<8>(a, splits, stream) : launch_rows<4>(a, splits, stream);
+}
+
+int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uint32_t *cta_first_dev,
+                                int ctas, const float *q, float *parts, uint32_t *status,
+                                cudaStream_t stream) {
+    DecodeArgs a{};
+    a.segs = segments_dev, a.cta_first = cta_first_dev;
+    a.q = q, a.parts = parts, a.status = status, a.params = nullptr;
+    a.m = 1, a.row_step = 0, a.capacity = 0xffffffffu;
+    return bits == 8 ? launch_one<8, 1>(a, dim3(ctas, 1), stream) : launch_one<4, 1>(a, dim3(ctas, 1), stream);
+}
+
+} // namespace saetta

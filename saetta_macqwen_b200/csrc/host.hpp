@@ -1,0 +1,158 @@
+// Host-side objects behind the C ABI.  They mirror, one for one, the Rust
+// structs of the reference that own device memory on this path:
+//   QuantRows        src/kv_quant.rs:158-283
+//   KvCache          src/gpu_layers.rs:179-293 (GpuKvCache)
+//   RowBackup        src/gpu_cache.rs:192-286
+//   Decode           src/attention.rs:19-171 (DecodeAttention), src/rows.rs:307-494 (AttentionRows)
+//   AttGemm          src/attention_gemm.rs:93-363
+// and declare the kernel launchers implemented in the .cu files.
+#pragma once
+
+#include <vector>
+
+#include "common.cuh"
+
+struct saetta_quant_rows {
+    int device = 0;
+    int bits = 8;
+    size_t per_token = 0; // groups of 64 per token (values / 64)
+    size_t capacity = 0;
+    void *data = nullptr;
+    void *scales = nullptr;
+    void *biases = nullptr;
+    bool owns = false;
+    size_t data_row_bytes() const { return per_token * 2 * size_t(bits) * 4; }
+    size_t param_row_bytes() const { return per_token * 2; }
+};
+
+struct saetta_kv_cache {
+    int device = 0;
+    int bits = 16;
+    int dtype = SAETTA_F16; // of a 16-bit cache
+    size_t heads = 0, kv_heads = 0, head_dim = 0, capacity = 0;
+    void *keys = nullptr;   // 16/32-bit rows, or the key codes
+    void *values = nullptr;
+    saetta_quant_rows k, v; // views into the buffers of a quantised cache
+    size_t row_values() const { return kv_heads * head_dim; }
+    size_t plain_row_bytes() const { return row_values() * (bits == 32 ? 4 : 2); }
+};
+
+struct saetta_row_backup {
+    struct Part {
+        void *copy;
+        size_t row_bytes;
+    };
+    std::vector<Part> parts;
+    int device = 0;
+    size_t from = 0, n = 0;
+    bool held = false;
+};
+
+struct saetta_decode {
+    int device = 0;
+    size_t heads = 0, kv_heads = 0, capacity = 0, rows = 1;
+    int splits = 0;        // grid of the split-KV kernel
+    float *parts = nullptr; // [splits][rows][heads][kPartStride]
+    uint32_t *status = nullptr;
+};
+
+struct saetta_decode_batch {
+    int device = 0;
+    size_t heads = 0, kv_heads = 0, max_seqs = 0;
+    int ctas = 0;
+    size_t max_parts = 0;
+    float *parts = nullptr;     // [max_parts][heads][kPartStride]
+    void *table_dev = nullptr;  // segment descriptors + per-sequence part ranges
+    void *table_host = nullptr; // pinned
+    size_t table_bytes = 0;
+    void *table_event = nullptr; // recorded after the table's upload
+    uint32_t *status = nullptr;
+};
+
+struct saetta_att_gemm {
+    int device = 0;
+    size_t chunk = 0, kv_heads = 0;
+    void *stage_k = nullptr, *stage_v = nullptr; // 16-bit copy of a quantised cache
+    size_t stage_tokens = 0;
+    uint32_t *status = nullptr;
+};
+
+namespace saetta {
+
+using QuantRows = saetta_quant_rows;
+
+// kv_quant.cu
+int launch_kv_quantize(int bits, uint32_t per_token, const float *x0, const QuantRows *r0,
+                       const float *x1, const QuantRows *r1, size_t rows, size_t pos,
+                       const saetta_token_params *params, cudaStream_t stream);
+int launch_kv_dequantize(const QuantRows *rows, void *out, int dtype, size_t tokens,
+                         cudaStream_t stream);
+int launch_kv_store_plain(int mode, const float *k, const float *v, void *keys, void *values,
+                          size_t row_values, size_t rows, size_t pos,
+                          const saetta_token_params *params, cudaStream_t stream);
+
+// What a split-KV launch reads: the cache in any of its storage forms.
+struct KvView {
+    int bits = 8;            // 32, 16, 8, 4
+    int dtype = SAETTA_F16;  // of 16-bit rows
+    const void *k = nullptr, *v = nullptr; // rows or codes
+    const void *ks = nullptr, *kz = nullptr, *vs = nullptr, *vz = nullptr;
+    uint32_t kv_heads = 2;
+};
+
+// One sequence-segment of a batched launch (decode_quant.cu reads these).
+struct Segment {
+    const void *k, *v, *ks, *kz, *vs, *vz;
+    uint32_t tile_begin, tile_end; // 32-token tiles
+    uint32_t kv_len;
+    uint32_t part;   // slot in the partials buffer
+    uint32_t seq;    // which q / out row
+    uint32_t pad[3];
+};
+
+// decode_quant.cu: tensor-core split-KV over 8/4-bit codes.
+int launch_decode_quant(const KvView &kv, const float *q, float *parts, uint32_t *status,
+                        uint32_t m, uint32_t row_step, int splits, uint32_t capacity,
+                        const saetta_token_params *params, cudaStream_t stream);
+size_t decode_quant_part_floats(size_t kv_heads); // floats per (part, row) of the internal partial format
+int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uint32_t *cta_first_dev,
+                                int ctas, const float *q, float *parts, uint32_t *status,
+                                cudaStream_t stream);
+int decode_quant_configure(int device);
+
+// decode_exact.cu: f32 arithmetic over f32 / 16-bit rows.
+int launch_decode_exact(const KvView &kv, const float *q, float *parts, uint32_t m,
+                        uint32_t row_step, int splits, uint32_t capacity,
+                        const saetta_token_params *params, cudaStream_t stream);
+int decode_exact_configure(int device);
+
+// merge.cu: log-sum-exp merge over parts, then the gate.
+//   frag:    parts in the fragment order decode_quant.cu writes, [part][row][kv][2064];
+//            first_part (device, [seqs+1]) gives each sequence's part range when
+//            non-null (batched), else every row merges parts 0..nparts.
+//   logical: parts [part][row][head][kPartStride] (decode_exact.cu, other ranks).
+// With out == null the merged (O, m, l) is written to part_out in the logical
+// layout instead of the gated result.
+int launch_merge_frag(const float *parts, uint32_t nparts, const uint32_t *first_part,
+                      uint32_t rows, uint32_t kv_heads, const float *q_and_gate, float *out,
+                      float *part_out, cudaStream_t stream);
+int launch_merge_logical(const float *parts, uint32_t nparts, uint32_t rows, uint32_t heads,
+                         const float *q_and_gate, float *out, float *part_out,
+                         cudaStream_t stream);
+
+// prefill_umma.cu: tcgen05 causal chunk attention.
+struct PrefillArgs {
+    const void *q;       // 16-bit [tokens][heads][256]
+    const void *k, *v;   // 16-bit [>= pos+tokens][kv_heads][256]
+    int dtype;
+    const float *q_and_gate; // may be null when part != null
+    float *out;          // [tokens][heads][256] or null
+    float *part;         // [tokens][heads][kPartStride] or null
+    uint32_t heads, kv_heads, pos, tokens;
+    uint32_t key_lo, key_hi; // keys considered (clipped by causality)
+    float scale;
+};
+int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream);
+int prefill_configure(int device);
+
+} // namespace saetta
