@@ -16,12 +16,23 @@ size_t decode_quant_part_floats(size_t kv_heads) { return kv_heads * size_t(kPar
 
 __device__ __forceinline__ float gate_of(float g) { return 1.0f / (1.0f + expf(-g)); }
 
-// grid (8, rows * kv_heads): 256 fragment elements of one (row, kv head) per block.
-__global__ void __launch_bounds__(256)
+// grid (32, rows * kv_heads), 1024 threads: 64 fragment elements of one (row, kv
+// head) per block, the parts dealt round-robin to 16 thread groups so that every
+// thread has only a handful of independent loads in flight (the merge is
+// latency-bound, not bandwidth-bound).  Sums are formed in a fixed order.
+constexpr int kMergeGroups = 16;
+constexpr int kMergeElems = 64;
+constexpr int kMergeMaxParts = 512; // m and l of at most this many parts are staged in shared memory
+
+__global__ void __launch_bounds__(kMergeGroups * kMergeElems)
 merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
                   const uint32_t *__restrict__ first_part, uint32_t rows, uint32_t kv_heads,
                   const float *__restrict__ q_and_gate, float *__restrict__ out,
                   float *__restrict__ part_out) {
+    __shared__ float w_s[kMergeMaxParts][8]; // first m, then the weight 2^(m_p - M), per part and head
+    __shared__ float l_s[kMergeMaxParts][8];
+    __shared__ float M_s[8], L_s[8];
+    __shared__ float red[kMergeGroups][kMergeElems];
     const uint32_t row = blockIdx.y / kv_heads, kv = blockIdx.y % kv_heads;
     uint32_t p0 = 0, p1 = nparts;
     if (first_part) {
@@ -29,32 +40,81 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
         p1 = first_part[row + 1];
     }
     const uint32_t prow = first_part ? 0 : row, prows = first_part ? 1 : rows;
-    const uint32_t e = blockIdx.x * 256 + threadIdx.x; // fragment element
-    const uint32_t r = e >> 5, lane = e & 31;
-    const uint32_t head = 2 * (lane & 3) + (r & 1);
     const size_t stride = size_t(prows) * kv_heads * kPartKv;
     const float *base = parts + (size_t(prow) * kv_heads + kv) * kPartKv;
+    const uint32_t tid = threadIdx.x, grp = tid / kMergeElems, el = tid % kMergeElems;
+    const uint32_t e = blockIdx.x * kMergeElems + el; // fragment element
+    const uint32_t r = e >> 5, lane = e & 31;
+    const uint32_t head = 2 * (lane & 3) + (r & 1);
 
-    float M = -INFINITY;
-    for (uint32_t p = p0; p < p1; p++) M = fmaxf(M, base[p * stride + kFragFloats + head]);
-    float acc = 0.f, l = 0.f;
-#pragma unroll 4
-    for (uint32_t p = p0; p < p1; p++) {
-        const float *pp = base + p * stride;
-        const float mp = pp[kFragFloats + head];
-        if (mp == -INFINITY) continue;
-        const float w = exp2f(mp - M);
-        l = fmaf(pp[kFragFloats + 8 + head], w, l);
-        acc = fmaf(pp[e], w, acc);
+    float acc = 0.f;
+    for (uint32_t c0 = p0; c0 < p1; c0 += kMergeMaxParts) { // one pass unless a sequence has > 512 parts
+        const uint32_t n = min(p1 - c0, uint32_t(kMergeMaxParts));
+        __syncthreads();
+        for (uint32_t x = tid; x < n * 16; x += blockDim.x) {
+            const uint32_t p = x >> 4, k = x & 15;
+            const float v = base[(c0 + p) * stride + kFragFloats + k];
+            if (k < 8) w_s[p][k] = v; else l_s[p][k - 8] = v;
+        }
+        __syncthreads();
+        if (tid < 256) { // warp h reduces head h
+            const uint32_t h = tid >> 5, ln = tid & 31;
+            float mx = -INFINITY;
+            for (uint32_t p = ln; p < n; p += 32) mx = fmaxf(mx, w_s[p][h]);
+#pragma unroll
+            for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            const float Mold = c0 == p0 ? -INFINITY : M_s[h];
+            const float Mnew = fmaxf(Mold, mx);
+            float lsum = 0.f;
+            for (uint32_t p = ln; p < n; p += 32) {
+                const float mp = w_s[p][h];
+                const float w = mp == -INFINITY ? 0.f : exp2f(mp - Mnew);
+                w_s[p][h] = w;
+                lsum += l_s[p][h] * w;
+            }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+            if (ln == 0) {
+                const float carry = Mold == -INFINITY ? 0.f : exp2f(Mold - Mnew);
+                L_s[h] = (c0 == p0 ? 0.f : L_s[h] * carry) + lsum;
+                M_s[h] = Mnew;
+                red[0][h] = carry;     // reuse: the rescale of what was accumulated so far
+            }
+        }
+        __syncthreads();
+        if (c0 != p0) acc *= red[0][head];
+        __syncthreads();
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        uint32_t p = grp;
+        for (; p + 3 * kMergeGroups < n; p += 4 * kMergeGroups) {
+            const float v0 = base[(c0 + p) * stride + e];
+            const float v1 = base[(c0 + p + kMergeGroups) * stride + e];
+            const float v2 = base[(c0 + p + 2 * kMergeGroups) * stride + e];
+            const float v3 = base[(c0 + p + 3 * kMergeGroups) * stride + e];
+            a0 = fmaf(v0, w_s[p][head], a0);
+            a1 = fmaf(v1, w_s[p + kMergeGroups][head], a1);
+            a2 = fmaf(v2, w_s[p + 2 * kMergeGroups][head], a2);
+            a3 = fmaf(v3, w_s[p + 3 * kMergeGroups][head], a3);
+        }
+        for (; p < n; p += kMergeGroups) a0 = fmaf(base[(c0 + p) * stride + e], w_s[p][head], a0);
+        acc += (a0 + a1) + (a2 + a3);
     }
+    __syncthreads();
+    red[grp][el] = acc;
+    __syncthreads();
+    if (grp) return;
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMergeGroups; k++) sum += red[k][el];
+    const float M = M_s[head], l = L_s[head];
     const uint32_t mt = r >> 2, c = r & 3;
     const uint32_t dim = 64 * (mt >> 2) + 8 * (lane >> 2) + (mt & 3) + (c >= 2 ? 4 : 0);
     const size_t rh = size_t(row) * kv_heads * kHeadsPerKv + kv * kHeadsPerKv + head;
     if (out) {
         const float g = q_and_gate[rh * 2 * kDim + kDim + dim];
-        out[rh * kDim + dim] = acc / l * gate_of(g);
+        out[rh * kDim + dim] = sum / l * gate_of(g);
     } else {
-        part_out[rh * kPartStride + dim] = acc;
+        part_out[rh * kPartStride + dim] = sum;
         if (dim == 0) {
             part_out[rh * kPartStride + kPartM] = M;
             part_out[rh * kPartStride + kPartL] = l;
@@ -66,8 +126,8 @@ int launch_merge_frag(const float *parts, uint32_t nparts, const uint32_t *first
                       uint32_t rows, uint32_t kv_heads, const float *q_and_gate, float *out,
                       float *part_out, cudaStream_t stream) {
     if (!rows) return SAETTA_OK;
-    merge_frag_kernel<<<dim3(8, rows * kv_heads), 256, 0, stream>>>(parts, nparts, first_part, rows,
-                                                                     kv_heads, q_and_gate, out, part_out);
+    merge_frag_kernel<<<dim3(kFragFloats / kMergeElems, rows * kv_heads), kMergeGroups * kMergeElems, 0, stream>>>(
+        parts, nparts, first_part, rows, kv_heads, q_and_gate, out, part_out);
     SAETTA_CUDA(cudaGetLastError());
     return SAETTA_OK;
 }
