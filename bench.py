@@ -209,6 +209,34 @@ def prefill_point(sa, torch, pos, tokens, steps, warmup, stream, quant_bits=None
 _CPU_DATA = {}
 
 
+def point_table(sa, torch, stream, s, w):
+    return {
+        "decode_32k_8bit": lambda: decode_point(sa, torch, 32768, 8, 1, 10, s, w, stream),
+        "decode_128k_8bit": lambda: decode_point(sa, torch, 131072, 8, 1, 4, s, w, stream),
+        "decode_256k_8bit": lambda: decode_point(sa, torch, 262144, 8, 1, 4, s, w, stream),
+        "decode_256k_4bit": lambda: decode_point(sa, torch, 262144, 4, 1, 4, s, w, stream),
+        "verify_m4_32k_8bit": lambda: decode_point(sa, torch, 32768, 8, 4, 10, s, w, stream),
+        "batch64_ragged_8bit": lambda: batch_point(sa, torch, 8, min(s, 3), 2, stream),
+        "batch64_ragged_4bit": lambda: batch_point(sa, torch, 4, min(s, 3), 2, stream),
+        "prefill_4k_pos0_bf16": lambda: prefill_point(sa, torch, 0, 4096, s, w, stream),
+        "prefill_4k_pos32k_8bit": lambda: prefill_point(sa, torch, 32768, 4096, min(s, 5), 2, stream, quant_bits=8),
+        "prefill_4k_pos128k_8bit": lambda: prefill_point(sa, torch, 131072, 4096, min(s, 3), 2, stream, quant_bits=8),
+    }
+
+
+def run_only(args):
+    """One point alone, few launches: the command the ncu captures under profiles/ run."""
+    import torch
+    import saetta_macqwen_b200 as sa
+
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    table = point_table(sa, torch, stream, args.steps, args.warmup)
+    r = table[args.only]()
+    r["point"] = args.only
+    print(json.dumps(r), flush=True)
+
+
 def cpu_sample(ctx, layers_sample, threads):
     """The oracle (the reference's CPU attention restated) on `layers_sample`
     layers of one decode row at `ctx` tokens; returns seconds per layer.  The
@@ -263,9 +291,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--points", default="all", help="'none' skips the extra measured points")
+    ap.add_argument("--only", default=None, help="run one named point alone (for profiling) and print its result")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.only:
+        return run_only(args)
     args.warmup = max(args.warmup, 3)
 
     import torch
@@ -402,16 +433,11 @@ def main():
         del caches, op
         torch.cuda.empty_cache()
         s, w = max(5, args.steps // 2), 3
-        for name, fn in [
-            ("decode_32k_8bit", lambda: decode_point(sa, torch, 32768, 8, 1, 10, s, w, stream)),
-            ("decode_128k_8bit", lambda: decode_point(sa, torch, 131072, 8, 1, 4, s, w, stream)),
-            ("decode_256k_4bit", lambda: decode_point(sa, torch, 262144, 4, 1, 4, s, w, stream)),
-            ("verify_m4_32k_8bit", lambda: decode_point(sa, torch, 32768, 8, 4, 10, s, w, stream)),
-            ("batch64_ragged_8bit", lambda: batch_point(sa, torch, 8, 3, 2, stream)),
-            ("batch64_ragged_4bit", lambda: batch_point(sa, torch, 4, 3, 2, stream)),
-            ("prefill_4k_pos0_bf16", lambda: prefill_point(sa, torch, 0, 4096, s, w, stream)),
-            ("prefill_4k_pos128k_8bit", lambda: prefill_point(sa, torch, 131072, 4096, 3, 2, stream, quant_bits=8)),
-        ]:
+        table = point_table(sa, torch, stream, s, w)
+        for name in ["decode_32k_8bit", "decode_128k_8bit", "decode_256k_4bit", "verify_m4_32k_8bit",
+                     "batch64_ragged_8bit", "batch64_ragged_4bit", "prefill_4k_pos0_bf16",
+                     "prefill_4k_pos32k_8bit", "prefill_4k_pos128k_8bit"]:
+            fn = table[name]
             try:
                 r = fn()
                 if "gbs" in r:

@@ -795,6 +795,7 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     DeviceGuard guard(op->device);
     const size_t end = size_t(p.pos) + p.tokens;
     if (key_hi > end) key_hi = end;
+    int v_dtype = dtype;
     if (kq || vq) {
         if (!kq || !vq || kq->bits != vq->bits) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: quant needs both sides");
         if (end > kq->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: pos + tokens exceeds the capacity");
@@ -802,12 +803,23 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
         if (int rc = saetta_att_gemm_reserve(op, key_hi)) return rc;
         // The quantised cache is read through a 16-bit copy, as the reference's
         // kv_stage reads it (src/kv_quant.rs:121-126 semantics).
+        // Keys take q's type; values are staged as binary16 (exactly the reference's
+        // round_trip_as_half), so P is binary16 too and keeps an 11-bit significand.
         if (int rc = launch_kv_dequantize(kq, op->stage_k, dtype, key_hi, st)) return rc;
-        if (int rc = launch_kv_dequantize(vq, op->stage_v, dtype, key_hi, st)) return rc;
+        if (int rc = launch_kv_dequantize(vq, op->stage_v, SAETTA_F16, key_hi, st)) return rc;
         keys = op->stage_k, values = op->stage_v;
+        v_dtype = SAETTA_F16;
     }
     if (!keys || !values) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: keys or values null");
-    PrefillArgs a{q, keys, values, dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
+    if (!(kq || vq) && dtype == SAETTA_BF16) {
+        // P must share V's type in the second MMA; bfloat16's 8-bit significand would put P's
+        // rounding at the tolerance, so bfloat16 values go through a binary16 copy (exact in range).
+        if (int rc = saetta_att_gemm_reserve(op, key_hi)) return rc;
+        if (int rc = launch_bf16_to_f16(values, op->stage_v, key_hi * p.kv_heads * kDim, st)) return rc;
+        values = op->stage_v;
+        v_dtype = SAETTA_F16;
+    }
+    PrefillArgs a{q, keys, values, dtype, v_dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
                   uint32_t(key_lo), uint32_t(key_hi), p.scale};
     return launch_prefill(a, op->status, st);
 }
@@ -842,7 +854,7 @@ int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *
     if (device < 0 || device >= 64) return fail(SAETTA_ERR_BAD_ARG, "prefill encode: device");
     if (!status[device])
         if (int rc = alloc_zero((void **)&status[device], 16)) return rc;
-    PrefillArgs a{q_dev, keys_dev, values_dev, dtype, q_and_gate_dev, out_dev, nullptr, p.heads, p.kv_heads, p.pos,
+    PrefillArgs a{q_dev, keys_dev, values_dev, dtype, dtype, q_and_gate_dev, out_dev, nullptr, p.heads, p.kv_heads, p.pos,
                   p.tokens, 0, p.pos + p.tokens, p.scale};
     return launch_prefill(a, status[device], (cudaStream_t)stream);
 }

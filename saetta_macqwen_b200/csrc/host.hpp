@@ -87,6 +87,7 @@ int launch_kv_quantize(int bits, uint32_t per_token, const float *x0, const Quan
                        const saetta_token_params *params, cudaStream_t stream);
 int launch_kv_dequantize(const QuantRows *rows, void *out, int dtype, size_t tokens,
                          cudaStream_t stream);
+int launch_bf16_to_f16(const void *in, void *out, size_t values, cudaStream_t stream);
 int launch_kv_store_plain(int mode, const float *k, const float *v, void *keys, void *values,
                           size_t row_values, size_t rows, size_t pos,
                           const saetta_token_params *params, cudaStream_t stream);
@@ -144,7 +145,8 @@ int launch_merge_logical(const float *parts, uint32_t nparts, uint32_t rows, uin
 struct PrefillArgs {
     const void *q;       // 16-bit [tokens][heads][256]
     const void *k, *v;   // 16-bit [>= pos+tokens][kv_heads][256]
-    int dtype;
+    int dtype;           // of q and k
+    int v_dtype;         // of v: P takes the same type, so binary16 values keep P's 11-bit significand
     const float *q_and_gate; // may be null when part != null
     float *out;          // [tokens][heads][256] or null
     float *part;         // [tokens][heads][kPartStride] or null

@@ -160,6 +160,32 @@ kv_store_plain_kernel(const float *__restrict__ k, const float *__restrict__ v, 
     }
 }
 
+// bfloat16 -> binary16 copy of cache rows, 8 values per thread.  Exact for every
+// value binary16 can hold (bfloat16 has the shorter significand); magnitudes
+// past 65504 saturate instead of becoming infinite.
+__global__ void __launch_bounds__(256)
+bf16_to_f16_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, size_t octets) {
+    const size_t o = size_t(blockIdx.x) * 256 + threadIdx.x;
+    if (o >= octets) return;
+    uint4 v = in[o];
+    uint32_t *w = reinterpret_cast<uint32_t *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float a = fminf(fmaxf(__uint_as_float(w[i] << 16), -65504.f), 65504.f);
+        const float b = fminf(fmaxf(__uint_as_float(w[i] & 0xffff0000u), -65504.f), 65504.f);
+        w[i] = pack_half2(a, b);
+    }
+    out[o] = v;
+}
+
+int launch_bf16_to_f16(const void *in, void *out, size_t values, cudaStream_t stream) {
+    const size_t octets = values / 8;
+    if (!octets) return SAETTA_OK;
+    bf16_to_f16_kernel<<<unsigned((octets + 255) / 256), 256, 0, stream>>>((const uint4 *)in, (uint4 *)out, octets);
+    SAETTA_CUDA(cudaGetLastError());
+    return SAETTA_OK;
+}
+
 int launch_kv_store_plain(int mode, const float *k, const float *v, void *keys, void *values,
                           size_t row_values, size_t rows, size_t pos,
                           const saetta_token_params *params, cudaStream_t stream) {

@@ -1,6 +1,497 @@
-// placeholder until the tcgen05 kernel lands
+// Chunked causal prefill attention on the 5th-generation tensor cores.
+//
+// Stands in for attention_prefill::encode / attention_fa8 and for AttGemm's
+// prefill_ag_* passes (src/attention_prefill.rs:39-72, src/attention_gemm.rs:150-362,
+// kernels/attention_prefill.metal, kernels/attention_gemm.metal) of the
+// reference.  Same contract: token i of the chunk sees keys 0 ..= pos + i of the
+// cache (which already holds the chunk's rows), the eight query heads of a kv
+// head share its K/V, out = softmax(q K^T scale) V * sigmoid(gate).  The design
+// is a single fused flash kernel instead of the reference's separate scores /
+// softmax / PV passes through device memory:
+//
+//  * A tile is 128 query rows = 16 tokens x 8 heads of one kv head (row =
+//    token*8 + head, the reference's GQA packing), so one K/V block feeds all
+//    eight heads.  Persistent CTAs walk the tiles heaviest first.
+//  * Warp 0 streams Q (once per tile) and 64-key K and V blocks into shared
+//    memory with TMA tensor copies (128-byte swizzle, two stages each).
+//  * Warp 1 issues tcgen05.mma: S = Q K^T (128x64x256, f32 in TMEM, two S
+//    buffers) and O += P V (128x256x64, V read MN-major straight from its
+//    [key][dim] rows).  S of block j+1 is issued before P V of block j, so the
+//    tensor pipe works while the softmax warps are busy.
+//  * Warps 2..5 (one TMEM lane = one row per thread) read S with tcgen05.ld, do
+//    the online softmax in log2 units, write P in V's 16-bit type into swizzled shared
+//    memory for the second MMA, and only rescale O in TMEM when the running
+//    maximum has grown by more than 2^8.  The epilogue divides by l and applies
+//    the sigmoid gate, or leaves (O, m, l) partials for a cross-GPU merge.
+//  * All mbarrier waits are bounded; a wait that gives up sets the status word
+//    and the CTA-wide abort flag, every role leaves its loop, and TMEM is freed.
+#include <cuda.h>
+
+#include <algorithm>
+
 #include "host.hpp"
+
 namespace saetta {
-int prefill_configure(int) { return SAETTA_OK; }
-int launch_prefill(const PrefillArgs &, uint32_t *, cudaStream_t) { return fail(SAETTA_ERR_UNSUPPORTED, "prefill kernel not built"); }
+
+constexpr int kBM = 128;      // rows per tile
+constexpr int kTokTile = 16;  // tokens per tile
+constexpr int kBN = 64;       // keys per block
+constexpr int kQChunk = kBM * 128;  // bytes of one 64-dim slab of the Q tile
+constexpr int kKChunk = kBN * 128;  // bytes of one 64-dim slab of a K or V block
+constexpr int kQBytes = 4 * kQChunk;
+constexpr int kKBytes = 4 * kKChunk;
+constexpr int kPBytes = kBM * kBN * 2;
+constexpr int kPfThreads = 192;
+constexpr int kPfSmem = kQBytes + 4 * kKBytes + 2 * kPBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr float kLog2ePf = 1.4426950408889634f;
+constexpr float kPfRescale = 8.0f;
+
+struct PfParams {
+    const float *q_and_gate;
+    float *out, *part;
+    uint32_t *status;
+    uint32_t heads, kv_heads, pos, tokens, key_lo, key_hi;
+    float scale_log2;
+    uint32_t fmt;   // of Q and K: 0 binary16, 1 bfloat16 (also the UMMA format code)
+    uint32_t v_fmt; // of V, and therefore of P (both operands of one MMA must share a format)
+};
+
+// ----------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+#define SAETTA_R32(a, o)                                                                                              \
+    "=r"(a[o + 0]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]),    \
+        "=r"(a[o + 7]), "=r"(a[o + 8]), "=r"(a[o + 9]), "=r"(a[o + 10]), "=r"(a[o + 11]), "=r"(a[o + 12]),             \
+        "=r"(a[o + 13]), "=r"(a[o + 14]), "=r"(a[o + 15]), "=r"(a[o + 16]), "=r"(a[o + 17]), "=r"(a[o + 18]),          \
+        "=r"(a[o + 19]), "=r"(a[o + 20]), "=r"(a[o + 21]), "=r"(a[o + 22]), "=r"(a[o + 23]), "=r"(a[o + 24]),          \
+        "=r"(a[o + 25]), "=r"(a[o + 26]), "=r"(a[o + 27]), "=r"(a[o + 28]), "=r"(a[o + 29]), "=r"(a[o + 30]),          \
+        "=r"(a[o + 31])
+#define SAETTA_W32(a, o)                                                                                              \
+    "r"(a[o + 0]), "r"(a[o + 1]), "r"(a[o + 2]), "r"(a[o + 3]), "r"(a[o + 4]), "r"(a[o + 5]), "r"(a[o + 6]),           \
+        "r"(a[o + 7]), "r"(a[o + 8]), "r"(a[o + 9]), "r"(a[o + 10]), "r"(a[o + 11]), "r"(a[o + 12]), "r"(a[o + 13]),   \
+        "r"(a[o + 14]), "r"(a[o + 15]), "r"(a[o + 16]), "r"(a[o + 17]), "r"(a[o + 18]), "r"(a[o + 19]),                \
+        "r"(a[o + 20]), "r"(a[o + 21]), "r"(a[o + 22]), "r"(a[o + 23]), "r"(a[o + 24]), "r"(a[o + 25]),                \
+        "r"(a[o + 26]), "r"(a[o + 27]), "r"(a[o + 28]), "r"(a[o + 29]), "r"(a[o + 30]), "r"(a[o + 31])
+
+// 32 consecutive f32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : SAETTA_R32(r, 0)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+        ::SAETTA_W32(r, 0), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle (cute::UMMA::SmemDescriptor:
+// start address, leading and stride byte offsets in 16-byte units, version 1,
+// layout type 2 in bits 61..63).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = uint64_t((saddr & 0x3ffffu) >> 4);
+    d |= uint64_t(lbo_bytes >> 4) << 16;
+    d |= uint64_t(sbo_bytes >> 4) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+
+struct PfTile {
+    uint32_t tok0, kv, b_begin, nb;
+};
+
+__device__ __forceinline__ bool pf_tile(const PfParams &p, uint32_t round, PfTile &t) {
+    const uint32_t tok_tiles = (p.tokens + kTokTile - 1) / kTokTile;
+    const uint32_t ntiles = tok_tiles * p.kv_heads;
+    const uint32_t G = gridDim.x, c = blockIdx.x;
+    const uint32_t n = round * G + ((round & 1) ? G - 1 - c : c); // heaviest first, snaking
+    if (n >= ntiles) return false;
+    const uint32_t tt = tok_tiles - 1 - n / p.kv_heads;
+    t.kv = n % p.kv_heads;
+    t.tok0 = tt * kTokTile;
+    const uint32_t hi = min(p.key_hi, p.pos + t.tok0 + kTokTile);
+    t.b_begin = p.key_lo / kBN;
+    const uint32_t b_end = hi > p.key_lo ? (hi + kBN - 1) / kBN : t.b_begin;
+    t.nb = b_end - t.b_begin;
+    return true;
+}
+
+__global__ void __launch_bounds__(kPfThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const PfParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sQ = smem;
+    uint8_t *sK = sQ + kQBytes;      // [2][kKBytes]
+    uint8_t *sV = sK + 2 * kKBytes;  // [2][kKBytes]
+    uint8_t *sP = sV + 2 * kKBytes;  // [2][kPBytes]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + 2 * kPBytes);
+    uint64_t *q_full = bars + 0, *q_empty = bars + 1, *k_full = bars + 2, *k_empty = bars + 4, *v_full = bars + 6,
+             *v_empty = bars + 8, *s_full = bars + 10, *s_empty = bars + 12, *p_full = bars + 14, *p_empty = bars + 16,
+             *o_final = bars + 18, *o_empty = bars + 19;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 20);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    volatile uint32_t *never_set = tmem_slot + 2; // stays 0: for waits that must ignore the abort flag
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 4);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1), mbar_init(&s_empty[s], 4), mbar_init(&p_full[s], 4), mbar_init(&p_empty[s], 1);
+        }
+        *abort_flag = 0;
+        *never_set = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_o = tmem, tmem_s = tmem + 256;
+
+    auto give_up = [&](uint32_t bit) {
+        atomicOr(p.status, bit);
+        *abort_flag = 1;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t g = 0, tc = 0;
+            bool ok = true;
+            PfTile t;
+            for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                if (!t.nb) continue;
+                if (!mbar_wait(q_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); break; }
+                mbar_expect_tx(q_full, kQBytes);
+                for (int c = 0; c < 4; c++) tma_load_4d(sQ + c * kQChunk, &map_q, q_full, c * 64, 0, int(t.kv), int(t.tok0));
+                for (uint32_t b = 0; b < t.nb; b++, g++) {
+                    const uint32_t st = g & 1, ph = (g >> 1) & 1;
+                    const int key0 = int((t.b_begin + b) * kBN);
+                    if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                    mbar_expect_tx(&k_full[st], kKBytes);
+                    for (int c = 0; c < 4; c++) tma_load_3d(sK + st * kKBytes + c * kKChunk, &map_k, &k_full[st], c * 64, int(t.kv), key0);
+                    if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                    mbar_expect_tx(&v_full[st], kKBytes);
+                    for (int c = 0; c < 4; c++) tma_load_3d(sV + st * kKBytes + c * kKChunk, &map_v, &v_full[st], c * 64, int(t.kv), key0);
+                }
+                tc++;
+            }
+            // On the way out after a failed wait, let the copies already issued land
+            // (bounded) so that no copy is in flight when the CTA's shared memory is released.
+            if (*abort_flag)
+                for (uint32_t k = g > 2 ? g - 2 : 0; k < g; k++) {
+                    mbar_wait(&k_full[k & 1], (k >> 1) & 1, never_set, 200000u);
+                    mbar_wait(&v_full[k & 1], (k >> 1) & 1, never_set, 200000u);
+                }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = (1u << 4) | (p.fmt << 7) | (p.fmt << 10) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+            const uint32_t idesc_o = (1u << 4) | (p.v_fmt << 7) | (p.v_fmt << 10) | (1u << 16) | (uint32_t(kDim >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP);
+            uint32_t g = 0, tc = 0;
+            bool ok = true;
+            PfTile t;
+            auto issue_s = [&](uint32_t gg) -> bool { // S[gg&1] = Q K^T for the block with running index gg
+                const uint32_t st = gg & 1, ph = (gg >> 1) & 1;
+                if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); return false; }
+                if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kDim / 16; ks++) {
+                    const uint64_t ad = umma_desc(q_addr + (ks >> 2) * kQChunk + (ks & 3) * 32, 16, 1024);
+                    const uint64_t bd = umma_desc(k_addr + st * kKBytes + (ks >> 2) * kKChunk + (ks & 3) * 32, 16, 1024);
+                    tc_mma(tmem_s + st * kBN, ad, bd, idesc_s, ks > 0);
+                }
+                tc_commit(&k_empty[st]);
+                tc_commit(&s_full[st]);
+                return true;
+            };
+            for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                if (!t.nb) continue;
+                if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; }
+                if (!(ok = issue_s(g))) break;
+                for (uint32_t b = 0; b < t.nb; b++) {
+                    if (b + 1 < t.nb) {
+                        if (!(ok = issue_s(g + b + 1))) break;
+                    } else {
+                        tc_commit(q_empty); // every S of this tile has been issued
+                    }
+                    const uint32_t gg = g + b, st = gg & 1, ph = (gg >> 1) & 1;
+                    if (!mbar_wait(&p_full[st], ph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                    if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < kBN / 16; ks++) {
+                        const uint64_t ad = umma_desc(p_addr + st * kPBytes + ks * 32, 16, 1024);
+                        // V is MN-major: 64 dims (128 B) x 8 keys per swizzle atom; next 64 dims one slab on
+                        // (leading offset), next 8 keys 1024 B on (stride offset); 16 keys per MMA.
+                        const uint64_t bd = umma_desc(v_addr + st * kKBytes + ks * 2048, kKChunk, 1024);
+                        tc_mma(tmem_o, ad, bd, idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&v_empty[st]);
+                    tc_commit(&p_empty[st]);
+                    if (b + 1 == t.nb) tc_commit(o_final);
+                }
+                g += t.nb;
+                tc++;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax, correction, epilogue
+        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        uint32_t g = 0, tc = 0;
+        bool ok = true;
+        PfTile t;
+        for (uint32_t round = 0; pf_tile(p, round, t); round++) {
+            const uint32_t tok = t.tok0 + (row >> 3), head = t.kv * kHeadsPerKv + (row & 7);
+            const bool row_live = tok < p.tokens;
+            const size_t rh = size_t(tok) * p.heads + head;
+            if (!t.nb) { // no key of the range is visible to this tile: an empty partial
+                if (row_live && p.part) {
+                    float *dst = p.part + rh * kPartStride;
+                    for (int d = 0; d < kDim; d++) dst[d] = 0.f;
+                    dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
+                }
+                continue;
+            }
+            const uint32_t lim_hi = min(p.key_hi, p.pos + tok + 1); // keys [key_lo, lim_hi) are visible
+            float m_ref = -INFINITY, l = 0.f;
+            for (uint32_t b = 0; ok && b < t.nb; b++, g++) {
+                const uint32_t st = g & 1, ph = (g >> 1) & 1;
+                const uint32_t key0 = (t.b_begin + b) * kBN;
+                if (!mbar_wait(&s_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                tc_fence_after();
+                uint32_t sr[2][32];
+                tmem_ld32(tmem_s + lane_addr + st * kBN, sr[0]);
+                tmem_ld32(tmem_s + lane_addr + st * kBN + 32, sr[1]);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_empty[st]);
+
+                // raw scores; the positive scale (in log2 units) is folded into the exponent's FFMA
+                float s[64];
+#pragma unroll
+                for (int c = 0; c < 64; c++) s[c] = __uint_as_float(sr[c >> 5][c & 31]);
+                const bool edge = key0 < p.key_lo || key0 + kBN > min(p.key_hi, p.pos + t.tok0 + 1);
+                if (edge) {
+#pragma unroll
+                    for (int c = 0; c < 64; c++)
+                        if (key0 + c < p.key_lo || key0 + c >= lim_hi) s[c] = -INFINITY;
+                }
+                float m4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+                for (int c = 4; c < 64; c++) m4[c & 3] = fmaxf(m4[c & 3], s[c]);
+                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+                // O is only rescaled when the maximum has moved by more than 2^8
+                const bool need = mx > m_ref + kPfRescale;
+                float factor = 1.f;
+                if (need) {
+                    factor = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - mx);
+                    m_ref = mx;
+                    l *= factor;
+                }
+                if (b > 0 && __any_sync(0xffffffffu, need)) {
+                    // P V of the block before must have landed in O before O is touched
+                    const uint32_t gp = g - 1;
+                    if (!mbar_wait(&p_empty[gp & 1], (gp >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < kDim; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_o + lane_addr + c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int k = 0; k < 32; k++) o[k] = __float_as_uint(__uint_as_float(o[k]) * factor);
+                        tmem_st32(tmem_o + lane_addr + c, o);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                if (!mbar_wait(&p_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                uint8_t *prow = sP + st * kPBytes + row * 128;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c8 = 0; c8 < 8; c8++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float a = ex2_approx(fmaf(s[c8 * 8 + 2 * k], p.scale_log2, -m_use));
+                        const float bb = ex2_approx(fmaf(s[c8 * 8 + 2 * k + 1], p.scale_log2, -m_use));
+                        sum4[k] += a + bb;
+                        if (p.v_fmt) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(a, bb);
+                            w[k] = *reinterpret_cast<uint32_t *>(&h);
+                        } else {
+                            w[k] = pack_half2(a, bb);
+                        }
+                    }
+                    *reinterpret_cast<uint4 *>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                l += sum;
+                fence_async_smem();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[st]);
+            }
+            if (!ok) break;
+            // ---------------- epilogue of the tile
+            if (!mbar_wait(o_final, tc & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+            tc_fence_after();
+            const float inv_l = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < kDim; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_addr + c, o);
+                tmem_wait_ld();
+                if (!row_live) continue;
+                if (p.out) {
+                    const float4 *gp = reinterpret_cast<const float4 *>(p.q_and_gate + rh * 2 * kDim + kDim + c);
+                    float4 *op = reinterpret_cast<float4 *>(p.out + rh * kDim + c);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const float4 gt = gp[k];
+                        float4 r;
+                        r.x = __uint_as_float(o[4 * k]) * __fdividef(inv_l, 1.f + __expf(-gt.x));
+                        r.y = __uint_as_float(o[4 * k + 1]) * __fdividef(inv_l, 1.f + __expf(-gt.y));
+                        r.z = __uint_as_float(o[4 * k + 2]) * __fdividef(inv_l, 1.f + __expf(-gt.z));
+                        r.w = __uint_as_float(o[4 * k + 3]) * __fdividef(inv_l, 1.f + __expf(-gt.w));
+                        op[k] = r;
+                    }
+                } else {
+                    float4 *op = reinterpret_cast<float4 *>(p.part + rh * kPartStride + c);
+#pragma unroll
+                    for (int k = 0; k < 8; k++)
+                        op[k] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
+                                            __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
+                }
+            }
+            if (row_live && p.part) {
+                p.part[rh * kPartStride + kPartM] = m_ref;
+                p.part[rh * kPartStride + kPartL] = l;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_empty);
+            tc++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+
+// ----------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+int prefill_configure(int device) {
+    (void)device;
+    SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    return SAETTA_OK;
+}
+
+int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(SAETTA_ERR_CUDA, "prefill attention: cuTensorMapEncodeTiled is not available");
+    if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15)
+        return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q, keys and values must be 16-byte aligned");
+    const CUtensorMapDataType dt = a.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap mq, mk, mv;
+    {
+        const cuuint64_t dims[4] = {cuuint64_t(kDim), cuuint64_t(kHeadsPerKv), a.kv_heads, a.tokens};
+        const cuuint64_t strides[3] = {kDim * 2, cuuint64_t(kHeadsPerKv) * kDim * 2, cuuint64_t(a.heads) * kDim * 2};
+        const cuuint32_t box[4] = {64, kHeadsPerKv, 1, kTokTile}, el[4] = {1, 1, 1, 1};
+        CUresult r = enc(&mq, dt, 4, const_cast<void *>(a.q), dims, strides, box, el, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for q rejected");
+    }
+    const cuuint64_t keys_total = cuuint64_t(a.pos) + a.tokens;
+    const CUtensorMapDataType dtv = a.v_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    for (int side = 0; side < 2; side++) {
+        const cuuint64_t dims[3] = {cuuint64_t(kDim), a.kv_heads, keys_total};
+        const cuuint64_t strides[2] = {kDim * 2, cuuint64_t(a.kv_heads) * kDim * 2};
+        const cuuint32_t box[3] = {64, 1, kBN}, el[3] = {1, 1, 1};
+        CUresult r = enc(side ? &mv : &mk, side ? dtv : dt, 3, const_cast<void *>(side ? a.v : a.k), dims, strides, box, el,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the cache rejected");
+    }
+    PfParams p{a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
+               a.scale * kLog2ePf, a.dtype == SAETTA_BF16 ? 1u : 0u, a.v_dtype == SAETTA_BF16 ? 1u : 0u};
+    int dev = 0;
+    SAETTA_CUDA(cudaGetDevice(&dev));
+    const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads;
+    const uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count(dev)));
+    prefill_kernel<<<grid, kPfThreads, kPfSmem, stream>>>(mq, mk, mv, p);
+    SAETTA_CUDA(cudaGetLastError());
+    return SAETTA_OK;
+}
+
+} // namespace saetta

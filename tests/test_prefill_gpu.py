@@ -1,0 +1,131 @@
+"""Chunked causal prefill attention (tcgen05 kernel) against the CPU oracle.
+
+Mirrors tests/attention_prefill.rs of the reference: its chunk shapes (partial
+tiles and key blocks), its `spread` inputs and (i % 7) - 3 gate pattern, and its
+2e-3 max-abs bound -- here against the CPU oracle instead of another GPU kernel
+-- plus the benchmark configurations on bfloat16 N(0,1) inputs with partial RoPE,
+a quantised prefix read through its 16-bit copy, and the split-key partials.
+Tolerance: 2e-3 max-abs and 1e-3 relative RMS.
+"""
+import numpy as np
+import pytest
+
+import saetta_macqwen_b200 as sa
+from util import DIM, HEADS, KV, ROW, dev, max_abs, rel_rms
+
+pytestmark = pytest.mark.gpu
+
+
+def to16(torch, x, dtype):
+    return dev(x).to(torch.float16 if dtype == sa.F16 else torch.bfloat16)
+
+
+def run(torch, q, k, v, qg, pos, tokens, dtype, quant=None, op=None):
+    out = torch.full((tokens * HEADS * DIM,), float("nan"), dtype=torch.float32, device="cuda")
+    op = op or sa.AttGemm(0, 4096, KV)
+    p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
+    op.encode(to16(torch, q, dtype), None if quant else to16(torch, k, dtype), None if quant else to16(torch, v, dtype),
+              quant, dev(qg), out, p, dtype=dtype)
+    torch.cuda.synchronize()
+    return out.cpu().numpy().reshape(tokens, HEADS, DIM)
+
+
+@pytest.mark.parametrize("pos,tokens", [(0, 1), (0, 7), (5, 8), (70, 100), (1000, 64), (0, 300), (4093, 37)])
+def test_matches_cpu_on_reference_shapes(oracle, pos, tokens):
+    import torch
+
+    capacity = (pos + tokens + 63) // 64 * 64 + 64
+    q = oracle.round_f16(oracle.spread(tokens * HEADS * DIM, 1))
+    k = oracle.round_f16(oracle.spread(capacity * ROW, 2))
+    v = oracle.round_f16(oracle.spread(capacity * ROW, 3))
+    qg = ((np.arange(tokens * HEADS * 2 * DIM) % 7) - 3).astype(np.float32)
+    got = run(torch, q, k, v, qg, pos, tokens, sa.F16)
+    want = oracle.attention_rows(q, qg, k, v, [pos + i + 1 for i in range(tokens)], threads=8)
+    assert np.isfinite(got).all()
+    assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3, (pos, tokens, max_abs(got, want), rel_rms(got, want))
+
+
+def bf16_inputs(oracle, pos, tokens, seed):
+    total = pos + tokens
+    k = oracle.rope_rows(oracle.normal(total * ROW, seed).reshape(total, ROW), DIM, 64, range(total), 1e7)
+    v = oracle.normal(total * ROW, seed + 1)
+    q = oracle.rope_rows(oracle.normal(tokens * HEADS * DIM, seed + 2).reshape(tokens, -1), DIM, 64,
+                         range(pos, total), 1e7)
+    qg = np.zeros((tokens * HEADS, 2 * DIM), np.float32)
+    qg[:, DIM:] = oracle.normal(tokens * HEADS * DIM, seed + 3).reshape(-1, DIM)
+    return oracle.round_bf16(q.ravel()), oracle.round_bf16(k.ravel()), oracle.round_bf16(v), qg.ravel()
+
+
+def check_rows(oracle, got, q, qg, k, v, pos, rows):
+    qs = q.reshape(-1, HEADS * DIM)[rows]
+    gs = qg.reshape(-1, HEADS * 2 * DIM)[rows]
+    want = oracle.attention_rows(qs, gs, k, v, [pos + int(r) + 1 for r in rows], threads=8)
+    g = got[rows]
+    assert np.isfinite(got).all()
+    assert max_abs(g, want) < 2e-3 and rel_rms(g, want) < 1e-3, (max_abs(g, want), rel_rms(g, want))
+    return max_abs(g, want), rel_rms(g, want)
+
+
+def test_config2_chunk_4096_bf16(oracle):
+    """4096-token chunk, no prior context, bf16 Q/K/V ~N(0,1) with partial RoPE, causal, gate."""
+    import torch
+
+    pos, tokens = 0, 4096
+    q, k, v, qg = bf16_inputs(oracle, pos, tokens, 200)
+    got = run(torch, q, k, v, qg, pos, tokens, sa.BF16)
+    rng = np.random.default_rng(0)
+    rows = np.unique(np.concatenate([[0, 1, 15, 16, 17, 63, 64, 65, 2047, 2048, 4079, 4080, 4095],
+                                     rng.integers(0, tokens, 51)]))
+    print("config 2:", check_rows(oracle, got, q, qg, k, v, pos, rows))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_quantised_prefix_reads_through_16bit_copy(oracle, bits):
+    """AttGemm::encode with quant: the chunk's rows are quantised into the cache
+    first (src/prefill.rs:1656-1666), then keys and values are read as the
+    16-bit rounding of s*q+z (src/kv_quant.rs:121-126; keys in q's bfloat16, values binary16)."""
+    import torch
+
+    pos, tokens = 1000, 72
+    total = pos + tokens
+    q, k, v, qg = bf16_inputs(oracle, pos, tokens, 300)
+    cache = sa.GpuKvCache(0, bits, total)
+    cache.store_at(dev(k), dev(v), 0, total)
+    got = run(torch, q, None, None, qg, pos, tokens, sa.BF16, quant=cache.quant())
+    kr = oracle.round_trip_as_half(k, bits, bf16=True)  # keys in q's type
+    vr = oracle.round_trip_as_half(v, bits)             # values as binary16, the reference's own reading
+    check_rows(oracle, got, q, qg, kr, vr, pos, np.arange(tokens))
+
+
+def test_split_key_partials_merge_to_the_whole(oracle):
+    import torch
+
+    pos, tokens = 500, 40
+    total = pos + tokens
+    q, k, v, qg = bf16_inputs(oracle, pos, tokens, 400)
+    whole = run(torch, q, k, v, qg, pos, tokens, sa.BF16)
+    op = sa.AttGemm(0, 4096, KV)
+    p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
+    cuts = [0, 200, 517, total]
+    parts = torch.zeros((len(cuts) - 1, tokens * HEADS * sa.PART_STRIDE), dtype=torch.float32, device="cuda")
+    qd, kd, vd = to16(torch, q, sa.BF16), to16(torch, k, sa.BF16), to16(torch, v, sa.BF16)
+    for i in range(len(cuts) - 1):
+        op.partial(qd, kd, vd, None, parts[i], p, cuts[i], cuts[i + 1], dtype=sa.BF16)
+    out = torch.zeros(tokens * HEADS * DIM, dtype=torch.float32, device="cuda")
+    sa.merge_partials(0, parts, len(cuts) - 1, tokens, HEADS, dev(qg), out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
+    assert max_abs(got, whole) < 2e-3 and rel_rms(got, whole) < 1e-3  # two roundings of P apart
+    want = oracle.attention_rows(q, qg, k, v, [pos + i + 1 for i in range(tokens)], threads=8)
+    assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3
+
+
+def test_shape_errors(oracle):
+    import torch
+
+    op = sa.AttGemm(0, 64, KV)
+    z = torch.zeros(16, device="cuda")
+    with pytest.raises(sa.SaettaError):  # more tokens than the op's chunk
+        op.encode(z, z, z, None, z, z, sa.FlashParams(HEADS, KV, 0, 65, 0.0625))
+    with pytest.raises(sa.SaettaError):  # 8 q heads per kv head
+        op.encode(z, z, z, None, z, z, sa.FlashParams(12, KV, 0, 8, 0.0625))
