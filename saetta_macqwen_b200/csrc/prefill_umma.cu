@@ -134,6 +134,16 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes
     return d;
 }
 
+#ifdef SAETTA_PF_TRACE
+// Cycle accounting per CTA and role for tuning builds only (never in the shipped library).
+__device__ unsigned long long pf_trace[160][16];
+#define PF_T0() const long long t0_ = clock64()
+#define PF_ADD(slot) if (lane == 0) pf_trace[blockIdx.x][slot] += (unsigned long long)(clock64() - t0_)
+#else
+#define PF_T0()
+#define PF_ADD(slot)
+#endif
+
 struct PfTile {
     uint32_t tok0, kv, b_begin, nb;
 };
@@ -239,8 +249,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             PfTile t;
             auto issue_s = [&](uint32_t gg) -> bool { // S[gg&1] = Q K^T for the block with running index gg
                 const uint32_t st = gg & 1, ph = (gg >> 1) & 1;
-                if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); return false; }
-                if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+                { PF_T0(); if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); return false; } PF_ADD(0); }
+                { PF_T0(); if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; } PF_ADD(1); }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kDim / 16; ks++) {
@@ -263,8 +273,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         tc_commit(q_empty); // every S of this tile has been issued
                     }
                     const uint32_t gg = g + b, st = gg & 1, ph = (gg >> 1) & 1;
-                    if (!mbar_wait(&p_full[st], ph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
-                    if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                    { PF_T0(); if (!mbar_wait(&p_full[st], ph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(2); }
+                    { PF_T0(); if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } PF_ADD(3); }
                     if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -307,12 +317,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (uint32_t b = 0; ok && b < t.nb; b++, g++) {
                 const uint32_t st = g & 1, ph = (g >> 1) & 1;
                 const uint32_t key0 = (t.b_begin + b) * kBN;
-                if (!mbar_wait(&s_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                { PF_T0(); if (!mbar_wait(&s_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } if (quarter == 0) { PF_ADD(4); } }
                 tc_fence_after();
                 uint32_t sr[2][32];
+                PF_T0();
                 tmem_ld32(tmem_s + lane_addr + st * kBN, sr[0]);
                 tmem_ld32(tmem_s + lane_addr + st * kBN + 32, sr[1]);
                 tmem_wait_ld();
+                if (quarter == 0) { PF_ADD(5); }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s_empty[st]);
@@ -357,7 +369,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tc_fence_before();
                 }
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                if (quarter == 0) { PF_ADD(6); } // from the first tmem load to here: S read + max + any rescale
                 if (!mbar_wait(&p_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                if (quarter == 0) { PF_ADD(7); }
                 uint8_t *prow = sP + st * kPBytes + row * 128;
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -383,10 +397,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_full[st]);
+                if (quarter == 0) { PF_ADD(8); }
             }
             if (!ok) break;
             // ---------------- epilogue of the tile
+            PF_T0();
             if (!mbar_wait(o_final, tc & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+            if (quarter == 0) { PF_ADD(9); }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll 1
@@ -423,6 +440,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(o_empty);
+            if (quarter == 0) { PF_ADD(10); }
             tc++;
         }
     }
@@ -495,3 +513,14 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
 }
 
 } // namespace saetta
+
+#ifdef SAETTA_PF_TRACE
+extern "C" int saetta_debug_prefill_trace(unsigned long long *out, int reset) {
+    if (out) cudaMemcpyFromSymbol(out, saetta::pf_trace, sizeof(saetta::pf_trace));
+    if (reset) {
+        static unsigned long long zero[160][16];
+        cudaMemcpyToSymbol(saetta::pf_trace, zero, sizeof(zero));
+    }
+    return 0;
+}
+#endif
