@@ -182,6 +182,26 @@ int saetta_decode_record_cache(saetta_decode *op, size_t m, const float *q_dev,
                                const saetta_kv_cache *cache, const float *q_and_gate_dev,
                                float *out_dev, const saetta_token_params *params_dev,
                                void *stream);
+/* No counterpart in the reference.  The same computation as
+ * saetta_decode_record_quant for m = 1 or 2 rows, for callers that are not
+ * allowed to allocate device memory: a host process whose memory pool was sized
+ * up front and hands this library no allocator, or a latency-critical decode
+ * loop in which cudaMalloc (which serialises the device) must never run.  No
+ * op object is needed and nothing is allocated, now or later: the split-KV
+ * partials go to a fixed array inside the library's device image (about 5.3 MB,
+ * resident on every GPU that loads the library until the process exits).
+ * Limits: m <= 2, 2 kv heads, capacity a multiple of 32; anything larger is
+ * refused with SAETTA_ERR_BAD_SHAPE and should go through saetta_decode_create.
+ * The first call on a device looks up the array's device address and raises the
+ * kernel's shared-memory limit; make that call once outside any stream capture.
+ * All calls on a device share the one array: two calls that overlap on the GPU
+ * (different streams) race on it and give wrong results; calls ordered on one
+ * stream are fine, and nothing needs clearing between them. */
+int saetta_decode_record_quant_static(int device, size_t m, const float *q_dev,
+                                      const saetta_quant_rows *keys,
+                                      const saetta_quant_rows *values,
+                                      const float *q_and_gate_dev, float *out_dev,
+                                      const saetta_token_params *params_dev, void *stream);
 /* Number of split-KV parts the op launches (its grid), and the device status
  * word of its bounded waits: 0 when no wait ever gave up.  Synchronises `stream`. */
 int saetta_decode_splits(const saetta_decode *op);

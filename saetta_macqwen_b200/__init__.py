@@ -98,6 +98,7 @@ SYMBOLS = {
     "saetta_decode_record": (_I, [_P, _Z, _P, _P, _P, _I, _P, _P, _P, _P]),
     "saetta_decode_record_quant": (_I, [_P, _Z, _P, _P, _P, _P, _P, _P, _P]),
     "saetta_decode_record_cache": (_I, [_P, _Z, _P, _P, _P, _P, _P, _P]),
+    "saetta_decode_record_quant_static": (_I, [_I, _Z, _P, _P, _P, _P, _P, _P, _P]),
     "saetta_decode_splits": (_I, [_P]),
     "saetta_decode_device_status": (_I, [_P, _P, C.POINTER(_U32)]),
     "saetta_decode_batch_create": (_I, [_I, _Z, _Z, _Z, _Z, _Z, _PP]),
@@ -329,6 +330,14 @@ class DecodeAttention(AttentionRows):
 
     def record_quant(self, q, keys, values, q_and_gate, out, params, stream=None):
         super().record_quant(1, q, keys, values, q_and_gate, out, params, stream=stream)
+
+
+def decode_record_quant_static(device, m, q, keys, values, q_and_gate, out, params, stream=None):
+    """Decode / 2-row verify over a quantised cache without any allocation: the
+    split-KV scratch is a fixed array inside the library (see the header).  For
+    callers that may not call cudaMalloc; m <= 2."""
+    _check(lib().saetta_decode_record_quant_static(device, m, ptr(q), keys.h, values.h, ptr(q_and_gate), ptr(out),
+                                                   ptr(params), _stream(stream)))
 
 
 class DecodeBatch:

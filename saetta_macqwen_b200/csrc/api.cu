@@ -578,6 +578,20 @@ int saetta_decode_record_quant(saetta_decode *op, size_t m, const float *q_dev, 
                       (cudaStream_t)stream);
 }
 
+int saetta_decode_record_quant_static(int device, size_t m, const float *q_dev, const saetta_quant_rows *keys,
+                                      const saetta_quant_rows *values, const float *q_and_gate_dev, float *out_dev,
+                                      const saetta_token_params *params_dev, void *stream) {
+    if (!q_dev || !keys || !values || !q_and_gate_dev || !out_dev || !params_dev)
+        return fail(SAETTA_ERR_BAD_ARG, "static decode: null pointer");
+    if (!aligned16(q_dev)) return fail(SAETTA_ERR_BAD_ARG, "static decode: q must be 16-byte aligned");
+    if (keys->bits != values->bits || keys->per_token != values->per_token || keys->capacity != values->capacity)
+        return fail(SAETTA_ERR_BAD_SHAPE, "static decode: keys and values differ in format");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "static decode: cannot select the device");
+    return decode_quant_static(device, view_of(keys, values), keys->capacity, q_dev, uint32_t(m), q_and_gate_dev,
+                               out_dev, params_dev, (cudaStream_t)stream);
+}
+
 static KvView view_of_cache(const saetta_kv_cache *c) {
     if (c->bits == 8 || c->bits == 4) return view_of(&c->k, &c->v);
     KvView kv;

@@ -26,6 +26,8 @@
 //    by the value scales; the value biases ride along as one more MMA.
 //  * Every wait on an mbarrier is bounded; a wait that gives up sets a bit in
 //    the status word, raises the CTA's abort flag and the CTA drains and leaves.
+#include <algorithm>
+
 #include "host.hpp"
 
 namespace saetta {
@@ -548,6 +550,59 @@ int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uin
     a.q = q, a.parts = parts, a.status = status, a.params = nullptr;
     a.m = 1, a.row_step = 0, a.capacity = 0xffffffffu;
     return bits == 8 ? launch_one<8, 1>(a, dim3(ctas, 1), stream) : launch_one<4, 1>(a, dim3(ctas, 1), stream);
+}
+
+// ----------------------------------------------------------------- fixed-scratch entry point
+//
+// Scratch for saetta_decode_record_quant_static: the split-KV partials and the
+// status word live in this file-scope device array instead of a cudaMalloc'd
+// buffer.  Every GPU that loads the library holds these bytes until exit.
+constexpr int kStaticMaxRows = 2;
+constexpr int kStaticMaxSplits = 160;
+constexpr size_t kStaticFloats = size_t(kStaticMaxSplits) * kStaticMaxRows * kKv * kPartKv; // 5.3 MB
+static __device__ __align__(256) float g_static_parts[kStaticFloats];
+static __device__ __align__(256) uint32_t g_static_status[64];
+
+struct StaticScratch {
+    float *parts = nullptr;   // device address of g_static_parts on that device
+    uint32_t *status = nullptr;
+    int splits = 0;
+};
+static StaticScratch g_static[64];
+
+// Looks up, once per device and with that device current, the device addresses
+// of the two arrays above.  In host code their names are only host-side handles:
+// a kernel must be given what cudaGetSymbolAddress returns.
+static int static_scratch(int device, StaticScratch **out) {
+    if (device < 0 || device >= 64) return fail(SAETTA_ERR_BAD_ARG, "static decode: device index out of range");
+    StaticScratch &s = g_static[device];
+    if (!s.parts) {
+        void *parts = nullptr, *status = nullptr;
+        SAETTA_CUDA(cudaGetSymbolAddress(&parts, g_static_parts));
+        SAETTA_CUDA(cudaGetSymbolAddress(&status, g_static_status));
+        if (int rc = decode_quant_configure(device)) return rc;
+        s.splits = std::min(sm_count(device), kStaticMaxSplits);
+        s.status = static_cast<uint32_t *>(status);
+        s.parts = static_cast<float *>(parts);
+    }
+    *out = &s;
+    return SAETTA_OK;
+}
+
+int decode_quant_static(int device, const KvView &kv, size_t capacity, const float *q, uint32_t m,
+                        const float *q_and_gate, float *out, const saetta_token_params *params,
+                        cudaStream_t stream) {
+    if (m < 1 || m > uint32_t(kStaticMaxRows))
+        return fail(SAETTA_ERR_BAD_SHAPE, "static decode: at most 2 query rows fit the fixed scratch (use saetta_decode_create for more)");
+    if (kv.kv_heads != kKv) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: built for 2 kv heads");
+    if (capacity % kTile || !capacity) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: capacity must be a positive multiple of 32");
+    if (capacity > 0xffffffe0ull) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: capacity too large");
+    StaticScratch *s = nullptr;
+    if (int rc = static_scratch(device, &s)) return rc;
+    const int splits = int(std::min<size_t>(size_t(s->splits), capacity / kTile));
+    // The kernels overwrite every partial they later read, so nothing has to be cleared between calls.
+    if (int rc = launch_decode_quant(kv, q, s->parts, s->status, m, 1, splits, uint32_t(capacity), params, stream)) return rc;
+    return launch_merge_frag(s->parts, uint32_t(splits), nullptr, m, kKv, q_and_gate, out, nullptr, stream);
 }
 
 } // namespace saetta

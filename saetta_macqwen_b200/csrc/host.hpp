@@ -120,6 +120,9 @@ int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uin
                                 int ctas, const float *q, float *parts, uint32_t *status,
                                 cudaStream_t stream);
 int decode_quant_configure(int device);
+int decode_quant_static(int device, const KvView &kv, size_t capacity, const float *q, uint32_t m,
+                        const float *q_and_gate, float *out, const saetta_token_params *params,
+                        cudaStream_t stream);
 
 // decode_exact.cu: f32 arithmetic over f32 / 16-bit rows.
 int launch_decode_exact(const KvView &kv, const float *q, float *parts, uint32_t m,
