@@ -35,7 +35,7 @@ namespace saetta {
 constexpr int kTile = 32;     // tokens per stage
 constexpr int kSub = 16;      // tokens per MMA sub-tile
 constexpr int kWarps = 8;     // consumer warps
-constexpr int kThreads = (kWarps + 1) * 32;
+constexpr int kThreads = (kWarps + 4) * 32; // two consumer warpgroups + the producer's warpgroup
 constexpr int kKv = 2;        // kv heads covered by one stage
 constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in fragment order
 constexpr int kPartKv = kFragFloats + 16; // + m[8], l[8]
@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kWarps);
         }
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = 0; // a word that stays 0, for waits that must ignore the abort flag
         mbar_fence_init();
     }
     __syncthreads();
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         return s;
     };
 
-    if (warp == kWarps) {
+    auto producer_role = [&]() {
         // ---------------------------------------------------------------- producer
         uint32_t it = 0;
         bool ok = true;
@@ -170,8 +171,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         const uint32_t issued = it;
         for (uint32_t k = issued > NS ? issued - NS : 0; k < issued; k++)
             mbar_wait(&full[k % NS], (k / NS) & 1, abort_flag, 2000000u);
+    };
+
+    // Registers move from the producer's warpgroup (only one of its warps works, and it needs
+    // few) to the two consumer warpgroups, whose accumulators and query fragments would
+    // otherwise spill inside the inner loop.
+    if (warp >= kWarps) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == kWarps) producer_role();
         return;
     }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
 
     // -------------------------------------------------------------------- consumers
     const int kv = warp & 1;
@@ -191,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         // Query fragments of head kv*8+g: 16 dims per group, scaled by log2(e)/16,
         // split into two halves; and the group sums for the bias term.
         uint32_t qh[4][8], ql[4][8];
-        uint32_t qsb = 0; // B fragment of the group sums (hi for i<2, lo for i>=2)
+        uint32_t qza0 = 0, qza1 = 0;
         {
             float qs[4];
             const float *qp = a.q + ((size_t(s.seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
@@ -223,17 +233,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                 qs[G] = sum;
             }
-            const int p = (i & 1) * 2; // groups 2(i&1), 2(i&1)+1
-            const float s0 = p ? qs[2] : qs[0], s1 = p ? qs[3] : qs[1];
+            // A fragment of the bias-term MMA: row g = high halves of the group sums of head g,
+            // row g+8 = low halves; k-slots 0..3 = groups (lanes i < 2 hold two groups each).
+            const float s0 = i == 0 ? qs[0] : qs[2], s1 = i == 0 ? qs[1] : qs[3];
             const float h0 = __half2float(__float2half_rn(s0)), h1 = __half2float(__float2half_rn(s1));
-            qsb = i < 2 ? pack_half2(h0, h1) : pack_half2(s0 - h0, s1 - h1);
+            qza0 = i < 2 ? pack_half2(h0, h1) : 0u;
+            qza1 = i < 2 ? pack_half2(s0 - h0, s1 - h1) : 0u;
         }
 
         float O[16][4];
         float Ob[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int e = 0; e < 16; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
-        float Mref[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float Mref = -INFINITY, lsum = 0.f; // of head g (this thread's row of the score MMA)
 
         for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
             const uint32_t st = it % NS, round = it / NS;
@@ -254,110 +266,111 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 const bool partial = tok0 + kSub > n_row;
                 const int lt = sub * kSub; // token offset inside the stage
 
-                // ------------------------------------------------ scores S^T[token][head]
-                float S[4] = {0.f, 0.f, 0.f, 0.f};
+                // ------------------------------------------------ scores S[head][token]
+                // MMA rows 0..7 = high halves of the 8 query heads, rows 8..15 = their low halves;
+                // columns = 8 tokens.  Lane (g, i) feeds token g of each 8-token tile and owns
+                // head g at tokens 2i, 2i+1.
+                float S[2][2];
                 const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
-                const uint2 sKa = *reinterpret_cast<const uint2 *>(sg + St::kKs + (lt + g) * St::kParamRow + kv * 8);
-                const uint2 sKb = *reinterpret_cast<const uint2 *>(sg + St::kKs + (lt + g + 8) * St::kParamRow + kv * 8);
 #pragma unroll
-                for (int G = 0; G < 4; G++) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (BITS == 8) {
-                        const uint4 ra = *reinterpret_cast<const uint4 *>(kc + (lt + g) * St::kCodeRow + G * 64 + i * 16);
-                        const uint4 rb = *reinterpret_cast<const uint4 *>(kc + (lt + g + 8) * St::kCodeRow + G * 64 + i * 16);
-                        const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wb[4] = {rb.x, rb.y, rb.z, rb.w};
+                for (int nt = 0; nt < 2; nt++) {
+                    const int trow = lt + nt * 8 + g;          // token this lane loads
+                    const int tc0 = lt + nt * 8 + 2 * i;       // tokens of this lane's columns
+                    const uint2 sK0 = *reinterpret_cast<const uint2 *>(sg + St::kKs + tc0 * St::kParamRow + kv * 8);
+                    const uint2 sK1 = *reinterpret_cast<const uint2 *>(sg + St::kKs + (tc0 + 1) * St::kParamRow + kv * 8);
+                    float s_a = 0.f, s_b = 0.f;
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const uint32_t a0 = hsub2_u32(prmt(wa[j], kMagic, 0x4140), k1024);
-                            const uint32_t a1 = hsub2_u32(prmt(wb[j], kMagic, 0x4140), k1024);
-                            const uint32_t a2 = hsub2_u32(prmt(wa[j], kMagic, 0x4342), k1024);
-                            const uint32_t a3 = hsub2_u32(prmt(wb[j], kMagic, 0x4342), k1024);
-                            mma_f16(acc, a0, a1, a2, a3, qh[G][2 * j], qh[G][2 * j + 1]);
-                            mma_f16(acc, a0, a1, a2, a3, ql[G][2 * j], ql[G][2 * j + 1]);
-                        }
-                    } else {
-                        const uint2 ra = *reinterpret_cast<const uint2 *>(kc + (lt + g) * St::kCodeRow + G * 32 + i * 8);
-                        const uint2 rb = *reinterpret_cast<const uint2 *>(kc + (lt + g + 8) * St::kCodeRow + G * 32 + i * 8);
-                        const uint32_t wa[2] = {ra.x, ra.y}, wb[2] = {rb.x, rb.y};
+                    for (int G = 0; G < 4; G++) {
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (BITS == 8) {
+                            const uint4 r = *reinterpret_cast<const uint4 *>(kc + trow * St::kCodeRow + G * 64 + i * 16);
+                            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-                        for (int w = 0; w < 2; w++) {
+                            for (int j = 0; j < 4; j++) {
+                                const uint32_t b0 = hsub2_u32(prmt(w[j], kMagic, 0x4140), k1024);
+                                const uint32_t b1 = hsub2_u32(prmt(w[j], kMagic, 0x4342), k1024);
+                                mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
+                            }
+                        } else {
+                            const uint2 r = *reinterpret_cast<const uint2 *>(kc + trow * St::kCodeRow + G * 32 + i * 8);
+                            const uint32_t w[2] = {r.x, r.y};
 #pragma unroll
-                            for (int hlf = 0; hlf < 2; hlf++) {
-                                const uint32_t xa = wa[w] >> (8 * hlf), xb = wb[w] >> (8 * hlf);
-                                const uint32_t a0 = hsub2_u32(lop_and_or(xa, 0x000f000fu, k1024), k1024);
-                                const uint32_t a1 = hsub2_u32(lop_and_or(xb, 0x000f000fu, k1024), k1024);
-                                const uint32_t a2 = hsub2_u32(lop_and_or(xa, 0x00f000f0u, k64), k64);
-                                const uint32_t a3 = hsub2_u32(lop_and_or(xb, 0x00f000f0u, k64), k64);
-                                const int j = 2 * w + hlf;
-                                mma_f16(acc, a0, a1, a2, a3, qh[G][2 * j], qh[G][2 * j + 1]);
-                                mma_f16(acc, a0, a1, a2, a3, ql[G][2 * j], ql[G][2 * j + 1]);
+                            for (int j = 0; j < 4; j++) {
+                                const uint32_t x = w[j >> 1] >> (8 * (j & 1));
+                                const uint32_t b0 = hsub2_u32(lop_and_or(x, 0x000f000fu, k1024), k1024);
+                                const uint32_t b1 = hsub2_u32(lop_and_or(x, 0x00f000f0u, k64), k64);
+                                mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
                             }
                         }
+                        const uint32_t p0 = G < 2 ? sK0.x : sK0.y, p1 = G < 2 ? sK1.x : sK1.y;
+                        const float sc0 = half_bits_to_float((p0 >> (16 * (G & 1))) & 0xffffu);
+                        const float sc1 = half_bits_to_float((p1 >> (16 * (G & 1))) & 0xffffu);
+                        s_a = fmaf(sc0, acc[0] + acc[2], s_a);
+                        s_b = fmaf(sc1, acc[1] + acc[3], s_b);
                     }
-                    const uint32_t pa = G < 2 ? sKa.x : sKa.y, pb = G < 2 ? sKb.x : sKb.y;
-                    const float sa = half_bits_to_float((pa >> (16 * (G & 1))) & 0xffffu);
-                    const float sb = half_bits_to_float((pb >> (16 * (G & 1))) & 0xffffu);
-                    S[0] = fmaf(sa, acc[0], S[0]);
-                    S[1] = fmaf(sa, acc[1], S[1]);
-                    S[2] = fmaf(sb, acc[2], S[2]);
-                    S[3] = fmaf(sb, acc[3], S[3]);
-                }
-                {   // bias term: sum_G z[token][G] * qsum[head][G]; k-slots 0..3 pair with the
-                    // high halves of the sums, 4..7 with the low halves.
-                    const uint32_t za = *reinterpret_cast<const uint32_t *>(sg + St::kKz + (lt + g) * St::kParamRow + kv * 8 + (i & 1) * 4);
-                    const uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + (lt + g + 8) * St::kParamRow + kv * 8 + (i & 1) * 4);
-                    mma_f16(S, za, zb, 0u, 0u, qsb, 0u);
-                }
-                if (partial) {
-                    if (tok0 + g >= n_row) S[0] = S[1] = -INFINITY;
-                    if (tok0 + g + 8 >= n_row) S[2] = S[3] = -INFINITY;
+                    {   // bias term: sum_G z[token][G] * qsum[head][G] (k-slots 0..3 = groups)
+                        float accz[4] = {0.f, 0.f, 0.f, 0.f};
+                        uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + trow * St::kParamRow + kv * 8 + (i & 1) * 4);
+                        if (i >= 2) zb = 0u;
+                        mma_f16(accz, qza0, qza1, 0u, 0u, zb, 0u);
+                        s_a += accz[0] + accz[2];
+                        s_b += accz[1] + accz[3];
+                    }
+                    S[nt][0] = s_a, S[nt][1] = s_b;
+                    if (partial) {
+                        if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
+                        if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
+                    }
                 }
 
-                // ------------------------------------------------ online softmax (log2 units)
-                float mx0 = fmaxf(S[0], S[2]), mx1 = fmaxf(S[1], S[3]);
-#pragma unroll
-                for (int off = 4; off < 32; off <<= 1) {
-                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-                }
-                const bool need0 = mx0 > Mref[0] + kRescale, need1 = mx1 > Mref[1] + kRescale;
-                if (__any_sync(0xffffffffu, need0 || need1)) {
-                    const float n0 = need0 ? mx0 : Mref[0], n1 = need1 ? mx1 : Mref[1];
-                    const float f0 = need0 ? exp2f(Mref[0] - n0) : 1.f, f1 = need1 ? exp2f(Mref[1] - n1) : 1.f;
+                // ------------------------------------------------ online softmax of head g (log2 units)
+                float mx = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const bool need = mx > Mref + kRescale;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float f = need ? exp2f(Mref - mx) : 1.f; // exp2f(-inf) = 0 on the first tile
+                    if (need) Mref = mx, lsum *= f;
+                    // the accumulators' columns are heads 2i, 2i+1: fetch their factors from lanes g = 2i, 2i+1
+                    const float f0 = __shfl_sync(0xffffffffu, f, 8 * i), f1 = __shfl_sync(0xffffffffu, f, 8 * i + 4);
 #pragma unroll
                     for (int e = 0; e < 16; e++) {
                         O[e][0] *= f0, O[e][1] *= f1, O[e][2] *= f0, O[e][3] *= f1;
                     }
                     Ob[0] *= f0, Ob[1] *= f1, Ob[2] *= f0, Ob[3] *= f1;
-                    l[0] *= f0, l[1] *= f1;
-                    Mref[0] = n0, Mref[1] = n1;
                 }
-                const float p0 = exp2f(S[0] - Mref[0]), p1 = exp2f(S[1] - Mref[1]);
-                const float p2 = exp2f(S[2] - Mref[0]), p3 = exp2f(S[3] - Mref[1]);
-                l[0] += p0 + p2;
-                l[1] += p1 + p3;
+                const float p00 = exp2f(S[0][0] - Mref), p01 = exp2f(S[0][1] - Mref);
+                const float p10 = exp2f(S[1][0] - Mref), p11 = exp2f(S[1][1] - Mref);
+                lsum += (p00 + p01) + (p10 + p11);
 
                 // ------------------------------------------------ P (x value scales) as B fragments
-                uint2 sVa = *reinterpret_cast<const uint2 *>(sg + St::kVs + (lt + g) * St::kParamRow + kv * 8);
-                uint2 sVb = *reinterpret_cast<const uint2 *>(sg + St::kVs + (lt + g + 8) * St::kParamRow + kv * 8);
+                // B[k = token][n = head]: this lane's pairs (2i, 2i+1) and (8+2i, 9+2i) of head g are
+                // exactly its own score columns, so no data moves between lanes.
+                const int T0 = lt + 2 * i, T1 = T0 + 1, T2 = T0 + 8, T3 = T0 + 9;
+                uint2 sV[4];
+                sV[0] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T0 * St::kParamRow + kv * 8);
+                sV[1] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T1 * St::kParamRow + kv * 8);
+                sV[2] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T2 * St::kParamRow + kv * 8);
+                sV[3] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T3 * St::kParamRow + kv * 8);
                 if (partial) { // stale rows may hold anything: keep them out of 0 * x
-                    if (tok0 + g >= n_row) sVa = make_uint2(0u, 0u);
-                    if (tok0 + g + 8 >= n_row) sVb = make_uint2(0u, 0u);
+                    if (tok0 + 2 * i >= n_row) sV[0] = make_uint2(0u, 0u);
+                    if (tok0 + 2 * i + 1 >= n_row) sV[1] = make_uint2(0u, 0u);
+                    if (tok0 + 2 * i + 8 >= n_row) sV[2] = make_uint2(0u, 0u);
+                    if (tok0 + 2 * i + 9 >= n_row) sV[3] = make_uint2(0u, 0u);
                 }
                 uint32_t pbf[4][2];
 #pragma unroll
                 for (int G = 0; G < 4; G++) {
-                    const uint32_t pa = G < 2 ? sVa.x : sVa.y, pb = G < 2 ? sVb.x : sVb.y;
-                    const float sa = half_bits_to_float((pa >> (16 * (G & 1))) & 0xffffu);
-                    const float sb = half_bits_to_float((pb >> (16 * (G & 1))) & 0xffffu);
-                    pbf[G][0] = movmatrix_trans(pack_half2(p0 * sa, p1 * sa));
-                    pbf[G][1] = movmatrix_trans(pack_half2(p2 * sb, p3 * sb));
+                    float sc[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        sc[k] = half_bits_to_float(((G < 2 ? sV[k].x : sV[k].y) >> (16 * (G & 1))) & 0xffffu);
+                    pbf[G][0] = pack_half2(p00 * sc[0], p01 * sc[1]);
+                    pbf[G][1] = pack_half2(p10 * sc[2], p11 * sc[3]);
                 }
-                const uint32_t pu0 = movmatrix_trans(pack_half2(p0, p1));
-                const uint32_t pu1 = movmatrix_trans(pack_half2(p2, p3));
+                const uint32_t pu0 = pack_half2(p00, p01), pu1 = pack_half2(p10, p11);
 
                 // ------------------------------------------------ O^T[dim][head] += V^T P^T
-                const int T0 = lt + 2 * i, T1 = T0 + 1, T2 = T0 + 8, T3 = T0 + 9;
                 {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] z[t][G]
                     const uint8_t *vz = sg + St::kVz + kv * 8 + (g & 3) * 2;
                     uint32_t z0 = *reinterpret_cast<const uint16_t *>(vz + T0 * St::kParamRow);
@@ -421,12 +434,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         }
 
         // ---------------------------------------------------------------- end of segment
-        // l over the eight lanes that share the heads; value-bias rows into O.
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            l[0] += __shfl_xor_sync(0xffffffffu, l[0], off);
-            l[1] += __shfl_xor_sync(0xffffffffu, l[1], off);
-        }
+        // l of head g over the four lanes that share it; then every lane takes m and l of the
+        // heads of its accumulator columns (2i, 2i+1) from lanes g = 2i and g = 2i+1.
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+        float Mc2[2], l[2];
+        Mc2[0] = __shfl_sync(0xffffffffu, Mref, 8 * i), Mc2[1] = __shfl_sync(0xffffffffu, Mref, 8 * i + 4);
+        l[0] = __shfl_sync(0xffffffffu, lsum, 8 * i), l[1] = __shfl_sync(0xffffffffu, lsum, 8 * i + 4);
 #pragma unroll
         for (int G = 0; G < 4; G++) {
             const float b0 = __shfl_sync(0xffffffffu, Ob[0], 4 * G + i);
@@ -445,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
                     for (int c = 0; c < 4; c++) dst[(4 * e + c) * 32 + lane] = O[e][c];
                 if (g == 0) {
-                    dst[kFragFloats + 2 * i] = Mref[0], dst[kFragFloats + 2 * i + 1] = Mref[1];
+                    dst[kFragFloats + 2 * i] = Mc2[0], dst[kFragFloats + 2 * i + 1] = Mc2[1];
                     dst[kFragFloats + 8 + 2 * i] = l[0], dst[kFragFloats + 8 + 2 * i + 1] = l[1];
                 }
             }
@@ -453,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             // Warps that share a (kv, row) agree on one maximum, scale, and add up
             // in a fixed order through shared memory (deterministic).
             if (g == 0) {
-                ml[warp * 16 + 2 * i] = Mref[0], ml[warp * 16 + 2 * i + 1] = Mref[1];
+                ml[warp * 16 + 2 * i] = Mc2[0], ml[warp * 16 + 2 * i + 1] = Mc2[1];
                 ml[warp * 16 + 8 + 2 * i] = l[0], ml[warp * 16 + 8 + 2 * i + 1] = l[1];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
@@ -471,8 +485,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 lc[0] += m0 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i] * exp2f(m0 - Mc[0]);
                 lc[1] += m1 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i + 1] * exp2f(m1 - Mc[1]);
             }
-            const float f0 = Mref[0] == -INFINITY ? 0.f : exp2f(Mref[0] - Mc[0]);
-            const float f1 = Mref[1] == -INFINITY ? 0.f : exp2f(Mref[1] - Mc[1]);
+            const float f0 = Mc2[0] == -INFINITY ? 0.f : exp2f(Mc2[0] - Mc[0]);
+            const float f1 = Mc2[1] == -INFINITY ? 0.f : exp2f(Mc2[1] - Mc[1]);
             float *buf = merge + (row_in_pass * kKv + kv) * kFragFloats;
 #pragma unroll 1
             for (int sl = 0; sl < NSLOT; sl++) {
