@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         // split into two halves; and the group sums for the bias term.
         uint32_t qh[4][8], ql[4][8];
         uint32_t qza0 = 0, qza1 = 0;
+        float qoff[4]; // per group: what the code offsets (1024, and 64 for high nibbles) add to q.c
         {
             float qs[4];
             const float *qp = a.q + ((size_t(s.seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
@@ -213,13 +214,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     const float4 v = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
                     x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
                 }
-                float hi[16], lo[16], sum = 0.f;
+                float hi[16], lo[16], sum = 0.f, off = 0.f;
 #pragma unroll
                 for (int d = 0; d < 16; d++) {
                     x[d] *= kLog2e * 0.0625f;
                     hi[d] = __half2float(__float2half_rn(x[d]));
-                    lo[d] = x[d] - hi[d];
+                    lo[d] = __half2float(__float2half_rn(x[d] - hi[d]));
                     sum += x[d];
+                    // 8-bit: every code rides on 1024; 4-bit: even dims (low nibbles) on 1024, odd on 64
+                    off += (hi[d] + lo[d]) * ((BITS == 4 && (d & 1)) ? 64.f : 1024.f);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; j++)
@@ -231,7 +234,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     }
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                off += __shfl_xor_sync(0xffffffffu, off, 1);
+                off += __shfl_xor_sync(0xffffffffu, off, 2);
                 qs[G] = sum;
+                qoff[G] = off;
             }
             // A fragment of the bias-term MMA: row g = high halves of the group sums of head g,
             // row g+8 = low halves; k-slots 0..3 = groups (lanes i < 2 hold two groups each).
@@ -278,6 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     const int tc0 = lt + nt * 8 + 2 * i;       // tokens of this lane's columns
                     const uint2 sK0 = *reinterpret_cast<const uint2 *>(sg + St::kKs + tc0 * St::kParamRow + kv * 8);
                     const uint2 sK1 = *reinterpret_cast<const uint2 *>(sg + St::kKs + (tc0 + 1) * St::kParamRow + kv * 8);
+                    const float2 sKf0[2] = {h2f2(sK0.x), h2f2(sK0.y)}, sKf1[2] = {h2f2(sK1.x), h2f2(sK1.y)};
                     float s_a = 0.f, s_b = 0.f;
 #pragma unroll
                     for (int G = 0; G < 4; G++) {
@@ -287,8 +294,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                             const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
-                                const uint32_t b0 = hsub2_u32(prmt(w[j], kMagic, 0x4140), k1024);
-                                const uint32_t b1 = hsub2_u32(prmt(w[j], kMagic, 0x4342), k1024);
+                                // operands stay 1024 + c; 1024 * sum(q) is taken off the group sum below
+                                const uint32_t b0 = prmt(w[j], kMagic, 0x4140);
+                                const uint32_t b1 = prmt(w[j], kMagic, 0x4342);
                                 mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
                             }
                         } else {
@@ -297,16 +305,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
                             for (int j = 0; j < 4; j++) {
                                 const uint32_t x = w[j >> 1] >> (8 * (j & 1));
-                                const uint32_t b0 = hsub2_u32(lop_and_or(x, 0x000f000fu, k1024), k1024);
-                                const uint32_t b1 = hsub2_u32(lop_and_or(x, 0x00f000f0u, k64), k64);
+                                // low nibbles ride on 1024, high nibbles on 64: (1024, 64) * the matching
+                                // partial sums of q come off below
+                                const uint32_t b0 = lop_and_or(x, 0x000f000fu, k1024);
+                                const uint32_t b1 = lop_and_or(x, 0x00f000f0u, k64);
                                 mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
                             }
                         }
-                        const uint32_t p0 = G < 2 ? sK0.x : sK0.y, p1 = G < 2 ? sK1.x : sK1.y;
-                        const float sc0 = half_bits_to_float((p0 >> (16 * (G & 1))) & 0xffffu);
-                        const float sc1 = half_bits_to_float((p1 >> (16 * (G & 1))) & 0xffffu);
-                        s_a = fmaf(sc0, acc[0] + acc[2], s_a);
-                        s_b = fmaf(sc1, acc[1] + acc[3], s_b);
+                        const float sc0 = G == 0 ? sKf0[0].x : G == 1 ? sKf0[0].y : G == 2 ? sKf0[1].x : sKf0[1].y;
+                        const float sc1 = G == 0 ? sKf1[0].x : G == 1 ? sKf1[0].y : G == 2 ? sKf1[1].x : sKf1[1].y;
+                        s_a = fmaf(sc0, (acc[0] + acc[2]) - qoff[G], s_a);
+                        s_b = fmaf(sc1, (acc[1] + acc[3]) - qoff[G], s_b);
                     }
                     {   // bias term: sum_G z[token][G] * qsum[head][G] (k-slots 0..3 = groups)
                         float accz[4] = {0.f, 0.f, 0.f, 0.f};
@@ -358,17 +367,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     if (tok0 + 2 * i + 8 >= n_row) sV[2] = make_uint2(0u, 0u);
                     if (tok0 + 2 * i + 9 >= n_row) sV[3] = make_uint2(0u, 0u);
                 }
+                // P'[token][head] = P * value scale of (token, group): the two tokens of a pair have
+                // their own scales, gathered into one half2 by a byte permute
+                const uint32_t pu0 = pack_half2(p00, p01), pu1 = pack_half2(p10, p11);
                 uint32_t pbf[4][2];
 #pragma unroll
                 for (int G = 0; G < 4; G++) {
-                    float sc[4];
-#pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        sc[k] = half_bits_to_float(((G < 2 ? sV[k].x : sV[k].y) >> (16 * (G & 1))) & 0xffffu);
-                    pbf[G][0] = pack_half2(p00 * sc[0], p01 * sc[1]);
-                    pbf[G][1] = pack_half2(p10 * sc[2], p11 * sc[3]);
+                    const uint32_t sel = (G & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t s01 = prmt(G < 2 ? sV[0].x : sV[0].y, G < 2 ? sV[1].x : sV[1].y, sel);
+                    const uint32_t s23 = prmt(G < 2 ? sV[2].x : sV[2].y, G < 2 ? sV[3].x : sV[3].y, sel);
+                    pbf[G][0] = hmul2_u32(pu0, s01);
+                    pbf[G][1] = hmul2_u32(pu1, s23);
                 }
-                const uint32_t pu0 = pack_half2(p00, p01), pu1 = pack_half2(p10, p11);
 
                 // ------------------------------------------------ O^T[dim][head] += V^T P^T
                 {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] z[t][G]
