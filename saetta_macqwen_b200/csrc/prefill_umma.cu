@@ -12,15 +12,21 @@
 //  * A tile is 128 query rows = 16 tokens x 8 heads of one kv head (row =
 //    token*8 + head, the reference's GQA packing), so one K/V block feeds all
 //    eight heads.  Persistent CTAs walk the tiles heaviest first.
-//  * Warp 0 streams Q (once per tile) and 64-key K and V blocks into shared
-//    memory with TMA tensor copies (128-byte swizzle, two stages each).
-//  * Warp 1 issues tcgen05.mma: S = Q K^T (128x64x256, f32 in TMEM, two S
-//    buffers) and O += P V (128x256x64, V read MN-major straight from its
+//  * Warp 0 streams 64-key K and V blocks into shared memory with TMA tensor
+//    copies (128-byte swizzle, three stages each).
+//  * Both left-hand operands live in tensor memory, not shared memory: the Q
+//    tile (written once per tile with tcgen05.st) and P (written over the S
+//    columns it was computed from).  Shared-memory traffic per block is then
+//    only the TMA writes and the K / V operand reads, which is what lets the
+//    MMA pipe run near its rate.  TMEM: O 256 columns, Q 128, two S/P buffers of 64.
+//  * Warp 1 issues tcgen05.mma: S = Q K^T (128x64x256, A from TMEM) and
+//    O += P V (128x256x64, A from TMEM, V read MN-major straight from its
 //    [key][dim] rows).  S of block j+1 is issued before P V of block j, so the
-//    tensor pipe works while the softmax warps are busy.
-//  * Warps 2..5 (one TMEM lane = one row per thread) read S with tcgen05.ld, do
-//    the online softmax in log2 units, write P in V's 16-bit type into swizzled shared
-//    memory for the second MMA, and only rescale O in TMEM when the running
+//    tensor pipe works while the softmax warps are busy; the pipe runs MMAs in
+//    issue order, which is what makes reusing an S buffer for P safe.
+//  * Warps 2..5 (one TMEM lane = one row per thread) load their Q row, read S
+//    with tcgen05.ld, do the online softmax in log2 units, write P in V's 16-bit
+//    type back to TMEM, and only rescale O in TMEM when the running
 //    maximum has grown by more than 2^8.  The epilogue divides by l and applies
 //    the sigmoid gate, or leaves (O, m, l) partials for a cross-GPU merge.
 //  * All mbarrier waits are bounded; a wait that gives up sets the status word
@@ -36,17 +42,17 @@ namespace saetta {
 constexpr int kBM = 128;      // rows per tile
 constexpr int kTokTile = 16;  // tokens per tile
 constexpr int kBN = 64;       // keys per block
-constexpr int kQChunk = kBM * 128;  // bytes of one 64-dim slab of the Q tile
 constexpr int kKChunk = kBN * 128;  // bytes of one 64-dim slab of a K or V block
-constexpr int kQBytes = 4 * kQChunk;
 constexpr int kKBytes = 4 * kKChunk;
-constexpr int kPBytes = kBM * kBN * 2;
+constexpr int kPfStages = 3;
 constexpr int kPfThreads = 192;
-constexpr int kPfSmem = kQBytes + 4 * kKBytes + 2 * kPBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kPfSmem = 2 * kPfStages * kKBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kTmemO = 0, kTmemQ = 256, kTmemS = 384; // TMEM columns: O, Q (2 values per column), S/P buffers
 constexpr float kLog2ePf = 1.4426950408889634f;
 constexpr float kPfRescale = 8.0f;
 
 struct PfParams {
+    const void *q; // 16-bit [tokens][heads][256]
     const float *q_and_gate;
     float *out, *part;
     uint32_t *status;
@@ -80,6 +86,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// As tc_mma with the A operand in tensor memory (row m in lane m, two 16-bit values per column).
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -165,29 +179,26 @@ __device__ __forceinline__ bool pf_tile(const PfParams &p, uint32_t round, PfTil
 }
 
 __global__ void __launch_bounds__(kPfThreads, 1)
-prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-               const __grid_constant__ CUtensorMap map_v, const PfParams p) {
+prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+               const PfParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *sQ = smem;
-    uint8_t *sK = sQ + kQBytes;      // [2][kKBytes]
-    uint8_t *sV = sK + 2 * kKBytes;  // [2][kKBytes]
-    uint8_t *sP = sV + 2 * kKBytes;  // [2][kPBytes]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sP + 2 * kPBytes);
-    uint64_t *q_full = bars + 0, *q_empty = bars + 1, *k_full = bars + 2, *k_empty = bars + 4, *v_full = bars + 6,
-             *v_empty = bars + 8, *s_full = bars + 10, *s_empty = bars + 12, *p_full = bars + 14, *p_empty = bars + 16,
-             *o_final = bars + 18, *o_empty = bars + 19;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 20);
+    uint8_t *sK = smem;                        // [kPfStages][kKBytes]
+    uint8_t *sV = sK + kPfStages * kKBytes;    // [kPfStages][kKBytes]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + kPfStages * kKBytes);
+    uint64_t *q_full = bars + 0, *q_empty = bars + 1, *o_final = bars + 2, *o_empty = bars + 3, *k_full = bars + 4,
+             *k_empty = bars + 7, *v_full = bars + 10, *v_empty = bars + 13, *s_full = bars + 16, *p_full = bars + 18,
+             *pv_done = bars + 20;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 22);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     volatile uint32_t *never_set = tmem_slot + 2; // stays 0: for waits that must ignore the abort flag
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 4);
-        for (int s = 0; s < 2; s++) {
+        mbar_init(q_full, 4), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 4);
+        for (int s = 0; s < kPfStages; s++)
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1), mbar_init(&s_empty[s], 4), mbar_init(&p_full[s], 4), mbar_init(&p_empty[s], 1);
-        }
+        for (int s = 0; s < 2; s++) mbar_init(&s_full[s], 1), mbar_init(&p_full[s], 4), mbar_init(&pv_done[s], 1);
         *abort_flag = 0;
         *never_set = 0;
         mbar_fence_init();
@@ -200,7 +211,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_o = tmem, tmem_s = tmem + 256;
+    const uint32_t tmem_o = tmem + kTmemO, tmem_q = tmem + kTmemQ, tmem_s = tmem + kTmemS;
 
     auto give_up = [&](uint32_t bit) {
         atomicOr(p.status, bit);
@@ -215,11 +226,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             PfTile t;
             for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
                 if (!t.nb) continue;
-                if (!mbar_wait(q_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); break; }
-                mbar_expect_tx(q_full, kQBytes);
-                for (int c = 0; c < 4; c++) tma_load_4d(sQ + c * kQChunk, &map_q, q_full, c * 64, 0, int(t.kv), int(t.tok0));
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
-                    const uint32_t st = g & 1, ph = (g >> 1) & 1;
+                    const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1;
                     const int key0 = int((t.b_begin + b) * kBN);
                     if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
                     mbar_expect_tx(&k_full[st], kKBytes);
@@ -233,9 +241,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // On the way out after a failed wait, let the copies already issued land
             // (bounded) so that no copy is in flight when the CTA's shared memory is released.
             if (*abort_flag)
-                for (uint32_t k = g > 2 ? g - 2 : 0; k < g; k++) {
-                    mbar_wait(&k_full[k & 1], (k >> 1) & 1, never_set, 200000u);
-                    mbar_wait(&v_full[k & 1], (k >> 1) & 1, never_set, 200000u);
+                for (uint32_t k = g > kPfStages ? g - kPfStages : 0; k < g; k++) {
+                    mbar_wait(&k_full[k % kPfStages], (k / kPfStages) & 1, never_set, 200000u);
+                    mbar_wait(&v_full[k % kPfStages], (k / kPfStages) & 1, never_set, 200000u);
                 }
         }
     } else if (warp == 1) {
@@ -243,23 +251,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (lane == 0) {
             const uint32_t idesc_s = (1u << 4) | (p.fmt << 7) | (p.fmt << 10) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
             const uint32_t idesc_o = (1u << 4) | (p.v_fmt << 7) | (p.v_fmt << 10) | (1u << 16) | (uint32_t(kDim >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP);
+            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
             uint32_t g = 0, tc = 0;
             bool ok = true;
             PfTile t;
             auto issue_s = [&](uint32_t gg) -> bool { // S[gg&1] = Q K^T for the block with running index gg
-                const uint32_t st = gg & 1, ph = (gg >> 1) & 1;
+                const uint32_t st = gg % kPfStages, ph = (gg / kPfStages) & 1, sb = gg & 1;
                 { PF_T0(); if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); return false; } PF_ADD(0); }
-                { PF_T0(); if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; } PF_ADD(1); }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kDim / 16; ks++) {
-                    const uint64_t ad = umma_desc(q_addr + (ks >> 2) * kQChunk + (ks & 3) * 32, 16, 1024);
                     const uint64_t bd = umma_desc(k_addr + st * kKBytes + (ks >> 2) * kKChunk + (ks & 3) * 32, 16, 1024);
-                    tc_mma(tmem_s + st * kBN, ad, bd, idesc_s, ks > 0);
+                    tc_mma_ts(tmem_s + sb * kBN, tmem_q + ks * 8, bd, idesc_s, ks > 0);
                 }
                 tc_commit(&k_empty[st]);
-                tc_commit(&s_full[st]);
+                tc_commit(&s_full[sb]);
                 return true;
             };
             for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
@@ -272,21 +278,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     } else {
                         tc_commit(q_empty); // every S of this tile has been issued
                     }
-                    const uint32_t gg = g + b, st = gg & 1, ph = (gg >> 1) & 1;
-                    { PF_T0(); if (!mbar_wait(&p_full[st], ph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(2); }
+                    const uint32_t gg = g + b, st = gg % kPfStages, ph = (gg / kPfStages) & 1, sb = gg & 1, sph = (gg >> 1) & 1;
+                    { PF_T0(); if (!mbar_wait(&p_full[sb], sph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(2); }
                     { PF_T0(); if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } PF_ADD(3); }
                     if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kBN / 16; ks++) {
-                        const uint64_t ad = umma_desc(p_addr + st * kPBytes + ks * 32, 16, 1024);
                         // V is MN-major: 64 dims (128 B) x 8 keys per swizzle atom; next 64 dims one slab on
                         // (leading offset), next 8 keys 1024 B on (stride offset); 16 keys per MMA.
                         const uint64_t bd = umma_desc(v_addr + st * kKBytes + ks * 2048, kKChunk, 1024);
-                        tc_mma(tmem_o, ad, bd, idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
+                        tc_mma_ts(tmem_o, tmem_s + sb * kBN + ks * 8, bd, idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
                     }
                     tc_commit(&v_empty[st]);
-                    tc_commit(&p_empty[st]);
+                    tc_commit(&pv_done[sb]);
                     if (b + 1 == t.nb) tc_commit(o_final);
                 }
                 g += t.nb;
@@ -313,6 +318,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 continue;
             }
             const uint32_t lim_hi = min(p.key_hi, p.pos + tok + 1); // keys [key_lo, lim_hi) are visible
+            {   // this thread's Q row into tensor memory (two values per column), once the MMAs
+                // of the tile before no longer read the old one
+                if (!mbar_wait(q_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                tc_fence_after();
+                const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim);
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t w[32];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const uint4 v = row_live ? qrow[c * 8 + k] : make_uint4(0u, 0u, 0u, 0u);
+                        w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
+                    }
+                    tmem_st32(tmem_q + lane_addr + c * 32, w);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(q_full);
+            }
             float m_ref = -INFINITY, l = 0.f;
             for (uint32_t b = 0; ok && b < t.nb; b++, g++) {
                 const uint32_t st = g & 1, ph = (g >> 1) & 1;
@@ -325,9 +350,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 tmem_ld32(tmem_s + lane_addr + st * kBN + 32, sr[1]);
                 tmem_wait_ld();
                 if (quarter == 0) { PF_ADD(5); }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&s_empty[st]);
 
                 // raw scores; the positive scale (in log2 units) is folded into the exponent's FFMA
                 float s[64];
@@ -354,7 +376,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (b > 0 && __any_sync(0xffffffffu, need)) {
                     // P V of the block before must have landed in O before O is touched
                     const uint32_t gp = g - 1;
-                    if (!mbar_wait(&p_empty[gp & 1], (gp >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    if (!mbar_wait(&pv_done[gp & 1], (gp >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < kDim; c += 32) {
@@ -370,30 +392,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
                 if (quarter == 0) { PF_ADD(6); } // from the first tmem load to here: S read + max + any rescale
-                if (!mbar_wait(&p_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                 if (quarter == 0) { PF_ADD(7); }
-                uint8_t *prow = sP + st * kPBytes + row * 128;
+                // P over the first 32 columns of the S buffer it came from (two values per column)
+                uint32_t pw[32];
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int c8 = 0; c8 < 8; c8++) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const float a = ex2_approx(fmaf(s[c8 * 8 + 2 * k], p.scale_log2, -m_use));
-                        const float bb = ex2_approx(fmaf(s[c8 * 8 + 2 * k + 1], p.scale_log2, -m_use));
-                        sum4[k] += a + bb;
-                        if (p.v_fmt) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(a, bb);
-                            w[k] = *reinterpret_cast<uint32_t *>(&h);
-                        } else {
-                            w[k] = pack_half2(a, bb);
-                        }
+                for (int k = 0; k < 32; k++) {
+                    const float a = ex2_approx(fmaf(s[2 * k], p.scale_log2, -m_use));
+                    const float bb = ex2_approx(fmaf(s[2 * k + 1], p.scale_log2, -m_use));
+                    sum4[k & 3] += a + bb;
+                    if (p.v_fmt) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(a, bb);
+                        pw[k] = *reinterpret_cast<uint32_t *>(&h);
+                    } else {
+                        pw[k] = pack_half2(a, bb);
                     }
-                    *reinterpret_cast<uint4 *>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                tmem_st32(tmem_s + lane_addr + st * kBN, pw);
+                tmem_wait_st();
                 const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                 l += sum;
-                fence_async_smem();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_full[st]);
@@ -481,15 +499,7 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
     if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15)
         return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q, keys and values must be 16-byte aligned");
     const CUtensorMapDataType dt = a.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap mq, mk, mv;
-    {
-        const cuuint64_t dims[4] = {cuuint64_t(kDim), cuuint64_t(kHeadsPerKv), a.kv_heads, a.tokens};
-        const cuuint64_t strides[3] = {kDim * 2, cuuint64_t(kHeadsPerKv) * kDim * 2, cuuint64_t(a.heads) * kDim * 2};
-        const cuuint32_t box[4] = {64, kHeadsPerKv, 1, kTokTile}, el[4] = {1, 1, 1, 1};
-        CUresult r = enc(&mq, dt, 4, const_cast<void *>(a.q), dims, strides, box, el, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for q rejected");
-    }
+    CUtensorMap mk, mv;
     const cuuint64_t keys_total = cuuint64_t(a.pos) + a.tokens;
     const CUtensorMapDataType dtv = a.v_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     for (int side = 0; side < 2; side++) {
@@ -501,13 +511,13 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the cache rejected");
     }
-    PfParams p{a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
+    PfParams p{a.q, a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
                a.scale * kLog2ePf, a.dtype == SAETTA_BF16 ? 1u : 0u, a.v_dtype == SAETTA_BF16 ? 1u : 0u};
     int dev = 0;
     SAETTA_CUDA(cudaGetDevice(&dev));
     const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads;
     const uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count(dev)));
-    prefill_kernel<<<grid, kPfThreads, kPfSmem, stream>>>(mq, mk, mv, p);
+    prefill_kernel<<<grid, kPfThreads, kPfSmem, stream>>>(mk, mv, p);
     SAETTA_CUDA(cudaGetLastError());
     return SAETTA_OK;
 }
