@@ -774,6 +774,7 @@ void saetta_att_gemm_destroy(saetta_att_gemm *op) {
     DeviceGuard guard(op->device);
     cudaFree(op->stage_k);
     cudaFree(op->stage_v);
+    cudaFree(op->split_parts);
     cudaFree(op->status);
     delete op;
 }
@@ -835,6 +836,22 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     }
     PrefillArgs a{q, keys, values, dtype, v_dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
                   uint32_t(key_lo), uint32_t(key_hi), p.scale};
+    // Long context: every tile has about the same work, and tiles rarely divide evenly over
+    // the SMs.  Cut each tile's keys into two work items (twice as many, half as long) and merge
+    // their (m, l, O); the merge is a few tens of microseconds against milliseconds of MMA.
+    constexpr uint32_t kSplits = 2;
+    if (out && key_hi - key_lo >= 16384) {
+        const size_t need = size_t(kSplits) * p.tokens * p.heads * kPartStride;
+        if (need > op->split_floats) {
+            cudaFree(op->split_parts);
+            op->split_parts = nullptr, op->split_floats = 0;
+            if (int rc = alloc_zero((void **)&op->split_parts, need * sizeof(float))) return rc;
+            op->split_floats = need;
+        }
+        a.out = nullptr, a.part = op->split_parts, a.splits = kSplits;
+        if (int rc = launch_prefill(a, op->status, st)) return rc;
+        return launch_merge_logical(op->split_parts, kSplits, p.tokens, p.heads, q_and_gate, out, nullptr, st);
+    }
     return launch_prefill(a, op->status, st);
 }
 

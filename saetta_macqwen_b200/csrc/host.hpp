@@ -74,6 +74,8 @@ struct saetta_att_gemm {
     size_t chunk = 0, kv_heads = 0;
     void *stage_k = nullptr, *stage_v = nullptr; // 16-bit copy of a quantised cache
     size_t stage_tokens = 0;
+    float *split_parts = nullptr; // partials of the key splits of a long-context chunk
+    size_t split_floats = 0;
     uint32_t *status = nullptr;
 };
 
@@ -156,6 +158,8 @@ struct PrefillArgs {
     uint32_t heads, kv_heads, pos, tokens;
     uint32_t key_lo, key_hi; // keys considered (clipped by causality)
     float scale;
+    uint32_t splits = 1;     // > 1: each tile's keys are cut into `splits` work items, each leaving a
+                             // partial in part + split * tokens*heads*kPartStride (out must be null)
 };
 int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream);
 int prefill_configure(int device);

@@ -60,6 +60,8 @@ struct PfParams {
     float scale_log2;
     uint32_t fmt;   // of Q and K: 0 binary16, 1 bfloat16 (also the UMMA format code)
     uint32_t v_fmt; // of V, and therefore of P (both operands of one MMA must share a format)
+    uint32_t splits;      // each tile's key range is cut into this many work items (>1: partials per split)
+    uint32_t part_stride; // floats between the partial buffers of consecutive splits
 };
 
 // ----------------------------------------------------------------- PTX wrappers
@@ -159,22 +161,28 @@ __device__ unsigned long long pf_trace[160][16];
 #endif
 
 struct PfTile {
-    uint32_t tok0, kv, b_begin, nb;
+    uint32_t tok0, kv, b_begin, nb, split;
 };
 
+// Work item `round` of this CTA: (token tile, kv head, key split), heaviest tiles first, snaking
+// over the CTAs so that every CTA gets a similar mix.
 __device__ __forceinline__ bool pf_tile(const PfParams &p, uint32_t round, PfTile &t) {
     const uint32_t tok_tiles = (p.tokens + kTokTile - 1) / kTokTile;
-    const uint32_t ntiles = tok_tiles * p.kv_heads;
+    const uint32_t per_tok_tile = p.kv_heads * p.splits;
+    const uint32_t nitems = tok_tiles * per_tok_tile;
     const uint32_t G = gridDim.x, c = blockIdx.x;
-    const uint32_t n = round * G + ((round & 1) ? G - 1 - c : c); // heaviest first, snaking
-    if (n >= ntiles) return false;
-    const uint32_t tt = tok_tiles - 1 - n / p.kv_heads;
-    t.kv = n % p.kv_heads;
+    const uint32_t n = round * G + ((round & 1) ? G - 1 - c : c);
+    if (n >= nitems) return false;
+    const uint32_t tt = tok_tiles - 1 - n / per_tok_tile, rem = n % per_tok_tile;
+    t.kv = rem / p.splits;
+    t.split = rem % p.splits;
     t.tok0 = tt * kTokTile;
     const uint32_t hi = min(p.key_hi, p.pos + t.tok0 + kTokTile);
-    t.b_begin = p.key_lo / kBN;
-    const uint32_t b_end = hi > p.key_lo ? (hi + kBN - 1) / kBN : t.b_begin;
-    t.nb = b_end - t.b_begin;
+    const uint32_t b0 = p.key_lo / kBN;
+    const uint32_t b1 = hi > p.key_lo ? (hi + kBN - 1) / kBN : b0;
+    const uint32_t nb = b1 - b0;
+    t.b_begin = b0 + uint32_t(uint64_t(nb) * t.split / p.splits);
+    t.nb = b0 + uint32_t(uint64_t(nb) * (t.split + 1) / p.splits) - t.b_begin;
     return true;
 }
 
@@ -309,9 +317,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const uint32_t tok = t.tok0 + (row >> 3), head = t.kv * kHeadsPerKv + (row & 7);
             const bool row_live = tok < p.tokens;
             const size_t rh = size_t(tok) * p.heads + head;
+            float *part = p.part ? p.part + size_t(t.split) * p.part_stride : nullptr;
             if (!t.nb) { // no key of the range is visible to this tile: an empty partial
-                if (row_live && p.part) {
-                    float *dst = p.part + rh * kPartStride;
+                if (row_live && part) {
+                    float *dst = part + rh * kPartStride;
                     for (int d = 0; d < kDim; d++) dst[d] = 0.f;
                     dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
                 }
@@ -444,16 +453,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                         op[k] = r;
                     }
                 } else {
-                    float4 *op = reinterpret_cast<float4 *>(p.part + rh * kPartStride + c);
+                    float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
 #pragma unroll
                     for (int k = 0; k < 8; k++)
                         op[k] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
                                             __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
                 }
             }
-            if (row_live && p.part) {
-                p.part[rh * kPartStride + kPartM] = m_ref;
-                p.part[rh * kPartStride + kPartL] = l;
+            if (row_live && part) {
+                part[rh * kPartStride + kPartM] = m_ref;
+                part[rh * kPartStride + kPartL] = l;
             }
             tc_fence_before();
             __syncwarp();
@@ -512,10 +521,11 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
         if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the cache rejected");
     }
     PfParams p{a.q, a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
-               a.scale * kLog2ePf, a.dtype == SAETTA_BF16 ? 1u : 0u, a.v_dtype == SAETTA_BF16 ? 1u : 0u};
+               a.scale * kLog2ePf, a.dtype == SAETTA_BF16 ? 1u : 0u, a.v_dtype == SAETTA_BF16 ? 1u : 0u,
+               a.splits ? a.splits : 1u, uint32_t(size_t(a.tokens) * a.heads * kPartStride)};
     int dev = 0;
     SAETTA_CUDA(cudaGetDevice(&dev));
-    const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads;
+    const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads * (a.splits ? a.splits : 1u);
     const uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count(dev)));
     prefill_kernel<<<grid, kPfThreads, kPfSmem, stream>>>(mk, mv, p);
     SAETTA_CUDA(cudaGetLastError());

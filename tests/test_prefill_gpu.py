@@ -120,6 +120,17 @@ def test_split_key_partials_merge_to_the_whole(oracle):
     assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3
 
 
+def test_long_context_chunk_uses_key_splits(oracle):
+    """Past 16384 keys each tile's key range is cut into two work items whose
+    partials are merged; the result must still be the oracle's."""
+    import torch
+
+    pos, tokens = 17000, 40
+    q, k, v, qg = bf16_inputs(oracle, pos, tokens, 500)
+    got = run(torch, q, k, v, qg, pos, tokens, sa.BF16)
+    check_rows(oracle, got, q, qg, k, v, pos, np.array([0, 1, 7, 15, 16, 17, 31, 32, 39]))
+
+
 def test_shape_errors(oracle):
     import torch
 
