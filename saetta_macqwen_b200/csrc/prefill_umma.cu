@@ -98,6 +98,7 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -327,17 +328,42 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 continue;
             }
             const uint32_t lim_hi = min(p.key_hi, p.pos + tok + 1); // keys [key_lo, lim_hi) are visible
+            // Pull what the end of this tile and the start of the next will read towards L2 now:
+            // this row's gate values (epilogue) and the same row of the next tile's Q.
+            if (row_live && p.out) {
+                const char *gp = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim);
+#pragma unroll
+                for (int k = 0; k < 8; k++) prefetch_l2(gp + k * 128);
+            }
+            {
+                PfTile nx;
+                if (pf_tile(p, round + 1, nx) && nx.nb && nx.tok0 + (row >> 3) < p.tokens) {
+                    const size_t nrh = size_t(nx.tok0 + (row >> 3)) * p.heads + nx.kv * kHeadsPerKv + (row & 7);
+                    const char *qp = reinterpret_cast<const char *>(p.q) + nrh * kDim * 2;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) prefetch_l2(qp + k * 128);
+                }
+            }
             {   // this thread's Q row into tensor memory (two values per column), once the MMAs
                 // of the tile before no longer read the old one
+                PF_T0();
                 if (!mbar_wait(q_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                 tc_fence_after();
                 const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim);
-#pragma unroll 1
+                // loads of the next 64 values are issued before the store of the current ones
+                uint4 qv[2][8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) qv[0][k] = row_live ? qrow[k] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
                 for (int c = 0; c < 4; c++) {
+                    if (c + 1 < 4) {
+#pragma unroll
+                        for (int k = 0; k < 8; k++) qv[(c + 1) & 1][k] = row_live ? qrow[(c + 1) * 8 + k] : make_uint4(0u, 0u, 0u, 0u);
+                    }
                     uint32_t w[32];
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
-                        const uint4 v = row_live ? qrow[c * 8 + k] : make_uint4(0u, 0u, 0u, 0u);
+                        const uint4 v = qv[c & 1][k];
                         w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
                     }
                     tmem_st32(tmem_q + lane_addr + c * 32, w);
@@ -346,6 +372,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(q_full);
+                if (quarter == 0) { PF_ADD(11); }
             }
             float m_ref = -INFINITY, l = 0.f;
             for (uint32_t b = 0; ok && b < t.nb; b++, g++) {
@@ -428,36 +455,52 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             }
             if (!ok) break;
             // ---------------- epilogue of the tile
+            // The gate values do not depend on O: the first quarter is requested before O is
+            // final, and each later quarter one step ahead of its use (two register buffers).
+            const bool gated = row_live && p.out;
+            const float4 *gp = reinterpret_cast<const float4 *>(p.q_and_gate + (gated ? rh * 2 * kDim + kDim : 0));
+            float4 gq[2][16];
+            if (gated) {
+#pragma unroll
+                for (int k = 0; k < 16; k++) gq[0][k] = gp[k];
+            }
             PF_T0();
             if (!mbar_wait(o_final, tc & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
             if (quarter == 0) { PF_ADD(9); }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll 1
-            for (int c = 0; c < kDim; c += 32) {
-                uint32_t o[32];
-                tmem_ld32(tmem_o + lane_addr + c, o);
-                tmem_wait_ld();
-                if (!row_live) continue;
-                if (p.out) {
-                    const float4 *gp = reinterpret_cast<const float4 *>(p.q_and_gate + rh * 2 * kDim + kDim + c);
-                    float4 *op = reinterpret_cast<float4 *>(p.out + rh * kDim + c);
 #pragma unroll
-                    for (int k = 0; k < 8; k++) {
-                        const float4 gt = gp[k];
-                        float4 r;
-                        r.x = __uint_as_float(o[4 * k]) * __fdividef(inv_l, 1.f + __expf(-gt.x));
-                        r.y = __uint_as_float(o[4 * k + 1]) * __fdividef(inv_l, 1.f + __expf(-gt.y));
-                        r.z = __uint_as_float(o[4 * k + 2]) * __fdividef(inv_l, 1.f + __expf(-gt.z));
-                        r.w = __uint_as_float(o[4 * k + 3]) * __fdividef(inv_l, 1.f + __expf(-gt.w));
-                        op[k] = r;
+            for (int qt = 0; qt < 4; qt++) {
+                if (gated && qt + 1 < 4) {
+#pragma unroll
+                    for (int k = 0; k < 16; k++) gq[(qt + 1) & 1][k] = gp[(qt + 1) * 16 + k];
+                }
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) {
+                    const int c = qt * 64 + cc * 32;
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_addr + c, o);
+                    tmem_wait_ld();
+                    if (!row_live) continue;
+                    if (p.out) {
+                        float4 *op = reinterpret_cast<float4 *>(p.out + rh * kDim + c);
+#pragma unroll
+                        for (int k = 0; k < 8; k++) {
+                            const float4 gt = gq[qt & 1][cc * 8 + k];
+                            float4 r;
+                            r.x = __uint_as_float(o[4 * k]) * __fdividef(inv_l, 1.f + __expf(-gt.x));
+                            r.y = __uint_as_float(o[4 * k + 1]) * __fdividef(inv_l, 1.f + __expf(-gt.y));
+                            r.z = __uint_as_float(o[4 * k + 2]) * __fdividef(inv_l, 1.f + __expf(-gt.z));
+                            r.w = __uint_as_float(o[4 * k + 3]) * __fdividef(inv_l, 1.f + __expf(-gt.w));
+                            op[k] = r;
+                        }
+                    } else {
+                        float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
+#pragma unroll
+                        for (int k = 0; k < 8; k++)
+                            op[k] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
+                                                __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
                     }
-                } else {
-                    float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
-#pragma unroll
-                    for (int k = 0; k < 8; k++)
-                        op[k] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
-                                            __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
                 }
             }
             if (row_live && part) {
