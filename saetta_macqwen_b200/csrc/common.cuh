@@ -53,8 +53,29 @@ struct DeviceGuard {
 
 int sm_count(int device);
 
+// Launch with programmatic dependent launch allowed: the grid may be scheduled while the kernel
+// before it in the stream is still draining; the kernel itself calls pdl_wait() before it touches
+// anything its predecessor may have written.  With a predecessor that never signals, this is an
+// ordinary stream-ordered launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #ifdef __CUDACC__
 // ----------------------------------------------------------------- PTX helpers
+
+// Programmatic dependent launch: wait until the grids this one depends on have completed and
+// their writes are visible; allow the grids that depend on this one to be scheduled.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -62,6 +62,14 @@ constexpr int smem_bytes() {
            2 * Stage<BITS>::kStages * 8 + 16;
 }
 
+#ifdef SAETTA_DQ_TRACE
+__device__ unsigned long long dq_trace[160][8][8]; // [cta][warp][event] global timer ns
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define DQ_MARK(ev) if (lane == 0 && warp < 8) dq_trace[blockIdx.x][warp][ev] = gtime()
+#else
+#define DQ_MARK(ev)
+#endif
+
 struct DecodeArgs {
     Segment seg;               // the one segment of a single-sequence launch (tiles filled on device)
     const Segment *segs;       // batched: descriptors, else null
@@ -102,6 +110,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + NS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    DQ_MARK(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; s++) {
             mbar_init(&full[s], 1);
@@ -112,6 +121,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();              // q, the token parameters and the cache may come from the kernel before
+    pdl_launch_dependents(); // the merge kernel may be scheduled as SMs free up; it waits for this grid
+    DQ_MARK(5);
 
     // The segments this CTA runs.
     uint32_t seg_lo = 0, seg_hi = 1;
@@ -247,6 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             qza1 = i < 2 ? pack_half2(s0 - h0, s1 - h1) : 0u;
         }
 
+        DQ_MARK(1);
         float O[16][4];
         float Ob[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -263,6 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 alive = false;
                 break;
             }
+            if (t == s.tile_begin) { DQ_MARK(2); }
             const uint8_t *sg = stages + st * St::kBytes;
 #pragma unroll 1
             for (int sub = 0; sub < kTile / kSub; sub++) {
@@ -444,6 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         }
 
         // ---------------------------------------------------------------- end of segment
+        DQ_MARK(3);
         // l of head g over the four lanes that share it; then every lane takes m and l of the
         // heads of its accumulator columns (2i, 2i+1) from lanes g = 2i and g = 2i+1.
         lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
@@ -497,6 +512,34 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             }
             const float f0 = Mc2[0] == -INFINITY ? 0.f : exp2f(Mc2[0] - Mc[0]);
             const float f1 = Mc2[1] == -INFINITY ? 0.f : exp2f(Mc2[1] - Mc[1]);
+            if (!a.segs) {
+                // One segment per launch: after the barrier above no warp reads the copy ring any
+                // more, so every warp parks its scaled accumulators in the ring at once; then each
+                // warp adds up its share of the elements in slot order (fixed, hence deterministic).
+                float *mine = reinterpret_cast<float *>(stages) + warp * kFragFloats;
+#pragma unroll
+                for (int e = 0; e < 16; e++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) mine[(4 * e + c) * 32 + lane] = O[e][c] * ((c & 1) ? f1 : f0);
+                asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                if (row_live) {
+                    constexpr int per = 64 / NSLOT;
+#pragma unroll
+                    for (int r = 0; r < per; r++) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int sl = 0; sl < NSLOT; sl++) {
+                            const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
+                            v += reinterpret_cast<const float *>(stages)[w * kFragFloats + (slot * per + r) * 32 + lane];
+                        }
+                        dst[(slot * per + r) * 32 + lane] = v;
+                    }
+                    if (slot == 0 && g == 0) {
+                        dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
+                        dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+                    }
+                }
+            } else {
             float *buf = merge + (row_in_pass * kKv + kv) * kFragFloats;
 #pragma unroll 1
             for (int sl = 0; sl < NSLOT; sl++) {
@@ -521,15 +564,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
                 }
             }
+            }
             asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // merge buffers free again
         }
+        DQ_MARK(4);
     }
 }
 
 template <int BITS, int ROWS>
 static int launch_one(const DecodeArgs &a, dim3 grid, cudaStream_t stream) {
-    decode_quant_kernel<BITS, ROWS><<<grid, kThreads, smem_bytes<BITS>(), stream>>>(a);
-    SAETTA_CUDA(cudaGetLastError());
+    SAETTA_CUDA(launch_pdl(decode_quant_kernel<BITS, ROWS>, grid, dim3(kThreads), smem_bytes<BITS>(), stream, a));
     return SAETTA_OK;
 }
 
@@ -630,3 +674,9 @@ int decode_quant_static(int device, const KvView &kv, size_t capacity, const flo
 }
 
 } // namespace saetta
+
+#ifdef SAETTA_DQ_TRACE
+extern "C" int saetta_debug_decode_trace(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, saetta::dq_trace, sizeof(saetta::dq_trace));
+}
+#endif

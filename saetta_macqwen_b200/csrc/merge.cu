@@ -34,6 +34,8 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
     __shared__ float M_s[8], L_s[8];
     __shared__ float red[kMergeGroups][kMergeElems];
     const uint32_t row = blockIdx.y / kv_heads, kv = blockIdx.y % kv_heads;
+    pdl_wait(); // the partials come from the kernel before
+    pdl_launch_dependents();
     uint32_t p0 = 0, p1 = nparts;
     if (first_part) {
         p0 = first_part[row];
@@ -126,9 +128,9 @@ int launch_merge_frag(const float *parts, uint32_t nparts, const uint32_t *first
                       uint32_t rows, uint32_t kv_heads, const float *q_and_gate, float *out,
                       float *part_out, cudaStream_t stream) {
     if (!rows) return SAETTA_OK;
-    merge_frag_kernel<<<dim3(kFragFloats / kMergeElems, rows * kv_heads), kMergeGroups * kMergeElems, 0, stream>>>(
-        parts, nparts, first_part, rows, kv_heads, q_and_gate, out, part_out);
-    SAETTA_CUDA(cudaGetLastError());
+    SAETTA_CUDA(launch_pdl(merge_frag_kernel, dim3(kFragFloats / kMergeElems, rows * kv_heads),
+                           dim3(kMergeGroups * kMergeElems), 0, stream, parts, nparts, first_part, rows, kv_heads,
+                           q_and_gate, out, part_out));
     return SAETTA_OK;
 }
 
