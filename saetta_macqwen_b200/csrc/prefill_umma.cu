@@ -19,16 +19,20 @@
 //    columns it was computed from).  Shared-memory traffic per block is then
 //    only the TMA writes and the K / V operand reads, which is what lets the
 //    MMA pipe run near its rate.  TMEM: O 256 columns, Q 128, two S/P buffers of 64.
-//  * Warp 1 issues tcgen05.mma: S = Q K^T (128x64x256, A from TMEM) and
-//    O += P V (128x256x64, A from TMEM, V read MN-major straight from its
-//    [key][dim] rows).  S of block j+1 is issued before P V of block j, so the
-//    tensor pipe works while the softmax warps are busy; the pipe runs MMAs in
-//    issue order, which is what makes reusing an S buffer for P safe.
-//  * Warps 2..5 (one TMEM lane = one row per thread) load their Q row, read S
-//    with tcgen05.ld, do the online softmax in log2 units, write P in V's 16-bit
-//    type back to TMEM, and only rescale O in TMEM when the running
-//    maximum has grown by more than 2^8.  The epilogue divides by l and applies
-//    the sigmoid gate, or leaves (O, m, l) partials for a cross-GPU merge.
+//  * Two threads issue tcgen05.mma, because one thread needs longer to issue a
+//    block's 20 instructions than the tensor pipe needs to run them: warp 1
+//    issues S = Q K^T (128x64x256, A from TMEM), up to two blocks ahead, and
+//    warp 10 issues O += P V (128x256x64, A from TMEM, V read MN-major straight
+//    from its [key][dim] rows).  An S buffer is reused for block j+2 once the
+//    P V product of block j has completed.
+//  * Warps 2..5 (one TMEM lane = one row per thread) read S with tcgen05.ld, do
+//    the online softmax in log2 units, write P in V's 16-bit type back to TMEM,
+//    and only rescale O in TMEM when the running maximum has grown by more than
+//    2^8.  Warps 6..9 move tiles in and out: the Q rows of the next tile into
+//    TMEM as soon as the last S of the current one is done, then the current
+//    tile's epilogue, so a tile change does not stall the MMAs.  The epilogue divides by l and applies
+//    the sigmoid gate, or leaves (O, m, l) partials for a merge (across GPUs, or across the
+//    two key halves a long-context tile is cut into).
 //  * All mbarrier waits are bounded; a wait that gives up sets the status word
 //    and the CTA-wide abort flag, every role leaves its loop, and TMEM is freed.
 #include <cuda.h>
@@ -45,8 +49,8 @@ constexpr int kBN = 64;       // keys per block
 constexpr int kKChunk = kBN * 128;  // bytes of one 64-dim slab of a K or V block
 constexpr int kKBytes = 4 * kKChunk;
 constexpr int kPfStages = 3;
-constexpr int kPfThreads = 192;
-constexpr int kPfSmem = 2 * kPfStages * kKBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kPfThreads = 352; // TMA warp, S-MMA warp, 4 softmax warps, 4 tile I/O warps, P V-MMA warp
+constexpr int kPfSmem = 2 * kPfStages * kKBytes + 1024 /*align*/ + 256 /*barriers*/ + 2 * 2 * kBM * 4 /*l, m per row, two tiles*/;
 constexpr int kTmemO = 0, kTmemQ = 256, kTmemS = 384; // TMEM columns: O, Q (2 values per column), S/P buffers
 constexpr float kLog2ePf = 1.4426950408889634f;
 constexpr float kPfRescale = 8.0f;
@@ -197,8 +201,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     uint64_t *bars = reinterpret_cast<uint64_t *>(sV + kPfStages * kKBytes);
     uint64_t *q_full = bars + 0, *q_empty = bars + 1, *o_final = bars + 2, *o_empty = bars + 3, *k_full = bars + 4,
              *k_empty = bars + 7, *v_full = bars + 10, *v_empty = bars + 13, *s_full = bars + 16, *p_full = bars + 18,
-             *pv_done = bars + 20;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 22);
+             *pv_done = bars + 20, *lm_full = bars + 22;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 24);
+    float *row_l = reinterpret_cast<float *>(bars + 32); // [2][128] row sums handed from the softmax warps
+    float *row_m = row_l + 2 * kBM;                      // [2][128] running maxima (log2 units)
     volatile uint32_t *abort_flag = tmem_slot + 1;
     volatile uint32_t *never_set = tmem_slot + 2; // stays 0: for waits that must ignore the abort flag
 
@@ -207,7 +213,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         mbar_init(q_full, 4), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 4);
         for (int s = 0; s < kPfStages; s++)
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
-        for (int s = 0; s < 2; s++) mbar_init(&s_full[s], 1), mbar_init(&p_full[s], 4), mbar_init(&pv_done[s], 1);
+        for (int s = 0; s < 2; s++)
+            mbar_init(&s_full[s], 1), mbar_init(&p_full[s], 4), mbar_init(&pv_done[s], 1), mbar_init(&lm_full[s], 4);
         *abort_flag = 0;
         *never_set = 0;
         mbar_fence_init();
@@ -256,124 +263,81 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------ MMA issuer for S = Q K^T
+        // Two threads issue MMAs, this one the score products and warp 10 the P V products: one
+        // thread alone spends longer issuing the 20 instructions of a block than the tensor
+        // pipe needs to run them.  An S buffer is reused two blocks later, once the P V product
+        // that read P out of it has completed (pv_done).
         if (lane == 0) {
             const uint32_t idesc_s = (1u << 4) | (p.fmt << 7) | (p.fmt << 10) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
-            const uint32_t idesc_o = (1u << 4) | (p.v_fmt << 7) | (p.v_fmt << 10) | (1u << 16) | (uint32_t(kDim >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
-            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+            const uint32_t k_addr = smem_u32(sK);
             uint32_t g = 0, tc = 0;
             bool ok = true;
             PfTile t;
-            auto issue_s = [&](uint32_t gg) -> bool { // S[gg&1] = Q K^T for the block with running index gg
-                const uint32_t st = gg % kPfStages, ph = (gg / kPfStages) & 1, sb = gg & 1;
-                { PF_T0(); if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); return false; } PF_ADD(0); }
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < kDim / 16; ks++) {
-                    const uint64_t bd = umma_desc(k_addr + st * kKBytes + (ks >> 2) * kKChunk + (ks & 3) * 32, 16, 1024);
-                    tc_mma_ts(tmem_s + sb * kBN, tmem_q + ks * 8, bd, idesc_s, ks > 0);
-                }
-                tc_commit(&k_empty[st]);
-                tc_commit(&s_full[sb]);
-                return true;
-            };
             for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
                 if (!t.nb) continue;
-                if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; }
-                if (!(ok = issue_s(g))) break;
-                for (uint32_t b = 0; b < t.nb; b++) {
-                    if (b + 1 < t.nb) {
-                        if (!(ok = issue_s(g + b + 1))) break;
-                    } else {
-                        tc_commit(q_empty); // every S of this tile has been issued
+                { PF_T0(); if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; } PF_ADD(12); }
+                for (uint32_t b = 0; b < t.nb; b++, g++) {
+                    const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1, sb = g & 1;
+                    { PF_T0(); if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } PF_ADD(0); }
+                    { PF_T0(); if (!mbar_wait(&pv_done[sb], ((g >> 1) & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(1); }
+                    tc_fence_after();
+                    const uint64_t bd0 = umma_desc(k_addr + st * kKBytes, 16, 1024);
+#pragma unroll
+                    for (int ks = 0; ks < kDim / 16; ks++) {
+                        // the descriptor's address field counts 16-byte units: +2 per 16-value k-step
+                        // inside a 64-value slab, one slab further every fourth step
+                        const uint64_t bd = bd0 + uint64_t(((ks >> 2) * kKChunk + (ks & 3) * 32) >> 4);
+                        tc_mma_ts(tmem_s + sb * kBN, tmem_q + ks * 8, bd, idesc_s, ks > 0);
                     }
-                    const uint32_t gg = g + b, st = gg % kPfStages, ph = (gg / kPfStages) & 1, sb = gg & 1, sph = (gg >> 1) & 1;
+                    tc_commit(&k_empty[st]);
+                    tc_commit(&s_full[sb]);
+                }
+                if (!ok) break;
+                tc_commit(q_empty); // every S of this tile has been issued
+                tc++;
+            }
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------ MMA issuer for O += P V
+        if (lane == 0) {
+            const uint32_t idesc_o = (1u << 4) | (p.v_fmt << 7) | (p.v_fmt << 10) | (1u << 16) | (uint32_t(kDim >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+            const uint32_t v_addr = smem_u32(sV);
+            uint32_t g = 0, tc = 0;
+            bool ok = true;
+            PfTile t;
+            for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                if (!t.nb) continue;
+                for (uint32_t b = 0; b < t.nb; b++, g++) {
+                    const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1, sb = g & 1, sph = (g >> 1) & 1;
                     { PF_T0(); if (!mbar_wait(&p_full[sb], sph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(2); }
                     { PF_T0(); if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } PF_ADD(3); }
-                    if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    { PF_T0(); if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(13); }
                     tc_fence_after();
+                    // V is MN-major: 64 dims (128 B) x 8 keys per swizzle atom; next 64 dims one slab on
+                    // (leading offset), next 8 keys 1024 B on (stride offset); 16 keys per MMA.
+                    const uint64_t bd0 = umma_desc(v_addr + st * kKBytes, kKChunk, 1024);
 #pragma unroll
-                    for (int ks = 0; ks < kBN / 16; ks++) {
-                        // V is MN-major: 64 dims (128 B) x 8 keys per swizzle atom; next 64 dims one slab on
-                        // (leading offset), next 8 keys 1024 B on (stride offset); 16 keys per MMA.
-                        const uint64_t bd = umma_desc(v_addr + st * kKBytes + ks * 2048, kKChunk, 1024);
-                        tc_mma_ts(tmem_o, tmem_s + sb * kBN + ks * 8, bd, idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
-                    }
+                    for (int ks = 0; ks < kBN / 16; ks++)
+                        tc_mma_ts(tmem_o, tmem_s + sb * kBN + ks * 8, bd0 + uint64_t((ks * 2048) >> 4), idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
                     tc_commit(&v_empty[st]);
                     tc_commit(&pv_done[sb]);
                     if (b + 1 == t.nb) tc_commit(o_final);
                 }
-                g += t.nb;
                 tc++;
             }
         }
-    } else {
-        // ------------------------------------------------------------ softmax, correction, epilogue
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ softmax and correction
         const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
         uint32_t g = 0, tc = 0;
         bool ok = true;
         PfTile t;
         for (uint32_t round = 0; pf_tile(p, round, t); round++) {
-            const uint32_t tok = t.tok0 + (row >> 3), head = t.kv * kHeadsPerKv + (row & 7);
-            const bool row_live = tok < p.tokens;
-            const size_t rh = size_t(tok) * p.heads + head;
-            float *part = p.part ? p.part + size_t(t.split) * p.part_stride : nullptr;
-            if (!t.nb) { // no key of the range is visible to this tile: an empty partial
-                if (row_live && part) {
-                    float *dst = part + rh * kPartStride;
-                    for (int d = 0; d < kDim; d++) dst[d] = 0.f;
-                    dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
-                }
-                continue;
-            }
+            if (!t.nb) continue;
+            const uint32_t tok = t.tok0 + (row >> 3);
             const uint32_t lim_hi = min(p.key_hi, p.pos + tok + 1); // keys [key_lo, lim_hi) are visible
-            // Pull what the end of this tile and the start of the next will read towards L2 now:
-            // this row's gate values (epilogue) and the same row of the next tile's Q.
-            if (row_live && p.out) {
-                const char *gp = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim);
-#pragma unroll
-                for (int k = 0; k < 8; k++) prefetch_l2(gp + k * 128);
-            }
-            {
-                PfTile nx;
-                if (pf_tile(p, round + 1, nx) && nx.nb && nx.tok0 + (row >> 3) < p.tokens) {
-                    const size_t nrh = size_t(nx.tok0 + (row >> 3)) * p.heads + nx.kv * kHeadsPerKv + (row & 7);
-                    const char *qp = reinterpret_cast<const char *>(p.q) + nrh * kDim * 2;
-#pragma unroll
-                    for (int k = 0; k < 4; k++) prefetch_l2(qp + k * 128);
-                }
-            }
-            {   // this thread's Q row into tensor memory (two values per column), once the MMAs
-                // of the tile before no longer read the old one
-                PF_T0();
-                if (!mbar_wait(q_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
-                tc_fence_after();
-                const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim);
-                // loads of the next 64 values are issued before the store of the current ones
-                uint4 qv[2][8];
-#pragma unroll
-                for (int k = 0; k < 8; k++) qv[0][k] = row_live ? qrow[k] : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    if (c + 1 < 4) {
-#pragma unroll
-                        for (int k = 0; k < 8; k++) qv[(c + 1) & 1][k] = row_live ? qrow[(c + 1) * 8 + k] : make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    uint32_t w[32];
-#pragma unroll
-                    for (int k = 0; k < 8; k++) {
-                        const uint4 v = qv[c & 1][k];
-                        w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
-                    }
-                    tmem_st32(tmem_q + lane_addr + c * 32, w);
-                }
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(q_full);
-                if (quarter == 0) { PF_ADD(11); }
-            }
             float m_ref = -INFINITY, l = 0.f;
             for (uint32_t b = 0; ok && b < t.nb; b++, g++) {
                 const uint32_t st = g & 1, ph = (g >> 1) & 1;
@@ -454,53 +418,139 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 if (quarter == 0) { PF_ADD(8); }
             }
             if (!ok) break;
-            // ---------------- epilogue of the tile
-            // The gate values do not depend on O: the first quarter is requested before O is
-            // final, and each later quarter one step ahead of its use (two register buffers).
+            // hand the row's sum and maximum to the tile I/O warps and go on to the next tile
+            row_l[(tc & 1) * kBM + row] = l;
+            row_m[(tc & 1) * kBM + row] = m_ref;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&lm_full[tc & 1]);
+            tc++;
+        }
+    } else if (warp < 10) {
+        // ------------------------------------------------------------ tile I/O: Q rows in, results out
+        // Per tile these warps write its Q rows into tensor memory and, at its end, scale and gate
+        // O out to memory.  The Q rows of tile k+1 go in as soon as the last S of tile k has been
+        // computed, before tile k's epilogue, so the MMA warp never waits for a tile change.
+        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        struct RowOf {
+            uint32_t tok;
+            bool live;
+            size_t rh;
+            float *part;
+        };
+        auto row_of = [&](const PfTile &t) {
+            RowOf r;
+            r.tok = t.tok0 + (row >> 3);
+            r.live = r.tok < p.tokens;
+            r.rh = size_t(r.tok) * p.heads + t.kv * kHeadsPerKv + (row & 7);
+            r.part = p.part ? p.part + size_t(t.split) * p.part_stride : nullptr;
+            return r;
+        };
+        // next work item with keys to visit; items without any get their empty partial here
+        auto next_item = [&](uint32_t &round, PfTile &t) -> bool {
+            while (pf_tile(p, round, t)) {
+                round++;
+                if (t.nb) return true;
+                const RowOf r = row_of(t);
+                if (r.live && r.part) {
+                    float *dst = r.part + r.rh * kPartStride;
+                    for (int d = 0; d < kDim; d++) dst[d] = 0.f;
+                    dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
+                }
+            }
+            return false;
+        };
+        auto load_q = [&](const PfTile &t, uint32_t k) -> bool {
+            const RowOf r = row_of(t);
+            const bool row_live = r.live;
+            const size_t rh = r.rh;
+            if (row_live && p.out) { // pull this row's gate values towards L2 for the epilogue
+                const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim);
+#pragma unroll
+                for (int j = 0; j < 8; j++) prefetch_l2(gpf + j * 128);
+            }
+            {   // this thread's Q row into tensor memory (two values per column), once the MMAs
+                // of the tile before no longer read the old one
+                PF_T0();
+                if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+                tc_fence_after();
+                const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim);
+                // loads of the next 64 values are issued before the store of the current ones
+                uint4 qv[2][8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) qv[0][k] = row_live ? qrow[k] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    if (c + 1 < 4) {
+#pragma unroll
+                        for (int k = 0; k < 8; k++) qv[(c + 1) & 1][k] = row_live ? qrow[(c + 1) * 8 + k] : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    uint32_t w[32];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const uint4 v = qv[c & 1][k];
+                        w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
+                    }
+                    tmem_st32(tmem_q + lane_addr + c * 32, w);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(q_full);
+                if (quarter == 0) { PF_ADD(11); }
+            }
+            return true;
+        };
+        auto epilogue = [&](const PfTile &t, uint32_t k) -> bool {
+            const RowOf r = row_of(t);
+            const bool row_live = r.live;
+            const size_t rh = r.rh;
+            float *part = r.part;
+            // The gate values do not depend on O: the first 32 are requested before O is final,
+            // and each later chunk one step ahead of its use (two register buffers).
             const bool gated = row_live && p.out;
             const float4 *gp = reinterpret_cast<const float4 *>(p.q_and_gate + (gated ? rh * 2 * kDim + kDim : 0));
-            float4 gq[2][16];
+            float4 gq[2][8];
             if (gated) {
 #pragma unroll
-                for (int k = 0; k < 16; k++) gq[0][k] = gp[k];
+                for (int j = 0; j < 8; j++) gq[0][j] = gp[j];
             }
             PF_T0();
-            if (!mbar_wait(o_final, tc & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+            if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+            const float l = row_l[(k & 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
+            if (!mbar_wait(o_final, k & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             if (quarter == 0) { PF_ADD(9); }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-            for (int qt = 0; qt < 4; qt++) {
-                if (gated && qt + 1 < 4) {
+            for (int ch = 0; ch < 8; ch++) {
+                if (gated && ch + 1 < 8) {
 #pragma unroll
-                    for (int k = 0; k < 16; k++) gq[(qt + 1) & 1][k] = gp[(qt + 1) * 16 + k];
+                    for (int j = 0; j < 8; j++) gq[(ch + 1) & 1][j] = gp[(ch + 1) * 8 + j];
                 }
+                const int c = ch * 32;
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_addr + c, o);
+                tmem_wait_ld();
+                if (!row_live) continue;
+                if (p.out) {
+                    float4 *op = reinterpret_cast<float4 *>(p.out + rh * kDim + c);
 #pragma unroll
-                for (int cc = 0; cc < 2; cc++) {
-                    const int c = qt * 64 + cc * 32;
-                    uint32_t o[32];
-                    tmem_ld32(tmem_o + lane_addr + c, o);
-                    tmem_wait_ld();
-                    if (!row_live) continue;
-                    if (p.out) {
-                        float4 *op = reinterpret_cast<float4 *>(p.out + rh * kDim + c);
-#pragma unroll
-                        for (int k = 0; k < 8; k++) {
-                            const float4 gt = gq[qt & 1][cc * 8 + k];
-                            float4 r;
-                            r.x = __uint_as_float(o[4 * k]) * __fdividef(inv_l, 1.f + __expf(-gt.x));
-                            r.y = __uint_as_float(o[4 * k + 1]) * __fdividef(inv_l, 1.f + __expf(-gt.y));
-                            r.z = __uint_as_float(o[4 * k + 2]) * __fdividef(inv_l, 1.f + __expf(-gt.z));
-                            r.w = __uint_as_float(o[4 * k + 3]) * __fdividef(inv_l, 1.f + __expf(-gt.w));
-                            op[k] = r;
-                        }
-                    } else {
-                        float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
-#pragma unroll
-                        for (int k = 0; k < 8; k++)
-                            op[k] = make_float4(__uint_as_float(o[4 * k]), __uint_as_float(o[4 * k + 1]),
-                                                __uint_as_float(o[4 * k + 2]), __uint_as_float(o[4 * k + 3]));
+                    for (int j = 0; j < 8; j++) {
+                        const float4 gt = gq[ch & 1][j];
+                        float4 v;
+                        v.x = __uint_as_float(o[4 * j]) * __fdividef(inv_l, 1.f + __expf(-gt.x));
+                        v.y = __uint_as_float(o[4 * j + 1]) * __fdividef(inv_l, 1.f + __expf(-gt.y));
+                        v.z = __uint_as_float(o[4 * j + 2]) * __fdividef(inv_l, 1.f + __expf(-gt.z));
+                        v.w = __uint_as_float(o[4 * j + 3]) * __fdividef(inv_l, 1.f + __expf(-gt.w));
+                        op[j] = v;
                     }
+                } else {
+                    float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        op[j] = make_float4(__uint_as_float(o[4 * j]), __uint_as_float(o[4 * j + 1]),
+                                            __uint_as_float(o[4 * j + 2]), __uint_as_float(o[4 * j + 3]));
                 }
             }
             if (row_live && part) {
@@ -511,7 +561,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(o_empty);
             if (quarter == 0) { PF_ADD(10); }
-            tc++;
+            return true;
+        };
+        uint32_t round = 0, k = 0;
+        PfTile cur, nxt;
+        bool have = next_item(round, cur);
+        if (have && !load_q(cur, 0)) have = false;
+        while (have) {
+            const bool more = next_item(round, nxt);
+            if (more && !load_q(nxt, k + 1)) break;
+            if (!epilogue(cur, k)) break;
+            cur = nxt, have = more, k++;
         }
     }
 
