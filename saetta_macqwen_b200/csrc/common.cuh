@@ -166,6 +166,10 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     __half2 r = __hmul2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
     return *reinterpret_cast<uint32_t *>(&r);
 }
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    __half2 r = __hfma2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b), *reinterpret_cast<__half2 *>(&c));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
 __device__ __forceinline__ float2 h2f2(uint32_t a) { return __half22float2(*reinterpret_cast<__half2 *>(&a)); }
 __device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));

@@ -203,6 +203,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
     const bool row_live = row < a.m;
     const int g = lane >> 2, i = lane & 3;
     constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
+    // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128
+    // (8 for 4-bit).  For zero-mean values the two terms then no longer cancel, so the 16-bit
+    // rounding of P costs 3x less relative error.  1152 = 0x6480, 1032 = 0x6408, 72 = 0x5480.
+    constexpr uint32_t k1152 = 0x64806480u, k1032 = 0x64086408u, k72 = 0x54805480u;
+    constexpr float kVCentre = BITS == 8 ? 128.f : 8.f;
 
     uint32_t it = 0;
     bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
@@ -385,18 +390,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 // their own scales, gathered into one half2 by a byte permute
                 const uint32_t pu0 = pack_half2(p00, p01), pu1 = pack_half2(p10, p11);
                 uint32_t pbf[4][2];
+                {
+                    float2 sf[4][2]; // [token of the lane's four][groups 0,1 | 2,3]
 #pragma unroll
-                for (int G = 0; G < 4; G++) {
-                    const uint32_t sel = (G & 1) ? 0x7632u : 0x5410u;
-                    const uint32_t s01 = prmt(G < 2 ? sV[0].x : sV[0].y, G < 2 ? sV[1].x : sV[1].y, sel);
-                    const uint32_t s23 = prmt(G < 2 ? sV[2].x : sV[2].y, G < 2 ? sV[3].x : sV[3].y, sel);
-                    pbf[G][0] = hmul2_u32(pu0, s01);
-                    pbf[G][1] = hmul2_u32(pu1, s23);
+                    for (int k = 0; k < 4; k++) sf[k][0] = h2f2(sV[k].x), sf[k][1] = h2f2(sV[k].y);
+#pragma unroll
+                    for (int G = 0; G < 4; G++) {
+                        const float a = (G & 1) ? sf[0][G >> 1].y : sf[0][G >> 1].x, b = (G & 1) ? sf[1][G >> 1].y : sf[1][G >> 1].x;
+                        const float c = (G & 1) ? sf[2][G >> 1].y : sf[2][G >> 1].x, d = (G & 1) ? sf[3][G >> 1].y : sf[3][G >> 1].x;
+                        pbf[G][0] = pack_half2(p00 * a, p01 * b); // f32 product, one rounding
+                        pbf[G][1] = pack_half2(p10 * c, p11 * d);
+                    }
                 }
 
                 // ------------------------------------------------ O^T[dim][head] += V^T P^T
-                {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] z[t][G]
-                    const uint8_t *vz = sg + St::kVz + kv * 8 + (g & 3) * 2;
+                {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] (z + C s)[t][G]
+                    const int gq = g & 3;
+                    const uint8_t *vz = sg + St::kVz + kv * 8 + gq * 2;
                     uint32_t z0 = *reinterpret_cast<const uint16_t *>(vz + T0 * St::kParamRow);
                     uint32_t z1 = *reinterpret_cast<const uint16_t *>(vz + T1 * St::kParamRow);
                     uint32_t z2 = *reinterpret_cast<const uint16_t *>(vz + T2 * St::kParamRow);
@@ -407,7 +417,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                         if (tok0 + 2 * i + 8 >= n_row) z2 = 0;
                         if (tok0 + 2 * i + 9 >= n_row) z3 = 0;
                     }
-                    const uint32_t a0 = g < 4 ? (z0 | z1 << 16) : 0u, a2 = g < 4 ? (z2 | z3 << 16) : 0u;
+                    // this lane's group is gq: its scales sit in half gq of the pairs gathered above
+                    const uint32_t sel = (gq & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t s01 = prmt(gq < 2 ? sV[0].x : sV[0].y, gq < 2 ? sV[1].x : sV[1].y, sel);
+                    const uint32_t s23 = prmt(gq < 2 ? sV[2].x : sV[2].y, gq < 2 ? sV[3].x : sV[3].y, sel);
+                    const uint32_t cc = pack_half2(kVCentre, kVCentre);
+                    const uint32_t a0 = g < 4 ? hfma2_u32(s01, cc, z0 | z1 << 16) : 0u;
+                    const uint32_t a2 = g < 4 ? hfma2_u32(s23, cc, z2 | z3 << 16) : 0u;
                     mma_f16(Ob, a0, 0u, a2, 0u, pu0, pu1);
                 }
                 const uint8_t *vc = sg + St::kV + kv * (kDim * BITS / 8);
@@ -426,10 +442,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const uint32_t sel = (e & 1) ? 0x4342u : 0x4140u;
-                            const uint32_t a0 = hsub2_u32(prmt(x01[e >> 1], kMagic, sel), k1024);
-                            const uint32_t a1 = hsub2_u32(prmt(u01[e >> 1], kMagic, sel), k1024);
-                            const uint32_t a2 = hsub2_u32(prmt(x23[e >> 1], kMagic, sel), k1024);
-                            const uint32_t a3 = hsub2_u32(prmt(u23[e >> 1], kMagic, sel), k1024);
+                            // 1024 + c minus 1152: the centred code c - 128 (see kVCentre)
+                            const uint32_t a0 = hsub2_u32(prmt(x01[e >> 1], kMagic, sel), k1152);
+                            const uint32_t a1 = hsub2_u32(prmt(u01[e >> 1], kMagic, sel), k1152);
+                            const uint32_t a2 = hsub2_u32(prmt(x23[e >> 1], kMagic, sel), k1152);
+                            const uint32_t a3 = hsub2_u32(prmt(u23[e >> 1], kMagic, sel), k1152);
                             mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
                         }
                     } else {
@@ -444,10 +461,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                         for (int e = 0; e < 4; e++) {
                             const int sh = 8 * (e >> 1);
                             const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
-                            const uint32_t a0 = hsub2_u32(lop_and_or(x01 >> sh, mask, mg), mg);
-                            const uint32_t a1 = hsub2_u32(lop_and_or(u01 >> sh, mask, mg), mg);
-                            const uint32_t a2 = hsub2_u32(lop_and_or(x23 >> sh, mask, mg), mg);
-                            const uint32_t a3 = hsub2_u32(lop_and_or(u23 >> sh, mask, mg), mg);
+                            const uint32_t ctr = (e & 1) ? k72 : k1032; // magic + 8: the centred code n - 8
+                            const uint32_t a0 = hsub2_u32(lop_and_or(x01 >> sh, mask, mg), ctr);
+                            const uint32_t a1 = hsub2_u32(lop_and_or(u01 >> sh, mask, mg), ctr);
+                            const uint32_t a2 = hsub2_u32(lop_and_or(x23 >> sh, mask, mg), ctr);
+                            const uint32_t a3 = hsub2_u32(lop_and_or(u23 >> sh, mask, mg), ctr);
                             mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
                         }
                     }

@@ -200,6 +200,46 @@ def test_batched_ragged_decode(oracle, bits):
         assert max_abs(got[i], want[0]) < 2e-3 and rel_rms(got[i], want[0]) < 1e-3, (bits, i, L)
 
 
+def test_config5_ragged_batch_of_64_long_sequences(oracle):
+    """64 sequences with lengths U[8192, 262144], 8-bit cache, one launch; the
+    oracle checks the shortest, the longest and two others (the rest are checked
+    for being finite)."""
+    import torch
+
+    rng = np.random.default_rng(5)
+    lens = rng.integers(8192, 262145, 64)
+    picked = sorted({int(np.argmin(lens)), int(np.argmax(lens)), 7, 40})
+    g = torch.Generator(device="cuda")
+    g.manual_seed(9)
+    caches, refs = [], {}
+    for i, L in enumerate(lens):
+        L = int(L)
+        c = sa.GpuKvCache(0, 8, L)
+        for p0 in range(0, L, 32768):
+            n = min(32768, L - p0)
+            k = torch.randn(n * ROW, device="cuda", generator=g)
+            v = torch.randn(n * ROW, device="cuda", generator=g)
+            c.store_at(k, v, p0, n)
+            if i in picked:
+                kk, vv = refs.setdefault(i, ([], []))
+                kk.append(oracle.round_trip(k.cpu().numpy(), 8))
+                vv.append(oracle.round_trip(v.cpu().numpy(), 8))
+        caches.append(c)
+    n = len(lens)
+    q = oracle.normal(n * HEADS * DIM, 50)
+    qg = oracle.normal(n * HEADS * 2 * DIM, 51)
+    op = sa.DecodeBatch(0, 64)
+    out = torch.zeros(n * HEADS * DIM, dtype=torch.float32, device="cuda")
+    op.record(caches, lens, dev(q), dev(qg), out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().reshape(n, HEADS, DIM)
+    assert np.isfinite(got).all()
+    for i in picked:
+        kk, vv = np.concatenate(refs[i][0]), np.concatenate(refs[i][1])
+        want = oracle.attention_rows(q.reshape(n, -1)[i], qg.reshape(n, -1)[i], kk, vv, [int(lens[i])], threads=16)
+        assert max_abs(got[i], want[0]) < 2e-3 and rel_rms(got[i], want[0]) < 1e-3, (i, int(lens[i]))
+
+
 def test_row_backup_and_resize_keep_rows(oracle):
     """src/gpu_cache.rs:234-274 and src/gpu_layers.rs:261-292: rows copied aside
     and put back, and a resize, leave attention results unchanged."""

@@ -140,3 +140,31 @@ def test_shape_errors(oracle):
         op.encode(z, z, z, None, z, z, sa.FlashParams(HEADS, KV, 0, 65, 0.0625))
     with pytest.raises(sa.SaettaError):  # 8 q heads per kv head
         op.encode(z, z, z, None, z, z, sa.FlashParams(12, KV, 0, 8, 0.0625))
+
+
+def test_config4_long_context_chunk_over_8bit_prefix(oracle):
+    """A 4096-token chunk at position 131072 on top of a 131072-token 8-bit cache
+    (the chunk's own rows quantised into the cache first), bf16 queries.  The
+    oracle is evaluated on a sample of rows: first, last, tile edges, a few
+    inside.  Keys are read as the bf16 rounding of s*q+z, values as binary16."""
+    import torch
+
+    pos, tokens, bits = 131072, 4096, 8
+    total = pos + tokens
+    cache = sa.GpuKvCache(0, bits, total)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4)
+    kr = np.empty((total, ROW), np.float32)
+    vr = np.empty((total, ROW), np.float32)
+    for p0 in range(0, total, 16384):  # N(0,1) rows made on the device, kept for the oracle
+        n = min(16384, total - p0)
+        k = torch.randn(n * ROW, device="cuda", generator=g)
+        v = torch.randn(n * ROW, device="cuda", generator=g)
+        cache.store_at(k, v, p0, n)
+        kr[p0:p0 + n] = oracle.round_trip_as_half(k.cpu().numpy(), bits, bf16=True).reshape(n, ROW)
+        vr[p0:p0 + n] = oracle.round_trip_as_half(v.cpu().numpy(), bits).reshape(n, ROW)
+    q = oracle.round_bf16(oracle.normal(tokens * HEADS * DIM, 41))
+    qg = oracle.normal(tokens * HEADS * 2 * DIM, 42)
+    got = run(torch, q, None, None, qg, pos, tokens, sa.BF16, quant=cache.quant())
+    rows = np.array([0, 15, 16, 2047, 2048, 4080, 4095])
+    print("config 4:", check_rows(oracle, got, q, qg, kr.ravel(), vr.ravel(), pos, rows))
