@@ -33,7 +33,7 @@ ROW = KV * DIM
 BYTES_PER_TOKEN = {8: 1088, 4: 576, 16: 2048}  # K + V, both kv heads, codes + scales + biases
 CTX = 262144
 LAYERS = 4
-TRAFFIC_PER_TOKEN = 1141.2  # measured dram bytes per token per layer (ncu), see profiles/
+TRAFFIC_PER_TOKEN = 1122.5  # measured dram bytes per token per layer (ncu), see profiles/
 METRIC = "Decode-attn achieved HBM GB/s @32k/256k KV; prefill-attn TFLOP/s per 4k chunk"
 
 
@@ -292,6 +292,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--points", default="all", help="'none' skips the extra measured points")
     ap.add_argument("--only", default=None, help="run one named point alone (for profiling) and print its result")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: merge kernel reads the peers' partials over NVLink (peer), or NCCL all-gather + merge")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -328,20 +330,32 @@ def main():
     gathered = torch.zeros(world * HEADS * sa.PART_STRIDE, device="cuda")
     launches_per_step = 2 * LAYERS
 
-    if world == 1:
-        def step():
-            for c in caches:
-                op.record_cache(1, q, c, qg, out, params, stream=stream)
-    else:
-        launches_per_step = 3 * LAYERS
+    group = None
+    if world > 1 and args.exchange == "peer":
+        def gather_bytes(b):
+            lst = [None] * world
+            dist.all_gather_object(lst, b)
+            return lst
+        group = sa.PeerGroup(dev, rank, world, 1, HEADS, gather_bytes)
 
-        def step():
-            for c in caches:
-                # the shard that holds the newest row is the last one; here every rank's
-                # shard is full, so every row sees all kv_len keys of the shard
-                op.partial_cache(1, q, c, part, params, row_step=0, stream=stream)
-                dist.all_gather_into_tensor(gathered, part)
-                sa.merge_partials(dev, gathered, world, 1, HEADS, qg, out, stream=stream)
+    def attend(c):
+        """One layer: every rank's shard is full, so every row sees all kv_len keys of the shard."""
+        if world == 1:
+            op.record_cache(1, q, c, qg, out, params, stream=stream)
+        elif group is not None:
+            op.partial_cache(1, q, c, group.staging, params, row_step=0, stream=stream)
+            group.merge(1, qg, out, stream=stream)  # waits for the peers' partials, reads them over NVLink
+        else:
+            op.partial_cache(1, q, c, part, params, row_step=0, stream=stream)
+            dist.all_gather_into_tensor(gathered, part)
+            sa.merge_partials(dev, gathered, world, 1, HEADS, qg, out, stream=stream)
+
+    if world > 1:
+        launches_per_step = (4 if group is not None else 3) * LAYERS
+
+    def step():
+        for c in caches:
+            attend(c)
 
     def barrier():
         if world > 1:
@@ -350,10 +364,11 @@ def main():
 
     sampler = ClockSampler(local)
     with torch.cuda.stream(stream):
-        if world == 1:
+        if world == 1 or group is not None:  # no library collective inside: the step is one CUDA graph
             graph = torch.cuda.CUDAGraph()
             step()
             stream.synchronize()
+            barrier()
             with torch.cuda.graph(graph, stream=stream):
                 step()
             run = graph.replay
@@ -377,6 +392,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     assert op.device_status(stream=stream) == 0, "a bounded device wait gave up"
+    if group is not None:
+        assert group.status(stream=stream) == 0, "a peer never published its partial"
     step_bytes = world * LAYERS * CTX * BYTES_PER_TOKEN[8]
     value = step_bytes / ms / 1e6  # GB/s
 
@@ -398,12 +415,7 @@ def main():
             d_k.copy_(h_k, non_blocking=True)
             d_v.copy_(h_v, non_blocking=True)
             c.store(d_k, d_v, params, rows=1, stream=stream)
-            if world == 1:
-                op.record_cache(1, q, c, qg, out, params, stream=stream)
-            else:
-                op.partial_cache(1, q, c, part, params, row_step=0, stream=stream)
-                dist.all_gather_into_tensor(gathered, part)
-                sa.merge_partials(dev, gathered, world, 1, HEADS, qg, out, stream=stream)
+            attend(c)
             h_out.copy_(out, non_blocking=True)
         stream.synchronize()  # the caller reads the result
 
@@ -468,13 +480,15 @@ def main():
                                    f"{LAYERS} layers with separate caches per step",
                        "layers": LAYERS, "ctx_per_gpu": CTX, "kv_bits": 8, "l2": "inputs larger than L2 "
                        f"({LAYERS * CTX * BYTES_PER_TOKEN[8] / 1e6:.0f} MB per step per GPU)",
-                       "replay": "CUDA graph" if world == 1 else "eager launches + NCCL all-gather of (m,l,O)"},
+                       "replay": "CUDA graph" if (world == 1 or group is not None) else "eager launches",
+                       "exchange": None if world == 1 else ("merge kernel reads the peers' (m,l,O) over NVLink"
+                                                            if group is not None else "NCCL all-gather of (m,l,O) + merge")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "peak_kind": peak_kind + " copy bandwidth",
                          "frac_of_nominal_8TBs": achieved / 8000.0,
                          "kernel": "decode_quant_kernel<8,1> + merge_frag_kernel, per layer",
                          # dram bytes read + written by one launch pair, from the ncu capture at
-                         # 131072 tokens (1141 B per token; profiles/decode_quant_8bit_128k.md), scaled by tokens
+                         # 131072 tokens (1122.5 B per token; profiles/decode_quant_8bit_128k.md), scaled by tokens
                          "traffic": int(CTX * TRAFFIC_PER_TOKEN)},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -106,6 +106,12 @@ SYMBOLS = {
     "saetta_decode_batch_record": (_I, [_P, _Z, _PP, C.POINTER(_U32), _P, _P, _P, _P]),
     "saetta_decode_partial_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P]),
     "saetta_merge_partials": (_I, [_I, _P, _Z, _Z, _Z, _P, _P, _P]),
+    "saetta_peer_group_create": (_I, [_I, _I, _I, _Z, _Z, _P, _PP]),
+    "saetta_peer_group_connect": (_I, [_P, _P]),
+    "saetta_peer_group_destroy": (None, [_P]),
+    "saetta_peer_group_staging": (_P, [_P]),
+    "saetta_peer_merge": (_I, [_P, _Z, _P, _P, _P]),
+    "saetta_peer_group_status": (_I, [_P, _P, C.POINTER(_U32)]),
     "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
     "saetta_att_gemm_destroy": (None, [_P]),
     "saetta_att_gemm_reserve": (_I, [_P, _Z]),
@@ -365,6 +371,39 @@ def merge_partials(device, parts, ranks, rows, heads, q_and_gate, out, stream=No
     """LSE merge of [ranks][rows][heads][PART_STRIDE] partials, then the gate."""
     _check(lib().saetta_merge_partials(device, ptr(parts), ranks, rows, heads, ptr(q_and_gate), ptr(out),
                                        _stream(stream)))
+
+
+class PeerGroup:
+    """Split-KV merge across the GPUs of one box, reading the peers' partials over
+    NVLink (no counterpart in the reference).  `all_gather_bytes(bytes) -> [bytes]`
+    is any host-side all-gather in rank order (torch.distributed works)."""
+
+    def __init__(self, device, rank, world, rows_max, heads, all_gather_bytes):
+        h = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        _check(lib().saetta_peer_group_create(device, rank, world, rows_max, heads, handle, C.byref(h)))
+        self.h = h
+        handles = b"".join(all_gather_bytes(bytes(handle)))
+        assert len(handles) == 64 * world
+        _check(lib().saetta_peer_group_connect(h, handles))
+
+    @property
+    def staging(self):
+        """Device address the partial entry points write this rank's (m, l, O) to."""
+        return lib().saetta_peer_group_staging(self.h)
+
+    def merge(self, rows, q_and_gate, out, stream=None):
+        _check(lib().saetta_peer_merge(self.h, rows, ptr(q_and_gate), ptr(out), _stream(stream)))
+
+    def status(self, stream=None):
+        s = C.c_uint32()
+        _check(lib().saetta_peer_group_status(self.h, _stream(stream), C.byref(s)))
+        return s.value
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_peer_group_destroy(self.h)
+            self.h = None
 
 
 class AttGemm:
