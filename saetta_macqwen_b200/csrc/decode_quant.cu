@@ -11,19 +11,25 @@
 //    ring of shared-memory stages with bulk (TMA engine) copies signalled on
 //    mbarriers, so every cache byte crosses HBM once and many tiles are in
 //    flight per SM.
-//  * Eight consumer warps each own one (kv head, query row) pair and a share of
-//    the 16-token sub-tiles.  Codes go from shared memory to registers with
-//    128/64-bit loads and are turned into binary16 MMA fragments with byte
-//    permutes (code c becomes the half 1024+c, minus 1024: exact).  The eight
-//    query heads of a kv head are the N dimension of mma.sync m16n8k16, so a
-//    code is dequantised once for all of them.
+//  * Eight consumer warps each own one kv head, one query row (decode) or two
+//    (MTP verify), and a share of the 16-token sub-tiles.  Codes go from shared
+//    memory to registers with 128/64-bit loads and are turned into binary16 MMA
+//    fragments with byte permutes (code c becomes the half 1024+c, minus 1024:
+//    exact), so a code is dequantised once for all eight query heads of its kv
+//    head -- and, with several rows, for two rows.
+//  * One row: the score MMA's 16 rows are the heads' query halves (hi, lo: f32
+//    precision), the value MMA is O^T[dim][head] += V^T P^T (16 dims per
+//    instruction).  Two rows: the 16 rows are the two rows' heads in both
+//    products, the value MMA is O[head][dim] += P V (8 dims per instruction),
+//    and the query fragments sit in shared memory to leave registers for the
+//    128 accumulators.  Either way the score fragment's layout is the layout
+//    the value product needs: P never moves between lanes.
 //  * Scores are accumulated per 64-value group and only then multiplied by the
 //    group's scale: x = s*c + z is applied exactly as s*(q.c) + z*sum(q), in f32.
-//    The query is split into two halves (hi + lo) so it keeps f32 precision.
 //  * Online softmax per warp with shuffles; the running maximum is only moved
 //    when it grows by more than 2^8 (the accumulators stay in range and are
-//    rarely rescaled).  P goes to the P.V product through movmatrix, multiplied
-//    by the value scales; the value biases ride along as one more MMA.
+//    rarely rescaled).  P is multiplied by the value scales before the product;
+//    the value biases ride along as one more MMA.
 //  * Every wait on an mbarrier is bounded; a wait that gives up sets a bit in
 //    the status word, raises the CTA's abort flag and the CTA drains and leaves.
 #include <algorithm>
@@ -54,11 +60,15 @@ struct Stage {
     static constexpr int kStages = BITS == 8 ? 5 : 8;
 };
 
-constexpr int kMergeBytes = 2 * kKv * kFragFloats * 4; // up to two rows per pass merge through smem
-constexpr int kMlFloats = kWarps * 4;                  // per warp: m[2] l[2] of its lane quad... see merge
+constexpr int kQFragBytes = 16 * 32 * 16;              // one set of query fragments: [group][k-step][lane] x 128 bit
+constexpr int kQAuxBytes = 4 * 128 * 4;                // per set: code-offset terms and sums [row][group][head]
+// One area with two users: the segment merge of batched one-row launches (one buffer per kv head),
+// or the query fragments of row-pair launches (up to four sets).
+constexpr int kMergeBytes = 4 * kQFragBytes;
+static_assert(kMergeBytes >= kKv * kFragFloats * 4, "merge buffers fit");
 template <int BITS>
 constexpr int smem_bytes() {
-    return Stage<BITS>::kStages * Stage<BITS>::kBytes + kMergeBytes + kWarps * 8 * 2 * 4 +
+    return Stage<BITS>::kStages * Stage<BITS>::kBytes + kMergeBytes + kQAuxBytes + kWarps * 2 * 16 * 4 +
            2 * Stage<BITS>::kStages * 8 + 16;
 }
 
@@ -100,12 +110,12 @@ template <int BITS, int ROWS>
 __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeArgs a) {
     using St = Stage<BITS>;
     constexpr int NS = St::kStages;
-    constexpr int NSLOT = kWarps / (kKv * ROWS); // warps sharing one (kv, row)
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *stages = smem;
     float *merge = reinterpret_cast<float *>(smem + NS * St::kBytes);
-    float *ml = merge + kMergeBytes / 4; // [warp][8 heads][m, l]
-    uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 16);
+    float *qsums = merge + kMergeBytes / 4;
+    float *ml = qsums + kQAuxBytes / 4; // [warp][row of the warp][m of 8 heads, l of 8 heads]
+    uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
     uint64_t *empty = full + NS;
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + NS);
 
@@ -196,396 +206,815 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
     asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
 
     // -------------------------------------------------------------------- consumers
-    const int kv = warp & 1;
-    const int row_in_pass = (warp >> 1) % ROWS;
-    const int slot = (warp >> 1) / ROWS;
-    const uint32_t row = row0 + row_in_pass;
-    const bool row_live = row < a.m;
-    const int g = lane >> 2, i = lane & 3;
-    constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
-    // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128
-    // (8 for 4-bit).  For zero-mean values the two terms then no longer cancel, so the 16-bit
-    // rounding of P costs 3x less relative error.  1152 = 0x6480, 1032 = 0x6408, 72 = 0x5480.
-    constexpr uint32_t k1152 = 0x64806480u, k1032 = 0x64086408u, k72 = 0x54805480u;
-    constexpr float kVCentre = BITS == 8 ? 128.f : 8.f;
+    if constexpr (ROWS == 1) {
+        constexpr int NSLOT = kWarps / kKv; // warps sharing one kv head
+        const int kv = warp & 1;
+        const int row_in_pass = (warp >> 1) % ROWS;
+        const int slot = (warp >> 1) / ROWS;
+        const uint32_t row = row0 + row_in_pass;
+        const bool row_live = row < a.m;
+        const int g = lane >> 2, i = lane & 3;
+        constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
+        // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128
+        // (8 for 4-bit).  For zero-mean values the two terms then no longer cancel, so the 16-bit
+        // rounding of P costs 3x less relative error.  1152 = 0x6480, 1032 = 0x6408, 72 = 0x5480.
+        constexpr uint32_t k1152 = 0x64806480u, k1032 = 0x64086408u, k72 = 0x54805480u;
+        constexpr float kVCentre = BITS == 8 ? 128.f : 8.f;
 
-    uint32_t it = 0;
-    bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
-    for (uint32_t si = seg_lo; si < seg_hi; si++) {
-        const Segment s = load_segment(si);
-        const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
+        uint32_t it = 0;
+        bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
+        for (uint32_t si = seg_lo; si < seg_hi; si++) {
+            const Segment s = load_segment(si);
+            const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
 
-        // Query fragments of head kv*8+g: 16 dims per group, scaled by log2(e)/16,
-        // split into two halves; and the group sums for the bias term.
-        uint32_t qh[4][8], ql[4][8];
-        uint32_t qza0 = 0, qza1 = 0;
-        float qoff[4]; // per group: what the code offsets (1024, and 64 for high nibbles) add to q.c
-        {
-            float qs[4];
-            const float *qp = a.q + ((size_t(s.seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
-#pragma unroll
-            for (int G = 0; G < 4; G++) {
-                float x[16];
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const float4 v = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
-                    x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
-                }
-                float hi[16], lo[16], sum = 0.f, off = 0.f;
-#pragma unroll
-                for (int d = 0; d < 16; d++) {
-                    x[d] *= kLog2e * 0.0625f;
-                    hi[d] = __half2float(__float2half_rn(x[d]));
-                    lo[d] = __half2float(__float2half_rn(x[d] - hi[d]));
-                    sum += x[d];
-                    // 8-bit: every code rides on 1024; 4-bit: even dims (low nibbles) on 1024, odd on 64
-                    off += (hi[d] + lo[d]) * ((BITS == 4 && (d & 1)) ? 64.f : 1024.f);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; j++)
-#pragma unroll
-                    for (int r = 0; r < 2; r++) {
-                        const int d0 = q_dim<BITS>(j, r, 0), d1 = q_dim<BITS>(j, r, 1);
-                        qh[G][2 * j + r] = pack_half2(hi[d0], hi[d1]);
-                        ql[G][2 * j + r] = pack_half2(lo[d0], lo[d1]);
-                    }
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                off += __shfl_xor_sync(0xffffffffu, off, 1);
-                off += __shfl_xor_sync(0xffffffffu, off, 2);
-                qs[G] = sum;
-                qoff[G] = off;
-            }
-            // A fragment of the bias-term MMA: row g = high halves of the group sums of head g,
-            // row g+8 = low halves; k-slots 0..3 = groups (lanes i < 2 hold two groups each).
-            const float s0 = i == 0 ? qs[0] : qs[2], s1 = i == 0 ? qs[1] : qs[3];
-            const float h0 = __half2float(__float2half_rn(s0)), h1 = __half2float(__float2half_rn(s1));
-            qza0 = i < 2 ? pack_half2(h0, h1) : 0u;
-            qza1 = i < 2 ? pack_half2(s0 - h0, s1 - h1) : 0u;
-        }
-
-        DQ_MARK(1);
-        float O[16][4];
-        float Ob[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int e = 0; e < 16; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
-        float Mref = -INFINITY, lsum = 0.f; // of head g (this thread's row of the score MMA)
-
-        for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
-            const uint32_t st = it % NS, round = it / NS;
-            if (!mbar_wait(&full[st], round & 1, abort_flag)) {
-                if (lane == 0) {
-                    atomicOr(a.status, kStatusFullTimeout);
-                    *abort_flag = 1;
-                }
-                alive = false;
-                break;
-            }
-            if (t == s.tile_begin) { DQ_MARK(2); }
-            const uint8_t *sg = stages + st * St::kBytes;
-#pragma unroll 1
-            for (int sub = 0; sub < kTile / kSub; sub++) {
-                const uint32_t q_idx = 2 * (t - s.tile_begin) + sub;
-                const uint32_t tok0 = t * kTile + sub * kSub; // first token of the sub-tile
-                if (!row_live || (q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_row) continue;
-                const bool partial = tok0 + kSub > n_row;
-                const int lt = sub * kSub; // token offset inside the stage
-
-                // ------------------------------------------------ scores S[head][token]
-                // MMA rows 0..7 = high halves of the 8 query heads, rows 8..15 = their low halves;
-                // columns = 8 tokens.  Lane (g, i) feeds token g of each 8-token tile and owns
-                // head g at tokens 2i, 2i+1.
-                float S[2][2];
-                const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
-#pragma unroll
-                for (int nt = 0; nt < 2; nt++) {
-                    const int trow = lt + nt * 8 + g;          // token this lane loads
-                    const int tc0 = lt + nt * 8 + 2 * i;       // tokens of this lane's columns
-                    const uint2 sK0 = *reinterpret_cast<const uint2 *>(sg + St::kKs + tc0 * St::kParamRow + kv * 8);
-                    const uint2 sK1 = *reinterpret_cast<const uint2 *>(sg + St::kKs + (tc0 + 1) * St::kParamRow + kv * 8);
-                    const float2 sKf0[2] = {h2f2(sK0.x), h2f2(sK0.y)}, sKf1[2] = {h2f2(sK1.x), h2f2(sK1.y)};
-                    float s_a = 0.f, s_b = 0.f;
-#pragma unroll
-                    for (int G = 0; G < 4; G++) {
-                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (BITS == 8) {
-                            const uint4 r = *reinterpret_cast<const uint4 *>(kc + trow * St::kCodeRow + G * 64 + i * 16);
-                            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                // operands stay 1024 + c; 1024 * sum(q) is taken off the group sum below
-                                const uint32_t b0 = prmt(w[j], kMagic, 0x4140);
-                                const uint32_t b1 = prmt(w[j], kMagic, 0x4342);
-                                mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
-                            }
-                        } else {
-                            const uint2 r = *reinterpret_cast<const uint2 *>(kc + trow * St::kCodeRow + G * 32 + i * 8);
-                            const uint32_t w[2] = {r.x, r.y};
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                const uint32_t x = w[j >> 1] >> (8 * (j & 1));
-                                // low nibbles ride on 1024, high nibbles on 64: (1024, 64) * the matching
-                                // partial sums of q come off below
-                                const uint32_t b0 = lop_and_or(x, 0x000f000fu, k1024);
-                                const uint32_t b1 = lop_and_or(x, 0x00f000f0u, k64);
-                                mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
-                            }
-                        }
-                        const float sc0 = G == 0 ? sKf0[0].x : G == 1 ? sKf0[0].y : G == 2 ? sKf0[1].x : sKf0[1].y;
-                        const float sc1 = G == 0 ? sKf1[0].x : G == 1 ? sKf1[0].y : G == 2 ? sKf1[1].x : sKf1[1].y;
-                        s_a = fmaf(sc0, (acc[0] + acc[2]) - qoff[G], s_a);
-                        s_b = fmaf(sc1, (acc[1] + acc[3]) - qoff[G], s_b);
-                    }
-                    {   // bias term: sum_G z[token][G] * qsum[head][G] (k-slots 0..3 = groups)
-                        float accz[4] = {0.f, 0.f, 0.f, 0.f};
-                        uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + trow * St::kParamRow + kv * 8 + (i & 1) * 4);
-                        if (i >= 2) zb = 0u;
-                        mma_f16(accz, qza0, qza1, 0u, 0u, zb, 0u);
-                        s_a += accz[0] + accz[2];
-                        s_b += accz[1] + accz[3];
-                    }
-                    S[nt][0] = s_a, S[nt][1] = s_b;
-                    if (partial) {
-                        if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
-                        if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
-                    }
-                }
-
-                // ------------------------------------------------ online softmax of head g (log2 units)
-                float mx = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const bool need = mx > Mref + kRescale;
-                if (__any_sync(0xffffffffu, need)) {
-                    const float f = need ? exp2f(Mref - mx) : 1.f; // exp2f(-inf) = 0 on the first tile
-                    if (need) Mref = mx, lsum *= f;
-                    // the accumulators' columns are heads 2i, 2i+1: fetch their factors from lanes g = 2i, 2i+1
-                    const float f0 = __shfl_sync(0xffffffffu, f, 8 * i), f1 = __shfl_sync(0xffffffffu, f, 8 * i + 4);
-#pragma unroll
-                    for (int e = 0; e < 16; e++) {
-                        O[e][0] *= f0, O[e][1] *= f1, O[e][2] *= f0, O[e][3] *= f1;
-                    }
-                    Ob[0] *= f0, Ob[1] *= f1, Ob[2] *= f0, Ob[3] *= f1;
-                }
-                const float p00 = exp2f(S[0][0] - Mref), p01 = exp2f(S[0][1] - Mref);
-                const float p10 = exp2f(S[1][0] - Mref), p11 = exp2f(S[1][1] - Mref);
-                lsum += (p00 + p01) + (p10 + p11);
-
-                // ------------------------------------------------ P (x value scales) as B fragments
-                // B[k = token][n = head]: this lane's pairs (2i, 2i+1) and (8+2i, 9+2i) of head g are
-                // exactly its own score columns, so no data moves between lanes.
-                const int T0 = lt + 2 * i, T1 = T0 + 1, T2 = T0 + 8, T3 = T0 + 9;
-                uint2 sV[4];
-                sV[0] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T0 * St::kParamRow + kv * 8);
-                sV[1] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T1 * St::kParamRow + kv * 8);
-                sV[2] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T2 * St::kParamRow + kv * 8);
-                sV[3] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T3 * St::kParamRow + kv * 8);
-                if (partial) { // stale rows may hold anything: keep them out of 0 * x
-                    if (tok0 + 2 * i >= n_row) sV[0] = make_uint2(0u, 0u);
-                    if (tok0 + 2 * i + 1 >= n_row) sV[1] = make_uint2(0u, 0u);
-                    if (tok0 + 2 * i + 8 >= n_row) sV[2] = make_uint2(0u, 0u);
-                    if (tok0 + 2 * i + 9 >= n_row) sV[3] = make_uint2(0u, 0u);
-                }
-                // P'[token][head] = P * value scale of (token, group): the two tokens of a pair have
-                // their own scales, gathered into one half2 by a byte permute
-                const uint32_t pu0 = pack_half2(p00, p01), pu1 = pack_half2(p10, p11);
-                uint32_t pbf[4][2];
-                {
-                    float2 sf[4][2]; // [token of the lane's four][groups 0,1 | 2,3]
-#pragma unroll
-                    for (int k = 0; k < 4; k++) sf[k][0] = h2f2(sV[k].x), sf[k][1] = h2f2(sV[k].y);
-#pragma unroll
-                    for (int G = 0; G < 4; G++) {
-                        const float a = (G & 1) ? sf[0][G >> 1].y : sf[0][G >> 1].x, b = (G & 1) ? sf[1][G >> 1].y : sf[1][G >> 1].x;
-                        const float c = (G & 1) ? sf[2][G >> 1].y : sf[2][G >> 1].x, d = (G & 1) ? sf[3][G >> 1].y : sf[3][G >> 1].x;
-                        pbf[G][0] = pack_half2(p00 * a, p01 * b); // f32 product, one rounding
-                        pbf[G][1] = pack_half2(p10 * c, p11 * d);
-                    }
-                }
-
-                // ------------------------------------------------ O^T[dim][head] += V^T P^T
-                {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] (z + C s)[t][G]
-                    const int gq = g & 3;
-                    const uint8_t *vz = sg + St::kVz + kv * 8 + gq * 2;
-                    uint32_t z0 = *reinterpret_cast<const uint16_t *>(vz + T0 * St::kParamRow);
-                    uint32_t z1 = *reinterpret_cast<const uint16_t *>(vz + T1 * St::kParamRow);
-                    uint32_t z2 = *reinterpret_cast<const uint16_t *>(vz + T2 * St::kParamRow);
-                    uint32_t z3 = *reinterpret_cast<const uint16_t *>(vz + T3 * St::kParamRow);
-                    if (partial) {
-                        if (tok0 + 2 * i >= n_row) z0 = 0;
-                        if (tok0 + 2 * i + 1 >= n_row) z1 = 0;
-                        if (tok0 + 2 * i + 8 >= n_row) z2 = 0;
-                        if (tok0 + 2 * i + 9 >= n_row) z3 = 0;
-                    }
-                    // this lane's group is gq: its scales sit in half gq of the pairs gathered above
-                    const uint32_t sel = (gq & 1) ? 0x7632u : 0x5410u;
-                    const uint32_t s01 = prmt(gq < 2 ? sV[0].x : sV[0].y, gq < 2 ? sV[1].x : sV[1].y, sel);
-                    const uint32_t s23 = prmt(gq < 2 ? sV[2].x : sV[2].y, gq < 2 ? sV[3].x : sV[3].y, sel);
-                    const uint32_t cc = pack_half2(kVCentre, kVCentre);
-                    const uint32_t a0 = g < 4 ? hfma2_u32(s01, cc, z0 | z1 << 16) : 0u;
-                    const uint32_t a2 = g < 4 ? hfma2_u32(s23, cc, z2 | z3 << 16) : 0u;
-                    mma_f16(Ob, a0, 0u, a2, 0u, pu0, pu1);
-                }
-                const uint8_t *vc = sg + St::kV + kv * (kDim * BITS / 8);
+            // Query fragments of head kv*8+g: 16 dims per group, scaled by log2(e)/16,
+            // split into two halves; and the group sums for the bias term.
+            uint32_t qh[4][8], ql[4][8];
+            uint32_t qza0 = 0, qza1 = 0;
+            float qoff[4]; // per group: what the code offsets (1024, and 64 for high nibbles) add to q.c
+            {
+                float qs[4];
+                const float *qp = a.q + ((size_t(s.seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
 #pragma unroll
                 for (int G = 0; G < 4; G++) {
-                    if (BITS == 8) {
-                        const uint2 t0 = *reinterpret_cast<const uint2 *>(vc + T0 * St::kCodeRow + G * 64 + g * 8);
-                        const uint2 t1 = *reinterpret_cast<const uint2 *>(vc + T1 * St::kCodeRow + G * 64 + g * 8);
-                        const uint2 t2 = *reinterpret_cast<const uint2 *>(vc + T2 * St::kCodeRow + G * 64 + g * 8);
-                        const uint2 t3 = *reinterpret_cast<const uint2 *>(vc + T3 * St::kCodeRow + G * 64 + g * 8);
-                        // [T0.b0 T1.b0 T0.b1 T1.b1] and [T0.b2 T1.b2 T0.b3 T1.b3], per dim row and token pair
-                        const uint32_t x01[2] = {prmt(t0.x, t1.x, 0x5140), prmt(t0.x, t1.x, 0x7362)};
-                        const uint32_t u01[2] = {prmt(t0.y, t1.y, 0x5140), prmt(t0.y, t1.y, 0x7362)};
-                        const uint32_t x23[2] = {prmt(t2.x, t3.x, 0x5140), prmt(t2.x, t3.x, 0x7362)};
-                        const uint32_t u23[2] = {prmt(t2.y, t3.y, 0x5140), prmt(t2.y, t3.y, 0x7362)};
+                    float x[16];
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const uint32_t sel = (e & 1) ? 0x4342u : 0x4140u;
-                            // 1024 + c minus 1152: the centred code c - 128 (see kVCentre)
-                            const uint32_t a0 = hsub2_u32(prmt(x01[e >> 1], kMagic, sel), k1152);
-                            const uint32_t a1 = hsub2_u32(prmt(u01[e >> 1], kMagic, sel), k1152);
-                            const uint32_t a2 = hsub2_u32(prmt(x23[e >> 1], kMagic, sel), k1152);
-                            const uint32_t a3 = hsub2_u32(prmt(u23[e >> 1], kMagic, sel), k1152);
-                            mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+                    for (int c = 0; c < 4; c++) {
+                        const float4 v = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
+                        x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
+                    }
+                    float hi[16], lo[16], sum = 0.f, off = 0.f;
+#pragma unroll
+                    for (int d = 0; d < 16; d++) {
+                        x[d] *= kLog2e * 0.0625f;
+                        hi[d] = __half2float(__float2half_rn(x[d]));
+                        lo[d] = __half2float(__float2half_rn(x[d] - hi[d]));
+                        sum += x[d];
+                        // 8-bit: every code rides on 1024; 4-bit: even dims (low nibbles) on 1024, odd on 64
+                        off += (hi[d] + lo[d]) * ((BITS == 4 && (d & 1)) ? 64.f : 1024.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            const int d0 = q_dim<BITS>(j, r, 0), d1 = q_dim<BITS>(j, r, 1);
+                            qh[G][2 * j + r] = pack_half2(hi[d0], hi[d1]);
+                            ql[G][2 * j + r] = pack_half2(lo[d0], lo[d1]);
                         }
-                    } else {
-                        const uint32_t t0 = *reinterpret_cast<const uint32_t *>(vc + T0 * St::kCodeRow + G * 32 + g * 4);
-                        const uint32_t t1 = *reinterpret_cast<const uint32_t *>(vc + T1 * St::kCodeRow + G * 32 + g * 4);
-                        const uint32_t t2 = *reinterpret_cast<const uint32_t *>(vc + T2 * St::kCodeRow + G * 32 + g * 4);
-                        const uint32_t t3 = *reinterpret_cast<const uint32_t *>(vc + T3 * St::kCodeRow + G * 32 + g * 4);
-                        // low half-word: T0's nibbles 0..3 (dim row g), high: T1's; .y side: nibbles 4..7 (row g+8)
-                        const uint32_t x01 = prmt(t0, t1, 0x5410), u01 = prmt(t0, t1, 0x7632);
-                        const uint32_t x23 = prmt(t2, t3, 0x5410), u23 = prmt(t2, t3, 0x7632);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    off += __shfl_xor_sync(0xffffffffu, off, 1);
+                    off += __shfl_xor_sync(0xffffffffu, off, 2);
+                    qs[G] = sum;
+                    qoff[G] = off;
+                }
+                // A fragment of the bias-term MMA: row g = high halves of the group sums of head g,
+                // row g+8 = low halves; k-slots 0..3 = groups (lanes i < 2 hold two groups each).
+                const float s0 = i == 0 ? qs[0] : qs[2], s1 = i == 0 ? qs[1] : qs[3];
+                const float h0 = __half2float(__float2half_rn(s0)), h1 = __half2float(__float2half_rn(s1));
+                qza0 = i < 2 ? pack_half2(h0, h1) : 0u;
+                qza1 = i < 2 ? pack_half2(s0 - h0, s1 - h1) : 0u;
+            }
+
+            DQ_MARK(1);
+            float O[16][4];
+            float Ob[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int sh = 8 * (e >> 1);
-                            const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
-                            const uint32_t ctr = (e & 1) ? k72 : k1032; // magic + 8: the centred code n - 8
-                            const uint32_t a0 = hsub2_u32(lop_and_or(x01 >> sh, mask, mg), ctr);
-                            const uint32_t a1 = hsub2_u32(lop_and_or(u01 >> sh, mask, mg), ctr);
-                            const uint32_t a2 = hsub2_u32(lop_and_or(x23 >> sh, mask, mg), ctr);
-                            const uint32_t a3 = hsub2_u32(lop_and_or(u23 >> sh, mask, mg), ctr);
-                            mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+            for (int e = 0; e < 16; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
+            float Mref = -INFINITY, lsum = 0.f; // of head g (this thread's row of the score MMA)
+
+            for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
+                const uint32_t st = it % NS, round = it / NS;
+                if (!mbar_wait(&full[st], round & 1, abort_flag)) {
+                    if (lane == 0) {
+                        atomicOr(a.status, kStatusFullTimeout);
+                        *abort_flag = 1;
+                    }
+                    alive = false;
+                    break;
+                }
+                if (t == s.tile_begin) { DQ_MARK(2); }
+                const uint8_t *sg = stages + st * St::kBytes;
+#pragma unroll 1
+                for (int sub = 0; sub < kTile / kSub; sub++) {
+                    const uint32_t q_idx = 2 * (t - s.tile_begin) + sub;
+                    const uint32_t tok0 = t * kTile + sub * kSub; // first token of the sub-tile
+                    if (!row_live || (q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_row) continue;
+                    const bool partial = tok0 + kSub > n_row;
+                    const int lt = sub * kSub; // token offset inside the stage
+
+                    // ------------------------------------------------ scores S[head][token]
+                    // MMA rows 0..7 = high halves of the 8 query heads, rows 8..15 = their low halves;
+                    // columns = 8 tokens.  Lane (g, i) feeds token g of each 8-token tile and owns
+                    // head g at tokens 2i, 2i+1.
+                    float S[2][2];
+                    const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
+#pragma unroll
+                    for (int nt = 0; nt < 2; nt++) {
+                        const int trow = lt + nt * 8 + g;          // token this lane loads
+                        const int tc0 = lt + nt * 8 + 2 * i;       // tokens of this lane's columns
+                        const uint2 sK0 = *reinterpret_cast<const uint2 *>(sg + St::kKs + tc0 * St::kParamRow + kv * 8);
+                        const uint2 sK1 = *reinterpret_cast<const uint2 *>(sg + St::kKs + (tc0 + 1) * St::kParamRow + kv * 8);
+                        const float2 sKf0[2] = {h2f2(sK0.x), h2f2(sK0.y)}, sKf1[2] = {h2f2(sK1.x), h2f2(sK1.y)};
+                        float s_a = 0.f, s_b = 0.f;
+#pragma unroll
+                        for (int G = 0; G < 4; G++) {
+                            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (BITS == 8) {
+                                const uint4 r = *reinterpret_cast<const uint4 *>(kc + trow * St::kCodeRow + G * 64 + i * 16);
+                                const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    // operands stay 1024 + c; 1024 * sum(q) is taken off the group sum below
+                                    const uint32_t b0 = prmt(w[j], kMagic, 0x4140);
+                                    const uint32_t b1 = prmt(w[j], kMagic, 0x4342);
+                                    mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
+                                }
+                            } else {
+                                const uint2 r = *reinterpret_cast<const uint2 *>(kc + trow * St::kCodeRow + G * 32 + i * 8);
+                                const uint32_t w[2] = {r.x, r.y};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    const uint32_t x = w[j >> 1] >> (8 * (j & 1));
+                                    // low nibbles ride on 1024, high nibbles on 64: (1024, 64) * the matching
+                                    // partial sums of q come off below
+                                    const uint32_t b0 = lop_and_or(x, 0x000f000fu, k1024);
+                                    const uint32_t b1 = lop_and_or(x, 0x00f000f0u, k64);
+                                    mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
+                                }
+                            }
+                            const float sc0 = G == 0 ? sKf0[0].x : G == 1 ? sKf0[0].y : G == 2 ? sKf0[1].x : sKf0[1].y;
+                            const float sc1 = G == 0 ? sKf1[0].x : G == 1 ? sKf1[0].y : G == 2 ? sKf1[1].x : sKf1[1].y;
+                            s_a = fmaf(sc0, (acc[0] + acc[2]) - qoff[G], s_a);
+                            s_b = fmaf(sc1, (acc[1] + acc[3]) - qoff[G], s_b);
+                        }
+                        {   // bias term: sum_G z[token][G] * qsum[head][G] (k-slots 0..3 = groups)
+                            float accz[4] = {0.f, 0.f, 0.f, 0.f};
+                            uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + trow * St::kParamRow + kv * 8 + (i & 1) * 4);
+                            if (i >= 2) zb = 0u;
+                            mma_f16(accz, qza0, qza1, 0u, 0u, zb, 0u);
+                            s_a += accz[0] + accz[2];
+                            s_b += accz[1] + accz[3];
+                        }
+                        S[nt][0] = s_a, S[nt][1] = s_b;
+                        if (partial) {
+                            if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
+                            if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
+                        }
+                    }
+
+                    // ------------------------------------------------ online softmax of head g (log2 units)
+                    float mx = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const bool need = mx > Mref + kRescale;
+                    if (__any_sync(0xffffffffu, need)) {
+                        const float f = need ? exp2f(Mref - mx) : 1.f; // exp2f(-inf) = 0 on the first tile
+                        if (need) Mref = mx, lsum *= f;
+                        // the accumulators' columns are heads 2i, 2i+1: fetch their factors from lanes g = 2i, 2i+1
+                        const float f0 = __shfl_sync(0xffffffffu, f, 8 * i), f1 = __shfl_sync(0xffffffffu, f, 8 * i + 4);
+#pragma unroll
+                        for (int e = 0; e < 16; e++) {
+                            O[e][0] *= f0, O[e][1] *= f1, O[e][2] *= f0, O[e][3] *= f1;
+                        }
+                        Ob[0] *= f0, Ob[1] *= f1, Ob[2] *= f0, Ob[3] *= f1;
+                    }
+                    const float p00 = exp2f(S[0][0] - Mref), p01 = exp2f(S[0][1] - Mref);
+                    const float p10 = exp2f(S[1][0] - Mref), p11 = exp2f(S[1][1] - Mref);
+                    lsum += (p00 + p01) + (p10 + p11);
+
+                    // ------------------------------------------------ P (x value scales) as B fragments
+                    // B[k = token][n = head]: this lane's pairs (2i, 2i+1) and (8+2i, 9+2i) of head g are
+                    // exactly its own score columns, so no data moves between lanes.
+                    const int T0 = lt + 2 * i, T1 = T0 + 1, T2 = T0 + 8, T3 = T0 + 9;
+                    uint2 sV[4];
+                    sV[0] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T0 * St::kParamRow + kv * 8);
+                    sV[1] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T1 * St::kParamRow + kv * 8);
+                    sV[2] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T2 * St::kParamRow + kv * 8);
+                    sV[3] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T3 * St::kParamRow + kv * 8);
+                    if (partial) { // stale rows may hold anything: keep them out of 0 * x
+                        if (tok0 + 2 * i >= n_row) sV[0] = make_uint2(0u, 0u);
+                        if (tok0 + 2 * i + 1 >= n_row) sV[1] = make_uint2(0u, 0u);
+                        if (tok0 + 2 * i + 8 >= n_row) sV[2] = make_uint2(0u, 0u);
+                        if (tok0 + 2 * i + 9 >= n_row) sV[3] = make_uint2(0u, 0u);
+                    }
+                    // P'[token][head] = P * value scale of (token, group): the two tokens of a pair have
+                    // their own scales, gathered into one half2 by a byte permute
+                    const uint32_t pu0 = pack_half2(p00, p01), pu1 = pack_half2(p10, p11);
+                    uint32_t pbf[4][2];
+                    {
+                        float2 sf[4][2]; // [token of the lane's four][groups 0,1 | 2,3]
+#pragma unroll
+                        for (int k = 0; k < 4; k++) sf[k][0] = h2f2(sV[k].x), sf[k][1] = h2f2(sV[k].y);
+#pragma unroll
+                        for (int G = 0; G < 4; G++) {
+                            const float a = (G & 1) ? sf[0][G >> 1].y : sf[0][G >> 1].x, b = (G & 1) ? sf[1][G >> 1].y : sf[1][G >> 1].x;
+                            const float c = (G & 1) ? sf[2][G >> 1].y : sf[2][G >> 1].x, d = (G & 1) ? sf[3][G >> 1].y : sf[3][G >> 1].x;
+                            pbf[G][0] = pack_half2(p00 * a, p01 * b); // f32 product, one rounding
+                            pbf[G][1] = pack_half2(p10 * c, p11 * d);
+                        }
+                    }
+
+                    // ------------------------------------------------ O^T[dim][head] += V^T P^T
+                    {   // value biases: rows 0..3 of one more MMA hold sum_t P[t][h] (z + C s)[t][G]
+                        const int gq = g & 3;
+                        const uint8_t *vz = sg + St::kVz + kv * 8 + gq * 2;
+                        uint32_t z0 = *reinterpret_cast<const uint16_t *>(vz + T0 * St::kParamRow);
+                        uint32_t z1 = *reinterpret_cast<const uint16_t *>(vz + T1 * St::kParamRow);
+                        uint32_t z2 = *reinterpret_cast<const uint16_t *>(vz + T2 * St::kParamRow);
+                        uint32_t z3 = *reinterpret_cast<const uint16_t *>(vz + T3 * St::kParamRow);
+                        if (partial) {
+                            if (tok0 + 2 * i >= n_row) z0 = 0;
+                            if (tok0 + 2 * i + 1 >= n_row) z1 = 0;
+                            if (tok0 + 2 * i + 8 >= n_row) z2 = 0;
+                            if (tok0 + 2 * i + 9 >= n_row) z3 = 0;
+                        }
+                        // this lane's group is gq: its scales sit in half gq of the pairs gathered above
+                        const uint32_t sel = (gq & 1) ? 0x7632u : 0x5410u;
+                        const uint32_t s01 = prmt(gq < 2 ? sV[0].x : sV[0].y, gq < 2 ? sV[1].x : sV[1].y, sel);
+                        const uint32_t s23 = prmt(gq < 2 ? sV[2].x : sV[2].y, gq < 2 ? sV[3].x : sV[3].y, sel);
+                        const uint32_t cc = pack_half2(kVCentre, kVCentre);
+                        const uint32_t a0 = g < 4 ? hfma2_u32(s01, cc, z0 | z1 << 16) : 0u;
+                        const uint32_t a2 = g < 4 ? hfma2_u32(s23, cc, z2 | z3 << 16) : 0u;
+                        mma_f16(Ob, a0, 0u, a2, 0u, pu0, pu1);
+                    }
+                    const uint8_t *vc = sg + St::kV + kv * (kDim * BITS / 8);
+#pragma unroll
+                    for (int G = 0; G < 4; G++) {
+                        if (BITS == 8) {
+                            const uint2 t0 = *reinterpret_cast<const uint2 *>(vc + T0 * St::kCodeRow + G * 64 + g * 8);
+                            const uint2 t1 = *reinterpret_cast<const uint2 *>(vc + T1 * St::kCodeRow + G * 64 + g * 8);
+                            const uint2 t2 = *reinterpret_cast<const uint2 *>(vc + T2 * St::kCodeRow + G * 64 + g * 8);
+                            const uint2 t3 = *reinterpret_cast<const uint2 *>(vc + T3 * St::kCodeRow + G * 64 + g * 8);
+                            // [T0.b0 T1.b0 T0.b1 T1.b1] and [T0.b2 T1.b2 T0.b3 T1.b3], per dim row and token pair
+                            const uint32_t x01[2] = {prmt(t0.x, t1.x, 0x5140), prmt(t0.x, t1.x, 0x7362)};
+                            const uint32_t u01[2] = {prmt(t0.y, t1.y, 0x5140), prmt(t0.y, t1.y, 0x7362)};
+                            const uint32_t x23[2] = {prmt(t2.x, t3.x, 0x5140), prmt(t2.x, t3.x, 0x7362)};
+                            const uint32_t u23[2] = {prmt(t2.y, t3.y, 0x5140), prmt(t2.y, t3.y, 0x7362)};
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const uint32_t sel = (e & 1) ? 0x4342u : 0x4140u;
+                                // 1024 + c minus 1152: the centred code c - 128 (see kVCentre)
+                                const uint32_t a0 = hsub2_u32(prmt(x01[e >> 1], kMagic, sel), k1152);
+                                const uint32_t a1 = hsub2_u32(prmt(u01[e >> 1], kMagic, sel), k1152);
+                                const uint32_t a2 = hsub2_u32(prmt(x23[e >> 1], kMagic, sel), k1152);
+                                const uint32_t a3 = hsub2_u32(prmt(u23[e >> 1], kMagic, sel), k1152);
+                                mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+                            }
+                        } else {
+                            const uint32_t t0 = *reinterpret_cast<const uint32_t *>(vc + T0 * St::kCodeRow + G * 32 + g * 4);
+                            const uint32_t t1 = *reinterpret_cast<const uint32_t *>(vc + T1 * St::kCodeRow + G * 32 + g * 4);
+                            const uint32_t t2 = *reinterpret_cast<const uint32_t *>(vc + T2 * St::kCodeRow + G * 32 + g * 4);
+                            const uint32_t t3 = *reinterpret_cast<const uint32_t *>(vc + T3 * St::kCodeRow + G * 32 + g * 4);
+                            // low half-word: T0's nibbles 0..3 (dim row g), high: T1's; .y side: nibbles 4..7 (row g+8)
+                            const uint32_t x01 = prmt(t0, t1, 0x5410), u01 = prmt(t0, t1, 0x7632);
+                            const uint32_t x23 = prmt(t2, t3, 0x5410), u23 = prmt(t2, t3, 0x7632);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const int sh = 8 * (e >> 1);
+                                const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
+                                const uint32_t ctr = (e & 1) ? k72 : k1032; // magic + 8: the centred code n - 8
+                                const uint32_t a0 = hsub2_u32(lop_and_or(x01 >> sh, mask, mg), ctr);
+                                const uint32_t a1 = hsub2_u32(lop_and_or(u01 >> sh, mask, mg), ctr);
+                                const uint32_t a2 = hsub2_u32(lop_and_or(x23 >> sh, mask, mg), ctr);
+                                const uint32_t a3 = hsub2_u32(lop_and_or(u23 >> sh, mask, mg), ctr);
+                                mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+                            }
                         }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[st]);
-        }
 
-        // ---------------------------------------------------------------- end of segment
-        DQ_MARK(3);
-        // l of head g over the four lanes that share it; then every lane takes m and l of the
-        // heads of its accumulator columns (2i, 2i+1) from lanes g = 2i and g = 2i+1.
-        lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-        lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-        float Mc2[2], l[2];
-        Mc2[0] = __shfl_sync(0xffffffffu, Mref, 8 * i), Mc2[1] = __shfl_sync(0xffffffffu, Mref, 8 * i + 4);
-        l[0] = __shfl_sync(0xffffffffu, lsum, 8 * i), l[1] = __shfl_sync(0xffffffffu, lsum, 8 * i + 4);
+            // ---------------------------------------------------------------- end of segment
+            DQ_MARK(3);
+            // l of head g over the four lanes that share it; then every lane takes m and l of the
+            // heads of its accumulator columns (2i, 2i+1) from lanes g = 2i and g = 2i+1.
+            lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+            lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+            float Mc2[2], l[2];
+            Mc2[0] = __shfl_sync(0xffffffffu, Mref, 8 * i), Mc2[1] = __shfl_sync(0xffffffffu, Mref, 8 * i + 4);
+            l[0] = __shfl_sync(0xffffffffu, lsum, 8 * i), l[1] = __shfl_sync(0xffffffffu, lsum, 8 * i + 4);
 #pragma unroll
-        for (int G = 0; G < 4; G++) {
-            const float b0 = __shfl_sync(0xffffffffu, Ob[0], 4 * G + i);
-            const float b1 = __shfl_sync(0xffffffffu, Ob[1], 4 * G + i);
+            for (int G = 0; G < 4; G++) {
+                const float b0 = __shfl_sync(0xffffffffu, Ob[0], 4 * G + i);
+                const float b1 = __shfl_sync(0xffffffffu, Ob[1], 4 * G + i);
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                O[4 * G + e][0] += b0, O[4 * G + e][1] += b1;
-                O[4 * G + e][2] += b0, O[4 * G + e][3] += b1;
-            }
-        }
-        float *dst = a.parts + ((size_t(s.part) * a.m + row) * kKv + kv) * kPartKv;
-        if (NSLOT == 1) {
-            if (row_live) {
-#pragma unroll
-                for (int e = 0; e < 16; e++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) dst[(4 * e + c) * 32 + lane] = O[e][c];
-                if (g == 0) {
-                    dst[kFragFloats + 2 * i] = Mc2[0], dst[kFragFloats + 2 * i + 1] = Mc2[1];
-                    dst[kFragFloats + 8 + 2 * i] = l[0], dst[kFragFloats + 8 + 2 * i + 1] = l[1];
+                for (int e = 0; e < 4; e++) {
+                    O[4 * G + e][0] += b0, O[4 * G + e][1] += b1;
+                    O[4 * G + e][2] += b0, O[4 * G + e][3] += b1;
                 }
             }
-        } else {
-            // Warps that share a (kv, row) agree on one maximum, scale, and add up
-            // in a fixed order through shared memory (deterministic).
-            if (g == 0) {
-                ml[warp * 16 + 2 * i] = Mc2[0], ml[warp * 16 + 2 * i + 1] = Mc2[1];
-                ml[warp * 16 + 8 + 2 * i] = l[0], ml[warp * 16 + 8 + 2 * i + 1] = l[1];
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
-            float Mc[2] = {-INFINITY, -INFINITY}, lc[2] = {0.f, 0.f};
+            float *dst = a.parts + ((size_t(s.part) * a.m + row) * kKv + kv) * kPartKv;
+            if (NSLOT == 1) {
+                if (row_live) {
 #pragma unroll
-            for (int sl = 0; sl < NSLOT; sl++) {
-                const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
-                Mc[0] = fmaxf(Mc[0], ml[w * 16 + 2 * i]);
-                Mc[1] = fmaxf(Mc[1], ml[w * 16 + 2 * i + 1]);
-            }
+                    for (int e = 0; e < 16; e++)
 #pragma unroll
-            for (int sl = 0; sl < NSLOT; sl++) {
-                const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
-                const float m0 = ml[w * 16 + 2 * i], m1 = ml[w * 16 + 2 * i + 1];
-                lc[0] += m0 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i] * exp2f(m0 - Mc[0]);
-                lc[1] += m1 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i + 1] * exp2f(m1 - Mc[1]);
-            }
-            const float f0 = Mc2[0] == -INFINITY ? 0.f : exp2f(Mc2[0] - Mc[0]);
-            const float f1 = Mc2[1] == -INFINITY ? 0.f : exp2f(Mc2[1] - Mc[1]);
-            if (!a.segs) {
-                // One segment per launch: after the barrier above no warp reads the copy ring any
-                // more, so every warp parks its scaled accumulators in the ring at once; then each
-                // warp adds up its share of the elements in slot order (fixed, hence deterministic).
-                float *mine = reinterpret_cast<float *>(stages) + warp * kFragFloats;
-#pragma unroll
-                for (int e = 0; e < 16; e++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) mine[(4 * e + c) * 32 + lane] = O[e][c] * ((c & 1) ? f1 : f0);
+                        for (int c = 0; c < 4; c++) dst[(4 * e + c) * 32 + lane] = O[e][c];
+                    if (g == 0) {
+                        dst[kFragFloats + 2 * i] = Mc2[0], dst[kFragFloats + 2 * i + 1] = Mc2[1];
+                        dst[kFragFloats + 8 + 2 * i] = l[0], dst[kFragFloats + 8 + 2 * i + 1] = l[1];
+                    }
+                }
+            } else {
+                // Warps that share a (kv, row) agree on one maximum, scale, and add up
+                // in a fixed order through shared memory (deterministic).
+                if (g == 0) {
+                    ml[warp * 16 + 2 * i] = Mc2[0], ml[warp * 16 + 2 * i + 1] = Mc2[1];
+                    ml[warp * 16 + 8 + 2 * i] = l[0], ml[warp * 16 + 8 + 2 * i + 1] = l[1];
+                }
                 asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                float Mc[2] = {-INFINITY, -INFINITY}, lc[2] = {0.f, 0.f};
+#pragma unroll
+                for (int sl = 0; sl < NSLOT; sl++) {
+                    const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
+                    Mc[0] = fmaxf(Mc[0], ml[w * 16 + 2 * i]);
+                    Mc[1] = fmaxf(Mc[1], ml[w * 16 + 2 * i + 1]);
+                }
+#pragma unroll
+                for (int sl = 0; sl < NSLOT; sl++) {
+                    const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
+                    const float m0 = ml[w * 16 + 2 * i], m1 = ml[w * 16 + 2 * i + 1];
+                    lc[0] += m0 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i] * exp2f(m0 - Mc[0]);
+                    lc[1] += m1 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i + 1] * exp2f(m1 - Mc[1]);
+                }
+                const float f0 = Mc2[0] == -INFINITY ? 0.f : exp2f(Mc2[0] - Mc[0]);
+                const float f1 = Mc2[1] == -INFINITY ? 0.f : exp2f(Mc2[1] - Mc[1]);
+                if (!a.segs) {
+                    // One segment per launch: after the barrier above no warp reads the copy ring any
+                    // more, so every warp parks its scaled accumulators in the ring at once; then each
+                    // warp adds up its share of the elements in slot order (fixed, hence deterministic).
+                    float *mine = reinterpret_cast<float *>(stages) + warp * kFragFloats;
+#pragma unroll
+                    for (int e = 0; e < 16; e++)
+#pragma unroll
+                        for (int c = 0; c < 4; c++) mine[(4 * e + c) * 32 + lane] = O[e][c] * ((c & 1) ? f1 : f0);
+                    asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                    if (row_live) {
+                        constexpr int per = 64 / NSLOT;
+#pragma unroll
+                        for (int r = 0; r < per; r++) {
+                            float v = 0.f;
+#pragma unroll
+                            for (int sl = 0; sl < NSLOT; sl++) {
+                                const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
+                                v += reinterpret_cast<const float *>(stages)[w * kFragFloats + (slot * per + r) * 32 + lane];
+                            }
+                            dst[(slot * per + r) * 32 + lane] = v;
+                        }
+                        if (slot == 0 && g == 0) {
+                            dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
+                            dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+                        }
+                    }
+                } else {
+                float *buf = merge + (row_in_pass * kKv + kv) * kFragFloats;
+#pragma unroll 1
+                for (int sl = 0; sl < NSLOT; sl++) {
+                    if (sl == slot) {
+#pragma unroll
+                        for (int e = 0; e < 16; e++)
+#pragma unroll
+                            for (int c = 0; c < 4; c++) {
+                                const float v = O[e][c] * ((c & 1) ? f1 : f0);
+                                float *p = buf + (4 * e + c) * 32 + lane;
+                                *p = sl ? *p + v : v;
+                            }
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                }
                 if (row_live) {
                     constexpr int per = 64 / NSLOT;
 #pragma unroll
-                    for (int r = 0; r < per; r++) {
-                        float v = 0.f;
-#pragma unroll
-                        for (int sl = 0; sl < NSLOT; sl++) {
-                            const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
-                            v += reinterpret_cast<const float *>(stages)[w * kFragFloats + (slot * per + r) * 32 + lane];
-                        }
-                        dst[(slot * per + r) * 32 + lane] = v;
-                    }
+                    for (int r = 0; r < per; r++) dst[(slot * per + r) * 32 + lane] = buf[(slot * per + r) * 32 + lane];
                     if (slot == 0 && g == 0) {
                         dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
                         dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
                     }
                 }
-            } else {
-            float *buf = merge + (row_in_pass * kKv + kv) * kFragFloats;
-#pragma unroll 1
-            for (int sl = 0; sl < NSLOT; sl++) {
-                if (sl == slot) {
-#pragma unroll
-                    for (int e = 0; e < 16; e++)
-#pragma unroll
-                        for (int c = 0; c < 4; c++) {
-                            const float v = O[e][c] * ((c & 1) ? f1 : f0);
-                            float *p = buf + (4 * e + c) * 32 + lane;
-                            *p = sl ? *p + v : v;
-                        }
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // merge buffers free again
             }
-            if (row_live) {
+            DQ_MARK(4);
+        }
+    } else {
+        // Several query rows (MTP verify): a warp owns one kv head and two query rows.  The 16 rows
+        // of every MMA are the 8 heads of the kv head for the first row, then for the second, so the
+        // two rows share every dequantised fragment; keys and values are the B operands (8 tokens /
+        // 8 dims per instruction) and P is the A operand of the value product.  Queries are rounded
+        // to 16 bits here (one row keeps a low half instead).
+        constexpr int NR = 2;
+        constexpr int NP = ROWS / NR;                 // row groups per pass
+        constexpr int NSLOT = kWarps / (kKv * NP);    // warps sharing one (kv, row group)
+        constexpr int GP = 4 / NSLOT;                 // groups whose query fragments one warp prepares
+        static_assert(NSLOT == 2 || NSLOT == 4, "two or four warps per (kv head, row group)");
+        static_assert(kKv * NP * kQFragBytes <= kMergeBytes, "query fragments fit");
+        const int kv = warp & 1;
+        const int pair = (warp >> 1) % NP;
+        const int slot = (warp >> 1) / NP;
+        const int combo = pair * kKv + kv;
+        const uint32_t rowA = row0 + pair * NR;       // first query row of this warp
+        const int g = lane >> 2, i = lane & 3;
+        // Query fragments live in shared memory, one 128-bit A operand per (group, k-step, lane), in
+        // the area one-row launches use as their merge buffer.
+        uint4 *qf = reinterpret_cast<uint4 *>(merge) + combo * 512;
+        float *qaux = qsums + combo * 128; // off[r][G][head], sum[r][G][head]
+        constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
+        // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128
+        // (8 for 4-bit).  For zero-mean values the two terms then no longer cancel, so the 16-bit
+        // rounding of P costs 3x less relative error.  1152 = 0x6480, 1032 = 0x6408, 72 = 0x5480.
+        constexpr uint32_t k1152 = 0x64806480u, k1032 = 0x64086408u, k72 = 0x54805480u;
+        constexpr float kVCentre = BITS == 8 ? 128.f : 8.f;
+
+        uint32_t it = 0;
+        bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
+        for (uint32_t si = seg_lo; si < seg_hi; si++) {
+            const Segment s = load_segment(si);
+            uint32_t n_row[NR];      // keys each of the warp's rows sees (0 for a row past m)
+            uint32_t n_any = 0, n_all = 0xffffffffu;
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                n_row[r] = rowA + r < a.m ? min(s.kv_len + (rowA + r) * a.row_step, a.capacity) : 0u;
+                n_any = max(n_any, n_row[r]);
+                if (rowA + r < a.m) n_all = min(n_all, n_row[r]);
+            }
+
+            // ------------------------------------------------ query fragments
+            // Head kv*8+g, 16 dims per lane and group, scaled by log2(e)/16.  The warps that share the
+            // set split the groups between them.
+#pragma unroll
+            for (int gi = 0; gi < GP; gi++) {
+                const int G = slot * GP + gi;
+                uint32_t fa[8], fb[8]; // MMA rows g and g+8
+#pragma unroll
+                for (int r = 0; r < NR; r++) {
+                    const uint32_t qrow = rowA + r < a.m ? rowA + r : 0;
+                    const float *qp = a.q + ((size_t(s.seq) * a.m + qrow) * 16 + kv * 8 + g) * kDim + G * 64 + i * 16;
+                    float x[16];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const float4 v = *reinterpret_cast<const float4 *>(qp + c * 4);
+                        x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
+                    }
+                    float hi[16], sum = 0.f, off = 0.f;
+#pragma unroll
+                    for (int d = 0; d < 16; d++) {
+                        x[d] *= kLog2e * 0.0625f;
+                        hi[d] = __half2float(__float2half_rn(x[d]));
+                        sum += hi[d];
+                        // 8-bit: every code rides on 1024; 4-bit: even dims (low nibbles) on 1024, odd on 64
+                        off += hi[d] * ((BITS == 4 && (d & 1)) ? 64.f : 1024.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+#pragma unroll
+                        for (int w = 0; w < 2; w++) {
+                            const int d0 = q_dim<BITS>(j, w, 0), d1 = q_dim<BITS>(j, w, 1);
+                            if (r == 0) fa[2 * j + w] = pack_half2(hi[d0], hi[d1]);
+                            else fb[2 * j + w] = pack_half2(hi[d0], hi[d1]);
+                        }
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    off += __shfl_xor_sync(0xffffffffu, off, 1);
+                    off += __shfl_xor_sync(0xffffffffu, off, 2);
+                    if (i == 0) qaux[(r * 4 + G) * 8 + g] = off, qaux[64 + (r * 4 + G) * 8 + g] = sum;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    qf[(G * 4 + j) * 32 + lane] = make_uint4(fa[2 * j], fb[2 * j], fa[2 * j + 1], fb[2 * j + 1]);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            float qoff[NR][4]; // per row and group: what the code offsets (1024; 64 for high nibbles) add to q.c
+#pragma unroll
+            for (int r = 0; r < NR; r++)
+#pragma unroll
+                for (int G = 0; G < 4; G++) qoff[r][G] = qaux[(r * 4 + G) * 8 + g];
+            // A fragment of the bias-term MMA: k-slots 0..3 = groups (lanes i < 2 hold two each); row g =
+            // the first row's group sums (high halves), row g+8 = their low halves or the second row's sums.
+            uint32_t qza0 = 0, qza1 = 0;
+            if (i < 2) {
+                const float s0 = qaux[64 + (2 * i) * 8 + g], s1 = qaux[64 + (2 * i + 1) * 8 + g];
+                const float h0 = __half2float(__float2half_rn(s0)), h1 = __half2float(__float2half_rn(s1));
+                qza0 = pack_half2(h0, h1);
+                qza1 = pack_half2(qaux[64 + (4 + 2 * i) * 8 + g], qaux[64 + (4 + 2 * i + 1) * 8 + g]);
+            }
+
+            DQ_MARK(1);
+            // O[n-tile (group G, byte e)][c]: c0, c1 = MMA row g (dims G*64 + (2i | 2i+1)*8 + e), c2, c3 = row g+8.
+            float O[32][4];
+            float Ob[4] = {0.f, 0.f, 0.f, 0.f}; // sum_t P (z + C s): columns 2i, 2i+1 = groups (lanes i < 2)
+            float Mref[NR], lsum[NR];           // of head g, per query row
+#pragma unroll
+            for (int e = 0; e < 32; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; r++) Mref[r] = -INFINITY, lsum[r] = 0.f;
+
+            for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
+                const uint32_t st = it % NS, round = it / NS;
+                if (!mbar_wait(&full[st], round & 1, abort_flag)) {
+                    if (lane == 0) {
+                        atomicOr(a.status, kStatusFullTimeout);
+                        *abort_flag = 1;
+                    }
+                    alive = false;
+                    break;
+                }
+                if (t == s.tile_begin) { DQ_MARK(2); }
+                const uint8_t *sg = stages + st * St::kBytes;
+#pragma unroll 1
+                for (int sub = 0; sub < kTile / kSub; sub++) {
+                    const uint32_t q_idx = 2 * (t - s.tile_begin) + sub;
+                    const uint32_t tok0 = t * kTile + sub * kSub; // first token of the sub-tile
+                    if ((q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_any) continue;
+                    const bool partial = tok0 + kSub > n_all;
+                    const int lt = sub * kSub; // token offset inside the stage
+
+                    // ------------------------------------------------ scores S[head][token]
+                    // Columns = 8 tokens per n-tile nt.  Lane (g, i) feeds token g of each n-tile and owns
+                    // head g (both MMA rows) at tokens 2i, 2i+1.
+                    float S[NR][2][2];
+                    {
+                        const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
+                        float2 sKf[2][2][2]; // [nt][token 2i | 2i+1][groups 0,1 | 2,3]
+#pragma unroll
+                        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                            for (int c = 0; c < 2; c++) {
+                                const uint2 v = *reinterpret_cast<const uint2 *>(sg + St::kKs + (lt + nt * 8 + 2 * i + c) * St::kParamRow + kv * 8);
+                                sKf[nt][c][0] = h2f2(v.x), sKf[nt][c][1] = h2f2(v.y);
+                            }
+                        float sc[NR][2][2];
+#pragma unroll
+                        for (int r = 0; r < NR; r++) sc[r][0][0] = sc[r][0][1] = sc[r][1][0] = sc[r][1][1] = 0.f;
+#pragma unroll
+                        for (int G = 0; G < 4; G++) {
+                            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                            uint32_t w[2][4];
+#pragma unroll
+                            for (int nt = 0; nt < 2; nt++) {
+                                const int trow = lt + nt * 8 + g; // token this lane loads
+                                if (BITS == 8) {
+                                    const uint4 rr = *reinterpret_cast<const uint4 *>(kc + trow * St::kCodeRow + G * 64 + i * 16);
+                                    w[nt][0] = rr.x, w[nt][1] = rr.y, w[nt][2] = rr.z, w[nt][3] = rr.w;
+                                } else {
+                                    const uint2 rr = *reinterpret_cast<const uint2 *>(kc + trow * St::kCodeRow + G * 32 + i * 8);
+                                    w[nt][0] = rr.x, w[nt][1] = rr.x >> 8, w[nt][2] = rr.y, w[nt][3] = rr.y >> 8;
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const uint4 A = qf[(G * 4 + j) * 32 + lane];
+#pragma unroll
+                                for (int nt = 0; nt < 2; nt++) {
+                                    uint32_t b0, b1;
+                                    if (BITS == 8) {
+                                        // operands stay 1024 + c; 1024 * sum(q) is taken off the group sum below
+                                        b0 = prmt(w[nt][j], kMagic, 0x4140), b1 = prmt(w[nt][j], kMagic, 0x4342);
+                                    } else {
+                                        // low nibbles ride on 1024, high nibbles on 64: (1024, 64) * the matching
+                                        // partial sums of q come off below
+                                        b0 = lop_and_or(w[nt][j], 0x000f000fu, k1024), b1 = lop_and_or(w[nt][j], 0x00f000f0u, k64);
+                                    }
+                                    mma_f16(acc[nt], A.x, A.y, A.z, A.w, b0, b1);
+                                }
+                            }
+#pragma unroll
+                            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                                for (int c = 0; c < 2; c++) {
+                                    const float2 pr = sKf[nt][c][G >> 1];
+                                    const float scale = (G & 1) ? pr.y : pr.x;
+                                    sc[0][nt][c] = fmaf(scale, acc[nt][c] - qoff[0][G], sc[0][nt][c]);
+                                    sc[1][nt][c] = fmaf(scale, acc[nt][c + 2] - qoff[1][G], sc[1][nt][c]);
+                                }
+                        }
+#pragma unroll
+                        for (int nt = 0; nt < 2; nt++) {
+                            // bias term: sum_G z[token][G] * qsum[head][G] (k-slots 0..3 = groups)
+                            float accz[4] = {0.f, 0.f, 0.f, 0.f};
+                            uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + (lt + nt * 8 + g) * St::kParamRow + kv * 8 + (i & 1) * 4);
+                            if (i >= 2) zb = 0u;
+                            mma_f16(accz, qza0, qza1, 0u, 0u, zb, 0u);
+#pragma unroll
+                            for (int c = 0; c < 2; c++) {
+                                S[0][nt][c] = sc[0][nt][c] + accz[c];
+                                S[1][nt][c] = sc[1][nt][c] + accz[c + 2];
+                            }
+                        }
+                        if (partial) {
+#pragma unroll
+                            for (int r = 0; r < NR; r++)
+#pragma unroll
+                                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                                    for (int c = 0; c < 2; c++)
+                                        if (tok0 + nt * 8 + 2 * i + c >= n_row[r]) S[r][nt][c] = -INFINITY;
+                        }
+                    }
+
+                    // ------------------------------------------------ online softmax of head g (log2 units)
+                    float p[NR][4];
+#pragma unroll
+                    for (int r = 0; r < NR; r++) {
+                        float mx = fmaxf(fmaxf(S[r][0][0], S[r][0][1]), fmaxf(S[r][1][0], S[r][1][1]));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                        if (mx > Mref[r] + kRescale) { // uniform over the four lanes of the head
+                            const float f = exp2f(Mref[r] - mx); // exp2f(-inf) = 0 on the first tile
+                            Mref[r] = mx, lsum[r] *= f;
+#pragma unroll
+                            for (int e = 0; e < 32; e++) {
+                                O[e][2 * r] *= f, O[e][2 * r + 1] *= f;
+                            }
+                            Ob[2 * r] *= f, Ob[2 * r + 1] *= f;
+                        }
+                        const float mu = Mref[r] == -INFINITY ? 0.f : Mref[r]; // a row with no key yet: every p is 0
+                        p[r][0] = exp2f(S[r][0][0] - mu), p[r][1] = exp2f(S[r][0][1] - mu);
+                        p[r][2] = exp2f(S[r][1][0] - mu), p[r][3] = exp2f(S[r][1][1] - mu);
+                        lsum[r] += (p[r][0] + p[r][1]) + (p[r][2] + p[r][3]);
+                    }
+                    __syncwarp(); // the rescale branch is per head; the MMAs below need the whole warp
+
+                    // ------------------------------------------------ O[head][dim] += P V
+                    // P is the A operand: this lane's score columns (tokens 2i, 2i+1 and 8+2i, 9+2i of head
+                    // g) are exactly the A fragment's elements, so no data moves between lanes.
+                    const int T0 = lt + 2 * i, T1 = T0 + 1, T2 = T0 + 8, T3 = T0 + 9;
+                    uint2 sV[4];
+                    sV[0] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T0 * St::kParamRow + kv * 8);
+                    sV[1] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T1 * St::kParamRow + kv * 8);
+                    sV[2] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T2 * St::kParamRow + kv * 8);
+                    sV[3] = *reinterpret_cast<const uint2 *>(sg + St::kVs + T3 * St::kParamRow + kv * 8);
+                    if (partial) { // stale rows may hold anything: keep them out of 0 * x
+                        if (tok0 + 2 * i >= n_any) sV[0] = make_uint2(0u, 0u);
+                        if (tok0 + 2 * i + 1 >= n_any) sV[1] = make_uint2(0u, 0u);
+                        if (tok0 + 2 * i + 8 >= n_any) sV[2] = make_uint2(0u, 0u);
+                        if (tok0 + 2 * i + 9 >= n_any) sV[3] = make_uint2(0u, 0u);
+                    }
+                    // A fragment of x[0..3] (MMA row g) and y[0..3] (row g+8) at the lane's four tokens
+                    auto a_frag = [&](const float (&x)[4], const float (&y)[4], uint32_t (&A)[4]) {
+                        A[0] = pack_half2(x[0], x[1]), A[2] = pack_half2(x[2], x[3]);
+                        A[1] = pack_half2(y[0], y[1]), A[3] = pack_half2(y[2], y[3]);
+                    };
+                    {   // value biases: one MMA with B[token][n = group] = z + C s (columns 4..7 empty)
+                        const int gq = g & 3;
+                        const uint8_t *vz = sg + St::kVz + kv * 8 + gq * 2;
+                        uint32_t z0 = *reinterpret_cast<const uint16_t *>(vz + T0 * St::kParamRow);
+                        uint32_t z1 = *reinterpret_cast<const uint16_t *>(vz + T1 * St::kParamRow);
+                        uint32_t z2 = *reinterpret_cast<const uint16_t *>(vz + T2 * St::kParamRow);
+                        uint32_t z3 = *reinterpret_cast<const uint16_t *>(vz + T3 * St::kParamRow);
+                        if (partial) {
+                            if (tok0 + 2 * i >= n_any) z0 = 0;
+                            if (tok0 + 2 * i + 1 >= n_any) z1 = 0;
+                            if (tok0 + 2 * i + 8 >= n_any) z2 = 0;
+                            if (tok0 + 2 * i + 9 >= n_any) z3 = 0;
+                        }
+                        // this lane's group is gq: its scales sit in half gq of the pairs gathered above
+                        const uint32_t sel = (gq & 1) ? 0x7632u : 0x5410u;
+                        const uint32_t s01 = prmt(gq < 2 ? sV[0].x : sV[0].y, gq < 2 ? sV[1].x : sV[1].y, sel);
+                        const uint32_t s23 = prmt(gq < 2 ? sV[2].x : sV[2].y, gq < 2 ? sV[3].x : sV[3].y, sel);
+                        const uint32_t cc = pack_half2(kVCentre, kVCentre);
+                        const uint32_t b0 = g < 4 ? hfma2_u32(s01, cc, z0 | z1 << 16) : 0u;
+                        const uint32_t b1 = g < 4 ? hfma2_u32(s23, cc, z2 | z3 << 16) : 0u;
+                        uint32_t A[4];
+                        a_frag(p[0], p[1], A);
+                        mma_f16(Ob, A[0], A[1], A[2], A[3], b0, b1);
+                    }
+                    const uint8_t *vc = sg + St::kV + kv * (kDim * BITS / 8);
+#pragma unroll
+                    for (int G = 0; G < 4; G++) {
+                        uint32_t A[4];
+                        {   // P times the value scales of group G: f32 product, one rounding
+                            float cs[4], x[4], y[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const float2 pr = h2f2(G < 2 ? sV[k].x : sV[k].y);
+                                cs[k] = (G & 1) ? pr.y : pr.x;
+                                x[k] = p[0][k] * cs[k], y[k] = p[1][k] * cs[k];
+                            }
+                            a_frag(x, y, A);
+                        }
+                        if (BITS == 8) {
+                            // 8 dims (G*64 + g*8 ..) of the lane's four tokens
+                            const uint2 t0 = *reinterpret_cast<const uint2 *>(vc + T0 * St::kCodeRow + G * 64 + g * 8);
+                            const uint2 t1 = *reinterpret_cast<const uint2 *>(vc + T1 * St::kCodeRow + G * 64 + g * 8);
+                            const uint2 t2 = *reinterpret_cast<const uint2 *>(vc + T2 * St::kCodeRow + G * 64 + g * 8);
+                            const uint2 t3 = *reinterpret_cast<const uint2 *>(vc + T3 * St::kCodeRow + G * 64 + g * 8);
+                            // [T0.b0 T1.b0 T0.b1 T1.b1] and [T0.b2 T1.b2 T0.b3 T1.b3]; .y: bytes 4..7
+                            const uint32_t x01[4] = {prmt(t0.x, t1.x, 0x5140), prmt(t0.x, t1.x, 0x7362),
+                                                     prmt(t0.y, t1.y, 0x5140), prmt(t0.y, t1.y, 0x7362)};
+                            const uint32_t x23[4] = {prmt(t2.x, t3.x, 0x5140), prmt(t2.x, t3.x, 0x7362),
+                                                     prmt(t2.y, t3.y, 0x5140), prmt(t2.y, t3.y, 0x7362)};
+#pragma unroll
+                            for (int e = 0; e < 8; e++) { // n-tile e: dim G*64 + n*8 + e in column n
+                                const uint32_t sel = (e & 1) ? 0x4342u : 0x4140u;
+                                // 1024 + c minus 1152: the centred code c - 128 (see kVCentre)
+                                const uint32_t b0 = hsub2_u32(prmt(x01[e >> 1], kMagic, sel), k1152);
+                                const uint32_t b1 = hsub2_u32(prmt(x23[e >> 1], kMagic, sel), k1152);
+                                mma_f16(O[G * 8 + e], A[0], A[1], A[2], A[3], b0, b1);
+                            }
+                        } else {
+                            const uint32_t t0 = *reinterpret_cast<const uint32_t *>(vc + T0 * St::kCodeRow + G * 32 + g * 4);
+                            const uint32_t t1 = *reinterpret_cast<const uint32_t *>(vc + T1 * St::kCodeRow + G * 32 + g * 4);
+                            const uint32_t t2 = *reinterpret_cast<const uint32_t *>(vc + T2 * St::kCodeRow + G * 32 + g * 4);
+                            const uint32_t t3 = *reinterpret_cast<const uint32_t *>(vc + T3 * St::kCodeRow + G * 32 + g * 4);
+                            // low half-word: T0's nibbles 0..3, high: T1's; second word: nibbles 4..7
+                            const uint32_t x01[2] = {prmt(t0, t1, 0x5410), prmt(t0, t1, 0x7632)};
+                            const uint32_t x23[2] = {prmt(t2, t3, 0x5410), prmt(t2, t3, 0x7632)};
+#pragma unroll
+                            for (int e = 0; e < 8; e++) { // nibble e of the 8
+                                const int sh = 8 * ((e & 3) >> 1);
+                                const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
+                                const uint32_t ctr = (e & 1) ? k72 : k1032; // magic + 8: the centred code n - 8
+                                const uint32_t b0 = hsub2_u32(lop_and_or(x01[e >> 2] >> sh, mask, mg), ctr);
+                                const uint32_t b1 = hsub2_u32(lop_and_or(x23[e >> 2] >> sh, mask, mg), ctr);
+                                mma_f16(O[G * 8 + e], A[0], A[1], A[2], A[3], b0, b1);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);
+            }
+
+            // ---------------------------------------------------------------- end of segment
+            DQ_MARK(3);
+#pragma unroll
+            for (int r = 0; r < NR; r++) { // l of head g over the four lanes that share it
+                lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
+                lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 2);
+            }
+#pragma unroll
+            for (int G = 0; G < 4; G++) { // the bias sums of group G sit in lane i = G/2 of the head's four
+                const int src = (lane & ~3) | (G >> 1);
+                const float b0 = __shfl_sync(0xffffffffu, Ob[G & 1], src);
+                const float b1 = __shfl_sync(0xffffffffu, Ob[2 + (G & 1)], src);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    O[G * 8 + e][0] += b0, O[G * 8 + e][1] += b0;
+                    O[G * 8 + e][2] += b1, O[G * 8 + e][3] += b1;
+                }
+            }
+            // Warps that share a (kv, row group) agree on one maximum per row, scale, and add up in a
+            // fixed order through shared memory (deterministic).
+            if (i == 0) {
+#pragma unroll
+                for (int r = 0; r < NR; r++) {
+                    float *m = ml + (warp * NR + r) * 16;
+                    m[g] = Mref[r], m[8 + g] = lsum[r];
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            float Mc[NR], lc[NR], f[NR];
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                Mc[r] = -INFINITY, lc[r] = 0.f;
+#pragma unroll
+                for (int sl = 0; sl < NSLOT; sl++) Mc[r] = fmaxf(Mc[r], ml[((((sl * NP + pair) << 1) | kv) * NR + r) * 16 + g]);
+#pragma unroll
+                for (int sl = 0; sl < NSLOT; sl++) {
+                    const float *m = ml + ((((sl * NP + pair) << 1) | kv) * NR + r) * 16;
+                    lc[r] += m[g] == -INFINITY ? 0.f : m[8 + g] * exp2f(m[g] - Mc[r]);
+                }
+                f[r] = Mref[r] == -INFINITY ? 0.f : exp2f(Mref[r] - Mc[r]);
+            }
+            // After the barrier above no warp reads the copy ring any more, so every warp parks its
+            // scaled accumulators in the ring at once, in the fragment order of the one-row path (the
+            // merge kernel knows only that one): head h, dim d sits at
+            // (4*mt + c)*32 + 4*((d >> 3) & 7) + (h >> 1), mt = 4*(d >> 6) + (d & 3), c = (h & 1) + ((d >> 1) & 2).
+            // Then each warp adds up its share of the elements in slot order (fixed, hence deterministic).
+            float *ring = reinterpret_cast<float *>(stages);
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                float *mine = ring + (warp * NR + r) * kFragFloats + (g & 1) * 32 + (g >> 1);
+#pragma unroll
+                for (int e = 0; e < 32; e++)
+#pragma unroll
+                    for (int cc = 0; cc < 2; cc++) // head g, dim 64*(e >> 3) + 8*(2i + cc) + (e & 7)
+                        mine[(4 * (4 * (e >> 3) + (e & 3)) + 2 * ((e >> 2) & 1)) * 32 + 4 * (2 * i + cc)] = O[e][2 * r + cc] * f[r];
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+#pragma unroll
+            for (int r = 0; r < NR; r++) {
+                if (rowA + r >= a.m) continue;
+                float *dst = a.parts + ((size_t(s.part) * a.m + rowA + r) * kKv + kv) * kPartKv;
                 constexpr int per = 64 / NSLOT;
 #pragma unroll
-                for (int r = 0; r < per; r++) dst[(slot * per + r) * 32 + lane] = buf[(slot * per + r) * 32 + lane];
-                if (slot == 0 && g == 0) {
-                    dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
-                    dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+                for (int k = 0; k < per; k++) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int sl = 0; sl < NSLOT; sl++) {
+                        const int w = ((sl * NP + pair) << 1) | kv;
+                        v += ring[(w * NR + r) * kFragFloats + (slot * per + k) * 32 + lane];
+                    }
+                    dst[(slot * per + k) * 32 + lane] = v;
                 }
+                if (slot == 0 && i == 0) dst[kFragFloats + g] = Mc[r], dst[kFragFloats + 8 + g] = lc[r];
             }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // merge buffers free again
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // ring, merge buffer and query fragments free again
+            DQ_MARK(4);
         }
-        DQ_MARK(4);
     }
 }
 
