@@ -293,7 +293,8 @@ def main():
     ap.add_argument("--points", default="all", help="'none' skips the extra measured points")
     ap.add_argument("--only", default=None, help="run one named point alone (for profiling) and print its result")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: merge kernel reads the peers' partials over NVLink (peer), or NCCL all-gather + merge")
+                    help="N > 1: partials stored into the peers' mailboxes over NVLink by the kernel that makes them (peer), "
+                         "or NCCL all-gather + merge")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -343,8 +344,8 @@ def main():
         if world == 1:
             op.record_cache(1, q, c, qg, out, params, stream=stream)
         elif group is not None:
-            op.partial_cache(1, q, c, group.staging, params, row_step=0, stream=stream)
-            group.merge(1, qg, out, stream=stream)  # waits for the peers' partials, reads them over NVLink
+            op.publish_cache(1, q, c, group, params, row_step=0, stream=stream)  # partial -> every peer's mailbox
+            group.collect(1, qg, out, stream=stream)  # waits on local flags, merges what the peers stored
         else:
             op.partial_cache(1, q, c, part, params, row_step=0, stream=stream)
             dist.all_gather_into_tensor(gathered, part)
@@ -481,7 +482,7 @@ def main():
                        "layers": LAYERS, "ctx_per_gpu": CTX, "kv_bits": 8, "l2": "inputs larger than L2 "
                        f"({LAYERS * CTX * BYTES_PER_TOKEN[8] / 1e6:.0f} MB per step per GPU)",
                        "replay": "CUDA graph" if (world == 1 or group is not None) else "eager launches",
-                       "exchange": None if world == 1 else ("merge kernel reads the peers' (m,l,O) over NVLink"
+                       "exchange": None if world == 1 else ("(m,l,O) stored into the peers' mailboxes over NVLink by the merge kernel"
                                                             if group is not None else "NCCL all-gather of (m,l,O) + merge")},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "peak_kind": peak_kind + " copy bandwidth",

@@ -238,16 +238,19 @@ int saetta_decode_partial_cache(saetta_decode *op, size_t m, const float *q_dev,
 int saetta_merge_partials(int device, const float *parts_dev, size_t ranks, size_t rows,
                           size_t heads, const float *q_and_gate_dev, float *out_dev, void *stream);
 
-/* The same merge fused with its exchange: no all-gather, one kernel per rank
- * reads every peer's partial straight out of the peer's memory over NVLink
- * (plain peer loads) once the peer has published it, then merges and gates.
- * One process per GPU: create a group on every rank, exchange the 64-byte
- * handles (any host-side all-gather), connect, then per exchange let the
- * decode / prefill partial entry points write into saetta_peer_group_staging()
- * and call saetta_peer_merge on every rank.  The sequence counter lives on the
- * device, so the launches can sit in a captured CUDA graph.  The wait for a
- * peer is bounded (about a second); saetta_peer_group_status reports a peer
- * that never published.  All ranks must perform the same number of exchanges. */
+/* The same merge fused with its exchange: no all-gather.  The kernel that
+ * finishes a rank's partial stores it straight into every peer's mailbox over
+ * NVLink (plain peer stores, every word tagged with the exchange number), and
+ * one kernel per rank polls its own memory, merges what arrived and gates.  One process per GPU: create a
+ * group on every rank, exchange the 64-byte handles (any host-side
+ * all-gather), connect, then per exchange either
+ *   saetta_decode_publish_cache + saetta_peer_collect   (decode / verify), or
+ *   a partial written to saetta_peer_group_staging() + saetta_peer_merge
+ *   (any other partial, e.g. saetta_att_gemm_partial; publishes, then collects)
+ * on every rank.  The sequence counter lives on the device, so the launches can
+ * sit in a captured CUDA graph.  The wait for a peer is bounded (about a
+ * second); saetta_peer_group_status reports a peer that never published.  All
+ * ranks must perform the same number of exchanges. */
 typedef struct saetta_peer_group saetta_peer_group;
 int saetta_peer_group_create(int device, int rank, int world, size_t rows_max, size_t heads,
                              uint8_t handle_out[64], saetta_peer_group **out);
@@ -256,6 +259,14 @@ void saetta_peer_group_destroy(saetta_peer_group *g);
 float *saetta_peer_group_staging(saetta_peer_group *g);
 int saetta_peer_merge(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev,
                       void *stream);
+int saetta_peer_collect(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev,
+                        float *out_dev, void *stream);
+/* saetta_decode_partial_cache with the partial published to the group instead
+ * of written to a buffer (m rows, heads as the group was made for). */
+int saetta_decode_publish_cache(saetta_decode *op, size_t m, const float *q_dev,
+                                const saetta_kv_cache *cache, saetta_peer_group *group,
+                                uint32_t row_step, const saetta_token_params *params_dev,
+                                void *stream);
 int saetta_peer_group_status(saetta_peer_group *g, void *stream, uint32_t *status);
 
 /* ------------------------------------------------------------------ prefill

@@ -111,6 +111,8 @@ SYMBOLS = {
     "saetta_peer_group_destroy": (None, [_P]),
     "saetta_peer_group_staging": (_P, [_P]),
     "saetta_peer_merge": (_I, [_P, _Z, _P, _P, _P]),
+    "saetta_peer_collect": (_I, [_P, _Z, _P, _P, _P]),
+    "saetta_decode_publish_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P]),
     "saetta_peer_group_status": (_I, [_P, _P, C.POINTER(_U32)]),
     "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
     "saetta_att_gemm_destroy": (None, [_P]),
@@ -314,6 +316,11 @@ class AttentionRows:
         _check(lib().saetta_decode_partial_cache(self.h, m, ptr(q), cache.h, ptr(part), row_step, ptr(params),
                                                  _stream(stream)))
 
+    def publish_cache(self, m, q, cache, group, params, row_step=1, stream=None):
+        """partial_cache with the partial stored straight into every peer's mailbox."""
+        _check(lib().saetta_decode_publish_cache(self.h, m, ptr(q), cache.h, group.h, row_step, ptr(params),
+                                                 _stream(stream)))
+
     def device_status(self, stream=None):
         s = C.c_uint32()
         _check(lib().saetta_decode_device_status(self.h, _stream(stream), C.byref(s)))
@@ -374,9 +381,10 @@ def merge_partials(device, parts, ranks, rows, heads, q_and_gate, out, stream=No
 
 
 class PeerGroup:
-    """Split-KV merge across the GPUs of one box, reading the peers' partials over
-    NVLink (no counterpart in the reference).  `all_gather_bytes(bytes) -> [bytes]`
-    is any host-side all-gather in rank order (torch.distributed works)."""
+    """Split-KV merge across the GPUs of one box: partials are stored into the peers'
+    mailboxes over NVLink and merged from local memory (no counterpart in the
+    reference).  `all_gather_bytes(bytes) -> [bytes]` is any host-side all-gather
+    in rank order (torch.distributed works)."""
 
     def __init__(self, device, rank, world, rows_max, heads, all_gather_bytes):
         h = C.c_void_p()
@@ -393,7 +401,12 @@ class PeerGroup:
         return lib().saetta_peer_group_staging(self.h)
 
     def merge(self, rows, q_and_gate, out, stream=None):
+        """Publishes the partial in `staging`, then collects."""
         _check(lib().saetta_peer_merge(self.h, rows, ptr(q_and_gate), ptr(out), _stream(stream)))
+
+    def collect(self, rows, q_and_gate, out, stream=None):
+        """Waits for every rank's published partial, merges and gates."""
+        _check(lib().saetta_peer_collect(self.h, rows, ptr(q_and_gate), ptr(out), _stream(stream)))
 
     def status(self, stream=None):
         s = C.c_uint32()

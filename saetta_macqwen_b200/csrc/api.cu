@@ -536,7 +536,7 @@ static int decode_check(const saetta_decode *op, size_t m, const void *q, const 
 
 static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView &kv, size_t kv_capacity,
                       const float *q_and_gate, float *out, float *part_out, uint32_t row_step,
-                      const saetta_token_params *params, cudaStream_t st) {
+                      const saetta_token_params *params, cudaStream_t st, saetta_peer_group *group = nullptr) {
     if (kv.kv_heads != op->kv_heads) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache and op disagree on kv heads");
     if (kv_capacity > op->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache larger than the op's capacity");
     if (kv_capacity % 32) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache capacity must be a multiple of 32");
@@ -548,11 +548,13 @@ static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView 
                                          uint32_t(kv_capacity), params, st))
             return rc;
         return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
-                                 part_out, st);
+                                 part_out, st, group ? &group->push : nullptr);
     }
     if (int rc = launch_decode_exact(kv, q, op->parts, uint32_t(m), row_step, op->splits, uint32_t(kv_capacity), params, st))
         return rc;
-    return launch_merge_logical(op->parts, uint32_t(op->splits), uint32_t(m), heads, q_and_gate, out, part_out, st);
+    if (int rc = launch_merge_logical(op->parts, uint32_t(op->splits), uint32_t(m), heads, q_and_gate, out, part_out, st))
+        return rc;
+    return group ? launch_peer_publish(group, m, st) : SAETTA_OK; // part_out is the group's staging buffer
 }
 
 int saetta_decode_record(saetta_decode *op, size_t m, const float *q_dev, const void *keys_dev, const void *values_dev,
@@ -615,6 +617,20 @@ int saetta_decode_partial_cache(saetta_decode *op, size_t m, const float *q_dev,
     if (row_step > 1) return fail(SAETTA_ERR_BAD_ARG, "decode partial: row_step is 0 or 1");
     return decode_run(op, m, q_dev, view_of_cache(cache), cache->capacity, nullptr, nullptr, part_dev, row_step, params_dev,
                       (cudaStream_t)stream);
+}
+
+int saetta_decode_publish_cache(saetta_decode *op, size_t m, const float *q_dev, const saetta_kv_cache *cache,
+                                saetta_peer_group *group, uint32_t row_step, const saetta_token_params *params_dev,
+                                void *stream) {
+    if (!group) return fail(SAETTA_ERR_BAD_ARG, "decode publish: null pointer");
+    if (int rc = decode_check(op, m, q_dev, group->staging, params_dev)) return rc;
+    if (!cache) return fail(SAETTA_ERR_BAD_ARG, "decode attention: null pointer");
+    if (row_step > 1) return fail(SAETTA_ERR_BAD_ARG, "decode partial: row_step is 0 or 1");
+    if (!group->connected) return fail(SAETTA_ERR_BAD_ARG, "decode publish: the group is not connected");
+    if (group->device != op->device) return fail(SAETTA_ERR_BAD_ARG, "decode publish: op and group live on different devices");
+    if (m > group->rows_max || op->heads != group->heads) return fail(SAETTA_ERR_BAD_SHAPE, "decode publish: the group was made for another shape");
+    return decode_run(op, m, q_dev, view_of_cache(cache), cache->capacity, nullptr, nullptr, group->staging, row_step,
+                      params_dev, (cudaStream_t)stream, group);
 }
 
 int saetta_merge_partials(int device, const float *parts_dev, size_t ranks, size_t rows, size_t heads,

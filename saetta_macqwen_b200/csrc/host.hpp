@@ -8,6 +8,8 @@
 // and declare the kernel launchers implemented in the .cu files.
 #pragma once
 
+#include <cstring>
+
 #include <vector>
 
 #include "common.cuh"
@@ -79,6 +81,39 @@ struct saetta_att_gemm {
     uint32_t *status = nullptr;
 };
 
+// peer.cu: where one rank's partial goes in the mailboxes of the ranks of a box.
+namespace saetta {
+constexpr int kMaxPeers = 8;
+struct PeerPush {
+    unsigned long long *parts[kMaxPeers]; // each rank's mailbox: [2 slots][world][slot_floats] words of (value, exchange number)
+    uint32_t *seq_done;                   // this rank's counter of exchanges collected
+    uint32_t *seq_sent;                   // ... and published
+    uint32_t world, rank, slot_floats;
+};
+// One mailbox word: a float with the number of the exchange it belongs to, written by one 64-bit
+// store so that the reader sees both or neither.
+__host__ __device__ inline unsigned long long peer_word(float v, uint32_t seq) {
+#ifdef __CUDA_ARCH__
+    return (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(v);
+#else
+    uint32_t b;
+    memcpy(&b, &v, 4);
+    return (static_cast<unsigned long long>(seq) << 32) | b;
+#endif
+}
+
+} // namespace saetta
+
+struct saetta_peer_group {
+    int device = 0, rank = 0, world = 1;
+    size_t rows_max = 0, heads = 0, slot_floats = 0;
+    void *mailbox = nullptr; // the slots, then the two exchange counters and the status word
+    float *staging = nullptr;
+    void *peer_base[saetta::kMaxPeers] = {};
+    bool connected = false;
+    saetta::PeerPush push = {};
+    size_t words_offset() const { return 2 * size_t(world) * slot_floats * sizeof(unsigned long long); }
+};
 namespace saetta {
 
 using QuantRows = saetta_quant_rows;
@@ -102,6 +137,9 @@ struct KvView {
     const void *ks = nullptr, *kz = nullptr, *vs = nullptr, *vz = nullptr;
     uint32_t kv_heads = 2;
 };
+
+// Publishes the partial in the group's staging buffer (rows x heads x kPartStride floats).
+int launch_peer_publish(saetta_peer_group *g, size_t rows, cudaStream_t stream);
 
 // One sequence-segment of a batched launch (decode_quant.cu reads these).
 struct Segment {
@@ -139,9 +177,11 @@ int decode_exact_configure(int device);
 //   logical: parts [part][row][head][kPartStride] (decode_exact.cu, other ranks).
 // With out == null the merged (O, m, l) is written to part_out in the logical
 // layout instead of the gated result.
+// With `push` non-null the merged partial goes, instead of part_out, into this rank's place
+// in every peer's mailbox (see peer.cu).
 int launch_merge_frag(const float *parts, uint32_t nparts, const uint32_t *first_part,
                       uint32_t rows, uint32_t kv_heads, const float *q_and_gate, float *out,
-                      float *part_out, cudaStream_t stream);
+                      float *part_out, cudaStream_t stream, const PeerPush *push = nullptr);
 int launch_merge_logical(const float *parts, uint32_t nparts, uint32_t rows, uint32_t heads,
                          const float *q_and_gate, float *out, float *part_out,
                          cudaStream_t stream);

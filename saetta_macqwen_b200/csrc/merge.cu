@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(kMergeGroups * kMergeElems)
 merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
                   const uint32_t *__restrict__ first_part, uint32_t rows, uint32_t kv_heads,
                   const float *__restrict__ q_and_gate, float *__restrict__ out,
-                  float *__restrict__ part_out) {
+                  float *__restrict__ part_out, const PeerPush push) {
     __shared__ float w_s[kMergeMaxParts][8]; // first m, then the weight 2^(m_p - M), per part and head
     __shared__ float l_s[kMergeMaxParts][8];
     __shared__ float M_s[8], L_s[8];
@@ -36,6 +36,7 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
     const uint32_t row = blockIdx.y / kv_heads, kv = blockIdx.y % kv_heads;
     pdl_wait(); // the partials come from the kernel before
     pdl_launch_dependents();
+    const uint32_t xseq = push.world ? *push.seq_done + 1 : 0; // the exchange this launch publishes
     uint32_t p0 = 0, p1 = nparts;
     if (first_part) {
         p0 = first_part[row];
@@ -115,22 +116,37 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
     if (out) {
         const float g = q_and_gate[rh * 2 * kDim + kDim + dim];
         out[rh * kDim + dim] = sum / l * gate_of(g);
-    } else {
+    } else if (!push.world) {
         part_out[rh * kPartStride + dim] = sum;
         if (dim == 0) {
             part_out[rh * kPartStride + kPartM] = M;
             part_out[rh * kPartStride + kPartL] = l;
         }
+    } else {
+        // Straight into this rank's place in every rank's mailbox (remote stores over NVLink, this
+        // rank's own copy included).  Every word carries the exchange number, so the reader needs no
+        // flag and this kernel no fence: a word is there once its number is.
+        const size_t at = (size_t(xseq & 1) * push.world + push.rank) * push.slot_floats + rh * kPartStride;
+        for (uint32_t r = 0; r < push.world; r++) {
+            unsigned long long *dst = push.parts[r] + at;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + dim), "l"(peer_word(sum, xseq)) : "memory");
+            if (dim == 0) {
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + kPartM), "l"(peer_word(M, xseq)) : "memory");
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + kPartL), "l"(peer_word(l, xseq)) : "memory");
+            }
+        }
+        if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) *push.seq_sent = xseq; // read by the collecting kernel only
     }
 }
 
 int launch_merge_frag(const float *parts, uint32_t nparts, const uint32_t *first_part,
                       uint32_t rows, uint32_t kv_heads, const float *q_and_gate, float *out,
-                      float *part_out, cudaStream_t stream) {
+                      float *part_out, cudaStream_t stream, const PeerPush *push) {
     if (!rows) return SAETTA_OK;
+    PeerPush none = {};
     SAETTA_CUDA(launch_pdl(merge_frag_kernel, dim3(kFragFloats / kMergeElems, rows * kv_heads),
                            dim3(kMergeGroups * kMergeElems), 0, stream, parts, nparts, first_part, rows, kv_heads,
-                           q_and_gate, out, part_out));
+                           q_and_gate, out, part_out, push ? *push : none));
     return SAETTA_OK;
 }
 

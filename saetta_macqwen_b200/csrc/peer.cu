@@ -1,22 +1,30 @@
 // Split-KV merge across the GPUs of one box, fused with its exchange.
 //
 // No counterpart in the reference (one GPU).  Each rank's decode / prefill
-// kernels leave the (m, l, O) partial of its KV shard in a local staging
-// buffer.  Instead of an all-gather followed by a merge, ONE kernel per rank
-// waits for every peer's partial to be published and reads it straight out of
-// the peer's memory over NVLink (plain peer loads through NVSwitch; no
-// multicast, no library kernel on peer memory), merging and gating as it goes.
+// kernels produce the (m, l, O) partial of its KV shard.  Instead of an
+// all-gather followed by a merge, the kernel that finishes the partial stores
+// it straight into every peer's mailbox over NVLink (plain peer stores through
+// NVSwitch; no multicast, no library kernel on peer memory), and ONE kernel per
+// rank polls its own memory and merges and gates what has arrived.  A partial
+// crosses NVLink once, as fire-and-forget stores; nothing waits on a remote
+// read or on an acknowledgement.
 //
 // Mailbox protocol (memory shared between processes with CUDA IPC handles):
-// every rank owns two slots of partials and two flags.  publish_kernel copies
-// the staging partial into slot (seq & 1) and then stores seq into that slot's
-// flag with release semantics at system scope.  peer_merge_kernel acquires every
-// rank's flag until it equals seq, then reads the slots.  Two slots are enough:
-// a rank cannot publish exchange seq+2 before every peer has finished reading
-// exchange seq, because its own merge of seq+1 waits for the peers' seq+1 flags,
-// which they set only after their merge of seq.  The sequence number lives in
-// device memory, so a captured CUDA graph of these launches replays correctly.
-// The wait is bounded: after the limit the kernel sets a status bit and leaves.
+// every rank owns two slots, each with room for one partial per rank.  A slot
+// holds 64-bit words: a float and the number of the exchange it belongs to,
+// written by one 64-bit store.  For exchange number seq a rank writes its
+// partial into place (seq & 1, its rank) of every mailbox; the merge polls its
+// own slot seq & 1 until each word it needs carries seq, so a value is used as
+// soon as it has landed and no flag or fence sits between the ranks (one NVLink
+// crossing, not a round trip).  Two slots are enough: a rank cannot write
+// exchange seq+2 before every peer has finished reading exchange seq, because
+// its own merge of seq+1 waits for the peers' seq+1 words, which they send only
+// after their merge of seq.  The exchange numbers live in device memory, so a
+// captured CUDA graph of these launches replays correctly: the publishing
+// kernel reads the count of exchanges collected and writes the count sent, the
+// collecting kernel the other way round, so no kernel reads a word that one of
+// its own blocks writes.  The wait is bounded: after the limit the kernel sets
+// a status bit and leaves.
 #include <cstring>
 #include <new>
 
@@ -24,86 +32,94 @@
 
 namespace saetta {
 
-constexpr int kMaxPeers = 8;
-
-struct PeerPtrs {
-    const float *parts[kMaxPeers];       // each rank's [2][slot_floats]
-    const uint32_t *flags[kMaxPeers];    // each rank's [2]
-};
-
-__global__ void __launch_bounds__(256)
-publish_kernel(const float *__restrict__ staging, float *__restrict__ slots, uint32_t *flags, uint32_t *seq_dev,
-               uint32_t n_floats, uint32_t slot_floats) {
+// One block: copies the staging partial into every mailbox.
+__global__ void __launch_bounds__(1024)
+publish_kernel(const float *__restrict__ staging, const PeerPush push, uint32_t n_floats) {
     pdl_wait();
-    __shared__ uint32_t s_seq;
-    if (threadIdx.x == 0) s_seq = *seq_dev + 1;
-    __syncthreads();
-    const uint32_t s = s_seq;
-    float *dst = slots + size_t(s & 1) * slot_floats;
-    for (uint32_t i = threadIdx.x; i < n_floats; i += blockDim.x) dst[i] = staging[i];
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        *seq_dev = s;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags + (s & 1)), "r"(s) : "memory");
+    const uint32_t s = *push.seq_done + 1;
+    const size_t at = (size_t(s & 1) * push.world + push.rank) * push.slot_floats;
+    for (uint32_t i = threadIdx.x; i < n_floats; i += blockDim.x) {
+        const unsigned long long w = peer_word(staging[i], s);
+        for (uint32_t r = 0; r < push.world; r++)
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(push.parts[r] + at + i), "l"(w) : "memory");
     }
+    if (threadIdx.x == 0) *push.seq_sent = s;
 }
 
-// grid (heads, rows), 256 threads = one per dim.
-__global__ void __launch_bounds__(256)
-peer_merge_kernel(PeerPtrs peers, uint32_t world, const uint32_t *seq_dev, uint32_t slot_floats, uint32_t heads,
-                  const float *__restrict__ q_and_gate, float *__restrict__ out, uint32_t *status,
-                  uint32_t poll_limit) {
-    pdl_wait();
-    __shared__ uint32_t s_ok;
-    const uint32_t s = *seq_dev;
-    if (threadIdx.x < world) {
-        const uint32_t *flag = peers.flags[threadIdx.x] + (s & 1);
-        uint32_t v = 0, n = 0;
-        do {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v == s) break;
-            __nanosleep(200);
-        } while (++n < poll_limit);
-        if (v != s) atomicOr(status, kStatusFullTimeout);
+// Polls one mailbox word until it carries exchange number `s`; false after `limit` polls.
+__device__ __forceinline__ bool peer_poll(const unsigned long long *p, uint32_t s, uint32_t limit, float &v) {
+    for (uint32_t n = 0; n < limit; n++) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+        if (uint32_t(w >> 32) == s) {
+            v = __uint_as_float(uint32_t(w));
+            return true;
+        }
+        if (n > 16) __nanosleep(50);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) s_ok = (*reinterpret_cast<volatile uint32_t *>(status)) == 0;
-    __syncthreads();
-    if (!s_ok) return; // a peer never published: leave `out` as it is, the host sees the status word
+    return false;
+}
 
+// grid (heads, rows), 256 threads = one per dim.  Reads this rank's own mailbox only.
+__global__ void __launch_bounds__(256)
+peer_merge_kernel(const unsigned long long *__restrict__ slots, uint32_t world, const uint32_t *seq_sent,
+                  uint32_t *seq_done, uint32_t slot_floats, uint32_t heads, const float *__restrict__ q_and_gate,
+                  float *__restrict__ out, uint32_t *status, uint32_t poll_limit) {
+    pdl_wait();
+    __shared__ float ml_s[kMaxPeers][2];
+    __shared__ uint32_t s_bad;
+    const uint32_t s = *seq_sent;
     const uint32_t head = blockIdx.x, row = blockIdx.y, dim = threadIdx.x;
     const size_t rh = size_t(row) * heads + head;
+    const unsigned long long *base = slots + size_t(s & 1) * world * slot_floats + rh * kPartStride;
+    if (threadIdx.x == 0) s_bad = 0;
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x < 2 * world) // m and l of every rank
+        ok = peer_poll(base + size_t(threadIdx.x >> 1) * slot_floats + kPartM + (threadIdx.x & 1), s, poll_limit,
+                       ml_s[threadIdx.x >> 1][threadIdx.x & 1]);
+    float o[kMaxPeers];
+#pragma unroll
+    for (uint32_t r = 0; r < kMaxPeers; r++) {
+        o[r] = 0.f;
+        if (r < world && ok) ok = peer_poll(base + size_t(r) * slot_floats + dim, s, poll_limit, o[r]);
+    }
+    if (!ok) s_bad = 1;
+    __syncthreads();
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *seq_done = s;
+    if (s_bad) { // a peer never published: leave `out` as it is, the host sees the status word
+        if (threadIdx.x == 0) atomicOr(status, kStatusFullTimeout);
+        return;
+    }
     float M = -INFINITY;
-    for (uint32_t r = 0; r < world; r++)
-        M = fmaxf(M, __ldcv(peers.parts[r] + size_t(s & 1) * slot_floats + rh * kPartStride + kPartM));
+    for (uint32_t r = 0; r < world; r++) M = fmaxf(M, ml_s[r][0]);
     float acc = 0.f, l = 0.f;
-    for (uint32_t r = 0; r < world; r++) {
-        const float *pp = peers.parts[r] + size_t(s & 1) * slot_floats + rh * kPartStride;
-        const float mp = __ldcv(pp + kPartM);
-        if (mp == -INFINITY) continue;
-        const float w = exp2f(mp - M);
-        l = fmaf(__ldcv(pp + kPartL), w, l);
-        acc = fmaf(__ldcv(pp + dim), w, acc);
+#pragma unroll
+    for (uint32_t r = 0; r < kMaxPeers; r++) {
+        if (r >= world || ml_s[r][0] == -INFINITY) continue;
+        const float w = exp2f(ml_s[r][0] - M);
+        l = fmaf(ml_s[r][1], w, l);
+        acc = fmaf(o[r], w, acc);
     }
     const float g = q_and_gate[rh * 2 * kDim + kDim + dim];
     out[rh * kDim + dim] = acc / l * (1.0f / (1.0f + expf(-g)));
 }
 
+// The 32-bit words after the slots.
+static uint32_t *group_words(const saetta_peer_group *g) {
+    return reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(g->mailbox) + g->words_offset());
+}
+constexpr int kSeqDoneWord = 0, kSeqSentWord = 1, kStatusWord = 32;
+
+int launch_peer_publish(saetta_peer_group *g, size_t rows, cudaStream_t stream) {
+    const uint32_t n = uint32_t(rows * g->heads * kPartStride);
+    SAETTA_CUDA(launch_pdl(publish_kernel, dim3(1), dim3(1024), 0, stream, (const float *)g->staging, g->push, n));
+    return SAETTA_OK;
+}
+
 } // namespace saetta
 
 using namespace saetta;
-
-struct saetta_peer_group {
-    int device = 0, rank = 0, world = 1;
-    size_t rows_max = 0, heads = 0, slot_floats = 0;
-    void *mailbox = nullptr; // [2][slot_floats] floats, then 2 flags, then the sequence number, then status
-    float *staging = nullptr;
-    void *peer_base[kMaxPeers] = {};
-    bool connected = false;
-    PeerPtrs ptrs = {};
-    size_t flags_offset() const { return 2 * slot_floats * sizeof(float); }
-};
 
 extern "C" {
 
@@ -119,7 +135,7 @@ int saetta_peer_group_create(int device, int rank, int world, size_t rows_max, s
     if (!g) return fail(SAETTA_ERR_NO_MEM, "peer group: host allocation");
     g->device = device, g->rank = rank, g->world = world, g->rows_max = rows_max, g->heads = heads;
     g->slot_floats = rows_max * heads * kPartStride;
-    const size_t bytes = g->flags_offset() + 256;
+    const size_t bytes = g->words_offset() + 256;
     cudaError_t e = cudaMalloc(&g->mailbox, bytes);
     if (e == cudaSuccess) e = cudaMemset(g->mailbox, 0, bytes);
     if (e == cudaSuccess) e = cudaMalloc((void **)&g->staging, g->slot_floats * sizeof(float));
@@ -148,9 +164,10 @@ int saetta_peer_group_connect(saetta_peer_group *g, const uint8_t *handles /* [w
             memcpy(&h, handles + size_t(r) * 64, 64);
             SAETTA_CUDA(cudaIpcOpenMemHandle(&g->peer_base[r], h, cudaIpcMemLazyEnablePeerAccess));
         }
-        g->ptrs.parts[r] = reinterpret_cast<const float *>(g->peer_base[r]);
-        g->ptrs.flags[r] = reinterpret_cast<const uint32_t *>(reinterpret_cast<const char *>(g->peer_base[r]) + g->flags_offset());
+        g->push.parts[r] = reinterpret_cast<unsigned long long *>(g->peer_base[r]);
     }
+    g->push.seq_done = group_words(g) + kSeqDoneWord, g->push.seq_sent = group_words(g) + kSeqSentWord;
+    g->push.world = uint32_t(g->world), g->push.rank = uint32_t(g->rank), g->push.slot_floats = uint32_t(g->slot_floats);
     g->connected = true;
     return SAETTA_OK;
 }
@@ -167,28 +184,35 @@ void saetta_peer_group_destroy(saetta_peer_group *g) {
 
 float *saetta_peer_group_staging(saetta_peer_group *g) { return g ? g->staging : nullptr; }
 
-int saetta_peer_merge(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev, void *stream) {
-    if (!g || !q_and_gate_dev || !out_dev) return fail(SAETTA_ERR_BAD_ARG, "peer merge: null pointer");
+static int peer_check(const saetta_peer_group *g, size_t rows, const void *a, const void *b) {
+    if (!g || !a || !b) return fail(SAETTA_ERR_BAD_ARG, "peer merge: null pointer");
     if (!g->connected) return fail(SAETTA_ERR_BAD_ARG, "peer merge: the group is not connected");
     if (!rows || rows > g->rows_max) return fail(SAETTA_ERR_BAD_SHAPE, "peer merge: more rows than the group was made for");
-    DeviceGuard guard(g->device);
-    auto st = (cudaStream_t)stream;
-    char *base = reinterpret_cast<char *>(g->mailbox);
-    uint32_t *flags = reinterpret_cast<uint32_t *>(base + g->flags_offset());
-    uint32_t *seq = flags + 16, *status = flags + 32;
-    const uint32_t n = uint32_t(rows * g->heads * kPartStride);
-    SAETTA_CUDA(launch_pdl(publish_kernel, dim3(1), dim3(256), 0, st, (const float *)g->staging,
-                           reinterpret_cast<float *>(base), flags, seq, n, uint32_t(g->slot_floats)));
-    SAETTA_CUDA(launch_pdl(peer_merge_kernel, dim3(unsigned(g->heads), unsigned(rows)), dim3(256), 0, st, g->ptrs,
-                           uint32_t(g->world), (const uint32_t *)seq, uint32_t(g->slot_floats), uint32_t(g->heads),
-                           q_and_gate_dev, out_dev, status, 2000000u));
     return SAETTA_OK;
+}
+
+int saetta_peer_collect(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev, void *stream) {
+    if (int rc = peer_check(g, rows, q_and_gate_dev, out_dev)) return rc;
+    DeviceGuard guard(g->device);
+    uint32_t *words = group_words(g);
+    SAETTA_CUDA(launch_pdl(peer_merge_kernel, dim3(unsigned(g->heads), unsigned(rows)), dim3(256), 0, (cudaStream_t)stream,
+                           (const unsigned long long *)g->mailbox, uint32_t(g->world),
+                           (const uint32_t *)(words + kSeqSentWord), words + kSeqDoneWord, uint32_t(g->slot_floats),
+                           uint32_t(g->heads), q_and_gate_dev, out_dev, words + kStatusWord, 1000000u));
+    return SAETTA_OK;
+}
+
+int saetta_peer_merge(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev, void *stream) {
+    if (int rc = peer_check(g, rows, q_and_gate_dev, out_dev)) return rc;
+    DeviceGuard guard(g->device);
+    if (int rc = launch_peer_publish(g, rows, (cudaStream_t)stream)) return rc;
+    return saetta_peer_collect(g, rows, q_and_gate_dev, out_dev, stream);
 }
 
 int saetta_peer_group_status(saetta_peer_group *g, void *stream, uint32_t *status) {
     if (!g || !status) return fail(SAETTA_ERR_BAD_ARG, "peer status: null pointer");
     DeviceGuard guard(g->device);
-    const uint32_t *dev = reinterpret_cast<const uint32_t *>(reinterpret_cast<const char *>(g->mailbox) + g->flags_offset()) + 32;
+    const uint32_t *dev = group_words(g) + kStatusWord;
     SAETTA_CUDA(cudaMemcpyAsync(status, dev, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     SAETTA_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (*status) return fail(SAETTA_ERR_TIMEOUT, "a peer did not publish its partial in time");

@@ -1,7 +1,8 @@
-"""Split-KV decode over two GPUs with the fused peer-memory merge: each rank
-holds half of the sequence, computes its (m, l, O) partial, and one kernel per
-rank reads the other rank's partial over NVLink and merges.  Needs two GPUs
-(skipped otherwise); the ranks are separate processes, as in production."""
+"""Split-KV decode over several GPUs with the exchange fused into the kernels:
+each rank holds a slice of the sequence, stores its (m, l, O) partial into every
+rank's mailbox over NVLink, and merges what arrived from local memory.  Needs
+two GPUs or more (skipped otherwise); the ranks are separate processes, as in
+production."""
 import os
 
 import numpy as np
@@ -42,12 +43,17 @@ def _rank(rank, world, port, tokens, m, bits, out_q):
     out = torch.zeros(m * HEADS * DIM, device="cuda")
     qd, gd = dev(q), dev(qg)
     worst = 0.0
-    kr, vr = o.round_trip(keys, bits), o.round_trip(values, bits)
+    rt = (lambda x: o.round_trip(x, bits)) if bits in (4, 8) else o.round_f16
+    kr, vr = rt(keys), rt(values)
     want = o.attention_rows(q, qg, kr, vr, [pos + r + 1 for r in range(m)], threads=4)
-    for _ in range(3):  # several exchanges in a row: both mailbox slots get used
+    for it in range(4):  # several exchanges in a row: both mailbox slots get used
         out.zero_()
-        op.partial_cache(m, qd, cache, group.staging, p, row_step=step)
-        group.merge(m, gd, out)
+        if it % 2 == 0:  # the decode's merge kernel stores the partial into the mailboxes itself
+            op.publish_cache(m, qd, cache, group, p, row_step=step)
+            group.collect(m, gd, out)
+        else:            # any partial in the staging buffer: publish, then collect
+            op.partial_cache(m, qd, cache, group.staging, p, row_step=step)
+            group.merge(m, gd, out)
         torch.cuda.synchronize()
         assert group.status() == 0
         worst = max(worst, float(np.abs(out.cpu().numpy().reshape(m, HEADS, DIM) - want).max()))
@@ -56,20 +62,20 @@ def _rank(rank, world, port, tokens, m, bits, out_q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("bits,m", [(8, 1), (8, 4)])
-def test_two_ranks_merge_over_peer_memory(bits, m):
+@pytest.mark.parametrize("bits,m,world", [(8, 1, 2), (8, 4, 2), (4, 2, 2), (16, 1, 2), (8, 2, 4), (8, 1, 8)])
+def test_ranks_merge_through_peer_mailboxes(bits, m, world):
     import torch
     import torch.multiprocessing as mp
 
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
-    port = 29700 + (os.getpid() + m) % 1000
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, 3000, m, bits, out_q)) for r in range(2)]
+    port = 29700 + (os.getpid() + 7 * m + world) % 1000
+    procs = [ctx.Process(target=_rank, args=(r, world, port, 3000, m, bits, out_q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [out_q.get(timeout=180) for _ in procs]
+    results = [out_q.get(timeout=240) for _ in procs]
     for p in procs:
         p.join(60)
         assert p.exitcode == 0
