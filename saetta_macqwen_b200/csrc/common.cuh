@@ -131,6 +131,12 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32
         : "memory");
 }
 
+// Asks the TMA engine to bring `bytes` contiguous bytes into L2; nothing waits for it.
+// Address 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void l2_prefetch(const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // D += A(16x16, row) * B(16x8, col), f16 operands, f32 accumulate.
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                         uint32_t a3, uint32_t b0, uint32_t b1) {

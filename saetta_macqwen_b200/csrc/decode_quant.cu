@@ -46,6 +46,9 @@ constexpr int kKv = 2;        // kv heads covered by one stage
 constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in fragment order
 constexpr int kPartKv = kFragFloats + 16; // + m[8], l[8]
 constexpr float kLog2e = 1.4426950408889634f;
+// Tiles of a CTA's range pulled into L2 before the dependency wait.  Measured 0 / 4 / 8 / 16: four is best
+// (deeper prefetches queue ahead of the ring's own copies when the wait turns out to be short).
+constexpr int kPrefetchTiles = 4;
 constexpr float kRescale = 8.0f; // move the running maximum when it grows by more than 2^8
 
 template <int BITS>
@@ -131,6 +134,32 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         mbar_fence_init();
     }
     __syncthreads();
+#ifndef SAETTA_EXP_NO_PREFETCH
+    // While the kernel before this one drains, pull the head of this CTA's tile range into L2 (and
+    // warm the TLB).  The range comes from a possibly stale kv_len: it is only a hint, every value
+    // is read again after the wait; L2 is the point of coherence, so lines prefetched early still
+    // show what the kernel before writes afterwards.
+    if (warp == kWarps && lane == 0 && !a.segs) {
+        const uint32_t kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
+        const uint32_t longest = min(kv_hint + (a.m - 1) * a.row_step, a.capacity);
+        const uint32_t tiles = (longest + kTile - 1) / kTile;
+        const uint32_t tb = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
+        const uint32_t te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
+        const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
+        const size_t tok = size_t(tb) * kTile;
+        for (uint32_t t = 0; t < nt; t += 2) { // two tiles (32 KB of 8-bit codes) per request
+            const uint32_t n = min(nt - t, 2u);
+            l2_prefetch((const uint8_t *)a.seg.k + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
+            l2_prefetch((const uint8_t *)a.seg.v + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
+        }
+        if (nt) {
+            l2_prefetch((const uint8_t *)a.seg.ks + tok * St::kParamRow, nt * St::kParams);
+            l2_prefetch((const uint8_t *)a.seg.kz + tok * St::kParamRow, nt * St::kParams);
+            l2_prefetch((const uint8_t *)a.seg.vs + tok * St::kParamRow, nt * St::kParams);
+            l2_prefetch((const uint8_t *)a.seg.vz + tok * St::kParamRow, nt * St::kParams);
+        }
+    }
+#endif
     pdl_wait();              // q, the token parameters and the cache may come from the kernel before
     pdl_launch_dependents(); // the merge kernel may be scheduled as SMs free up; it waits for this grid
     DQ_MARK(5);
