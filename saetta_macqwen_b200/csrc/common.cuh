@@ -106,19 +106,24 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may itself block for a
-// short hardware-defined time) or as soon as *abort is set; returns false then.
+// Bounded wait: gives up about `limit` x 256 ns after its 64th poll (4,000,000: one second), or as
+// soon as *abort is set; returns false then.  The polls run back to back -- try_wait itself
+// suspends the thread for a short hardware-defined time -- because a sleep between polls would
+// delay the wake-up by more than the hand-offs between the roles of these kernels can afford.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
                                           volatile uint32_t *abort_flag,
                                           uint32_t limit = 4000000u) {
-    for (uint32_t n = 0; n < limit; n++) {
+    unsigned long long t0 = 0;
+    for (uint32_t n = 0;; n++) {
         if (mbar_test(bar, parity)) return true;
-        if (n > 64) {
+        if ((n & 63) == 63) {
             if (*abort_flag) return false;
-            __nanosleep(64);
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (!t0) t0 = t;
+            else if (t - t0 > (static_cast<unsigned long long>(limit) << 8)) return false;
         }
     }
-    return false;
 }
 
 // Bulk (TMA engine) copy of `bytes` contiguous bytes, global -> shared, signalling
