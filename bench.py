@@ -206,6 +206,36 @@ def prefill_point(sa, torch, pos, tokens, steps, warmup, stream, quant_bits=None
     return {"tflops": flops / ms / 1e9, "ms": ms, "flops": flops}
 
 
+def prep_point(sa, torch, tokens, bits, steps, warmup, stream):
+    """GB/s of attention prep fused with the quantised store for one prefill chunk: reads the q halves of
+    q_and_gate, k, v (f32), writes q as bf16 and the cache rows.  The inputs of consecutive steps are
+    distinct buffers, larger than L2 together."""
+    dev = torch.cuda.current_device()
+    copies = 6
+    qg = [torch.randn(tokens * HEADS * 2 * DIM, device="cuda") for _ in range(copies)]
+    k = [torch.randn(tokens * ROW, device="cuda") for _ in range(copies)]
+    v = [torch.randn(tokens * ROW, device="cuda") for _ in range(copies)]
+    qn, kn = torch.ones(DIM, device="cuda"), torch.ones(DIM, device="cuda")
+    q_out = torch.zeros(tokens * HEADS * DIM, dtype=torch.bfloat16, device="cuda")
+    cache = sa.GpuKvCache(dev, bits, tokens)
+    pp = sa.PrepParams(HEADS, KV, DIM, 64, 1.0e7, 1.0e-6)
+    fn = lambda i: sa.attention_prep(pp, tokens, qg[i % copies], k[i % copies], v[i % copies], qn, kn, q_out, sa.BF16,
+                                     cache, pos=0, stream=stream)
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            fn(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = tokens * (HEADS * DIM * 4 + 2 * ROW * 4 + HEADS * DIM * 2 + BYTES_PER_TOKEN[bits])
+    return {"gbs": nbytes / ms / 1e6, "ms": ms, "bytes": nbytes}
+
+
 _CPU_DATA = {}
 
 
@@ -218,6 +248,7 @@ def point_table(sa, torch, stream, s, w):
         "verify_m4_32k_8bit": lambda: decode_point(sa, torch, 32768, 8, 4, 10, s, w, stream),
         "batch64_ragged_8bit": lambda: batch_point(sa, torch, 8, min(s, 3), 2, stream),
         "batch64_ragged_4bit": lambda: batch_point(sa, torch, 4, min(s, 3), 2, stream),
+        "prep_store_4k_8bit": lambda: prep_point(sa, torch, 4096, 8, max(s, 12), w, stream),
         "prefill_4k_pos0_bf16": lambda: prefill_point(sa, torch, 0, 4096, s, w, stream),
         "prefill_4k_pos32k_8bit": lambda: prefill_point(sa, torch, 32768, 4096, min(s, 5), 2, stream, quant_bits=8),
         "prefill_4k_pos128k_8bit": lambda: prefill_point(sa, torch, 131072, 4096, min(s, 3), 2, stream, quant_bits=8),
@@ -448,7 +479,7 @@ def main():
         s, w = max(5, args.steps // 2), 3
         table = point_table(sa, torch, stream, s, w)
         for name in ["decode_32k_8bit", "decode_128k_8bit", "decode_256k_4bit", "verify_m4_32k_8bit",
-                     "batch64_ragged_8bit", "batch64_ragged_4bit", "prefill_4k_pos0_bf16",
+                     "batch64_ragged_8bit", "batch64_ragged_4bit", "prep_store_4k_8bit", "prefill_4k_pos0_bf16",
                      "prefill_4k_pos32k_8bit", "prefill_4k_pos128k_8bit"]:
             fn = table[name]
             try:

@@ -63,7 +63,7 @@ typedef struct saetta_flash_params {
 
 /* Storage type of 16-bit tensors (the reference stores binary16; the tensor-core
  * prefill also takes bfloat16). */
-typedef enum saetta_dtype { SAETTA_F16 = 0, SAETTA_BF16 = 1 } saetta_dtype;
+typedef enum saetta_dtype { SAETTA_F16 = 0, SAETTA_BF16 = 1, SAETTA_F32 = -1 /* only where an entry point says so */ } saetta_dtype;
 
 /* ------------------------------------------------------------------ QuantRows
  * src/kv_quant.rs:158-283 `QuantRows`: the codes, scales and biases of one cache
@@ -134,6 +134,34 @@ int saetta_kv_cache_store(saetta_kv_cache *cache, const float *k_dev, const floa
                           const saetta_token_params *params_dev, size_t rows, void *stream);
 int saetta_kv_cache_store_at(saetta_kv_cache *cache, const float *k_dev, const float *v_dev,
                              size_t pos, size_t tokens, void *stream);
+/* ------------------------------------------------------------------ attention prep
+ * kernels/layers.metal:637-697 `PrepParams`, `attention_prep` (16-bit cache) and
+ * `attention_prep_float` + `QuantRows::record` (quantised cache), called from
+ * GpuAttention::record_store (src/gpu_layers.rs:373-411) and per row from
+ * record_rows (:483-507); for a chunk, the prefill's norm + rope_rows + store
+ * (src/prefill.rs:1607-1633, 1656-1666).  Per token: q = rope(rms_norm(q) * q_norm),
+ * k = rope(rms_norm(k) * k_norm), and k, v into the token's cache slot in
+ * whatever form the cache holds -- one launch, the keys never pass through
+ * memory as f32.  rows tokens at params_dev->position + r (decode / verify; read
+ * on the device, capturable) or, with params_dev NULL, at pos + r (prefill).
+ * q_and_gate_dev [rows][heads][2*head_dim] (q first), k_dev / v_dev
+ * [rows][kv_heads][head_dim] f32; q_out_dev [rows][heads][head_dim] of q_dtype
+ * (SAETTA_F32 for decode, 16-bit for the prefill kernels); k_out_dev, when not
+ * NULL, also receives the normed and roped keys as f32 (what
+ * attention_prep_float leaves in k; may be k_dev itself).  The angle is formed
+ * in f64 as the CPU does (src/cpu/ops.rs:64-74), not in f32 as the Metal kernel. */
+typedef struct saetta_prep_params {
+    uint32_t heads, kv_heads, head_dim;
+    uint32_t rope_dims; /* rotary dims (2 * half_dims), a multiple of 16, at most 128 */
+    float rope_theta;
+    float eps;
+} saetta_prep_params;
+int saetta_attention_prep(saetta_prep_params p, size_t rows, const float *q_and_gate_dev,
+                          const float *k_dev, const float *v_dev, const float *q_norm_dev,
+                          const float *k_norm_dev, void *q_out_dev, int q_dtype,
+                          saetta_kv_cache *cache, const saetta_token_params *params_dev,
+                          size_t pos, float *k_out_dev, void *stream);
+
 /* dtype of a 16-bit cache's rows (SAETTA_F16 unless set otherwise before use). */
 int saetta_kv_cache_set_dtype(saetta_kv_cache *cache, int dtype);
 

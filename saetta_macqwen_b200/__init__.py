@@ -53,6 +53,12 @@ class FlashParams(C.Structure):
                 ("scale", C.c_float)]
 
 
+class PrepParams(C.Structure):
+    """kernels/layers.metal:637-644 `PrepParams` (theta instead of its log2, rope_dims instead of half)."""
+    _fields_ = [("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("rope_dims", C.c_uint32),
+                ("rope_theta", C.c_float), ("eps", C.c_float)]
+
+
 def build(verbose=False):
     """Compiles the library in-tree with nvcc for sm_100a (make in csrc/)."""
     cmd = ["make", "-C", os.path.join(_HERE, "csrc"), "-j8"]
@@ -87,6 +93,7 @@ SYMBOLS = {
     "saetta_kv_cache_store": (_I, [_P, _P, _P, _P, _Z, _P]),
     "saetta_kv_cache_store_at": (_I, [_P, _P, _P, _Z, _Z, _P]),
     "saetta_kv_cache_set_dtype": (_I, [_P, _I]),
+    "saetta_attention_prep": (_I, [PrepParams, _Z, _P, _P, _P, _P, _P, _P, _I, _P, _P, _Z, _P, _P]),
     "saetta_row_backup_create": (_I, [_PP]),
     "saetta_row_backup_destroy": (None, [_P]),
     "saetta_row_backup_save": (_I, [_P, _PP, _Z, _Z, _Z, _P]),
@@ -372,6 +379,17 @@ class DecodeBatch:
         if getattr(self, "h", None) and _lib is not None:
             _lib.saetta_decode_batch_destroy(self.h)
             self.h = None
+
+
+def attention_prep(p, rows, q_and_gate, k, v, q_norm, k_norm, q_out, q_dtype, cache, params=None, pos=0, k_out=None,
+                   stream=None):
+    """GpuAttention::record_store / the prep loop of record_rows / the prefill's norm + rope + store
+    (src/gpu_layers.rs:373-411, 483-507, src/prefill.rs:1607-1666): q normed and roped into q_out,
+    k normed and roped and v as it is into the cache slots of `rows` tokens, at params.position + r
+    (device-side) or at pos + r."""
+    _check(lib().saetta_attention_prep(p, rows, ptr(q_and_gate), ptr(k), ptr(v), ptr(q_norm), ptr(k_norm), ptr(q_out),
+                                       q_dtype, cache.h, ptr(params) if params is not None else None, pos,
+                                       ptr(k_out) if k_out is not None else None, _stream(stream)))
 
 
 def merge_partials(device, parts, ranks, rows, heads, q_and_gate, out, stream=None):

@@ -44,3 +44,18 @@ def quant_rows_from_oracle(sa, oracle, x, bits, capacity):
     sc[: tokens * 8] = torch.from_numpy(s.view(np.int16)).cuda()
     bi[: tokens * 8] = torch.from_numpy(z.view(np.int16)).cuda()
     return sa.QuantRows.wrap(0, bits, ROW, capacity, d, sc, bi)
+
+
+def read_dev(ptr, nbytes):
+    """`nbytes` of device memory at the raw address `ptr`, as a numpy byte array."""
+    import ctypes
+
+    import torch
+
+    torch.cuda.synchronize()
+    out = np.empty(nbytes, np.uint8)
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    rc = rt.cudaMemcpy(out.ctypes.data, ctypes.c_void_p(ptr), nbytes, 2)  # cudaMemcpyDeviceToHost
+    assert rc == 0, f"cudaMemcpy failed with {rc}"
+    return out
