@@ -134,6 +134,40 @@ int saetta_kv_cache_store(saetta_kv_cache *cache, const float *k_dev, const floa
                           const saetta_token_params *params_dev, size_t rows, void *stream);
 int saetta_kv_cache_store_at(saetta_kv_cache *cache, const float *k_dev, const float *v_dev,
                              size_t pos, size_t tokens, void *stream);
+/* ------------------------------------------------------------------ record / replay
+ * src/plan.rs:52-260 `Plan` and `Built`: dispatches recorded once and replayed
+ * for every token, the only thing that changes being the TokenParams buffer.
+ * On CUDA the recording is a stream capture and the replay a graph launch:
+ *   saetta_plan_create                       Plan::new
+ *   saetta_plan_params                       Plan::params (device pointer: pass it to every entry point
+ *                                            that takes params_dev while recording)
+ *   saetta_plan_begin ... entry points on saetta_plan_stream() ... saetta_plan_build
+ *                                            the ops (`op` = stream order), then Plan::build
+ *   saetta_plan_parallel_begin / _end        `op_parallel`: a side stream whose ops do not depend on the
+ *                                            op before them; _end joins it back
+ *   saetta_plan_set_params(token, position)  Plan::set_params(TokenParams::new(token, position))
+ *   saetta_plan_run / _commit + _wait / _run_timed   Built::run / commit + Pending::wait / run_timed
+ *   saetta_plan_len                          Plan::len (kernel launches recorded)
+ * The host copy of TokenParams is uploaded by the graph's first node, so a
+ * replay is a single graph launch.  Entry points that allocate (resize, the
+ * first encode that grows a staging copy) must not be recorded.
+ * Plan::build_where (profiling subsets) has no counterpart. */
+typedef struct saetta_plan saetta_plan;
+int saetta_plan_create(int device, saetta_plan **out);
+void saetta_plan_destroy(saetta_plan *plan);
+const saetta_token_params *saetta_plan_params(const saetta_plan *plan);
+void *saetta_plan_stream(const saetta_plan *plan);
+int saetta_plan_begin(saetta_plan *plan);
+int saetta_plan_parallel_begin(saetta_plan *plan, void **side_stream);
+int saetta_plan_parallel_end(saetta_plan *plan);
+int saetta_plan_build(saetta_plan *plan);
+int saetta_plan_len(const saetta_plan *plan, size_t *ops);
+int saetta_plan_set_params(saetta_plan *plan, uint32_t token, uint32_t position);
+int saetta_plan_commit(saetta_plan *plan);
+int saetta_plan_wait(saetta_plan *plan);
+int saetta_plan_run(saetta_plan *plan);
+int saetta_plan_run_timed(saetta_plan *plan, float *gpu_ms);
+
 /* ------------------------------------------------------------------ attention prep
  * kernels/layers.metal:637-697 `PrepParams`, `attention_prep` (16-bit cache) and
  * `attention_prep_float` + `QuantRows::record` (quantised cache), called from

@@ -93,6 +93,20 @@ SYMBOLS = {
     "saetta_kv_cache_store": (_I, [_P, _P, _P, _P, _Z, _P]),
     "saetta_kv_cache_store_at": (_I, [_P, _P, _P, _Z, _Z, _P]),
     "saetta_kv_cache_set_dtype": (_I, [_P, _I]),
+    "saetta_plan_create": (_I, [_I, _PP]),
+    "saetta_plan_destroy": (None, [_P]),
+    "saetta_plan_params": (_P, [_P]),
+    "saetta_plan_stream": (_P, [_P]),
+    "saetta_plan_begin": (_I, [_P]),
+    "saetta_plan_parallel_begin": (_I, [_P, _PP]),
+    "saetta_plan_parallel_end": (_I, [_P]),
+    "saetta_plan_build": (_I, [_P]),
+    "saetta_plan_len": (_I, [_P, C.POINTER(_Z)]),
+    "saetta_plan_set_params": (_I, [_P, _U32, _U32]),
+    "saetta_plan_commit": (_I, [_P]),
+    "saetta_plan_wait": (_I, [_P]),
+    "saetta_plan_run": (_I, [_P]),
+    "saetta_plan_run_timed": (_I, [_P, C.POINTER(C.c_float)]),
     "saetta_attention_prep": (_I, [PrepParams, _Z, _P, _P, _P, _P, _P, _P, _I, _P, _P, _Z, _P, _P]),
     "saetta_row_backup_create": (_I, [_PP]),
     "saetta_row_backup_destroy": (None, [_P]),
@@ -434,6 +448,87 @@ class PeerGroup:
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:
             _lib.saetta_peer_group_destroy(self.h)
+            self.h = None
+
+
+class Plan:
+    """src/plan.rs:52-260 `Plan` + `Built`: record once (stream capture), replay per token (graph launch).
+
+        plan = Plan(0)
+        with plan.recording():
+            sa.attention_prep(..., params=plan.params, stream=plan.stream)
+            op.record_cache(1, q, cache, qg, out, plan.params, stream=plan.stream)
+        plan.set_params(token, position); plan.run()
+    """
+
+    def __init__(self, device):
+        h = C.c_void_p()
+        _check(lib().saetta_plan_create(device, C.byref(h)))
+        self.h = h
+
+    @property
+    def params(self):
+        """Device address of the plan's TokenParams (an int: every entry point accepts it as params)."""
+        return lib().saetta_plan_params(self.h)
+
+    @property
+    def stream(self):
+        """The raw stream the ops are recorded on (an int: every entry point accepts it as stream)."""
+        return lib().saetta_plan_stream(self.h)
+
+    def begin(self):
+        _check(lib().saetta_plan_begin(self.h))
+
+    def build(self):
+        _check(lib().saetta_plan_build(self.h))
+
+    def recording(self):
+        plan = self
+
+        class _Rec:
+            def __enter__(self):
+                plan.begin()
+                return plan
+
+            def __exit__(self, et, ev, tb):
+                plan.build()
+                return False
+
+        return _Rec()
+
+    def parallel_begin(self):
+        s = C.c_void_p()
+        _check(lib().saetta_plan_parallel_begin(self.h, C.byref(s)))
+        return s.value
+
+    def parallel_end(self):
+        _check(lib().saetta_plan_parallel_end(self.h))
+
+    def __len__(self):
+        n = C.c_size_t()
+        _check(lib().saetta_plan_len(self.h, C.byref(n)))
+        return n.value
+
+    def set_params(self, token, position):
+        _check(lib().saetta_plan_set_params(self.h, token, position))
+
+    def commit(self):
+        _check(lib().saetta_plan_commit(self.h))
+
+    def wait(self):
+        _check(lib().saetta_plan_wait(self.h))
+
+    def run(self):
+        _check(lib().saetta_plan_run(self.h))
+
+    def run_timed(self):
+        ms = C.c_float()
+        _check(lib().saetta_plan_run_timed(self.h, C.byref(ms)))
+        return ms.value
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_plan_destroy(self.h)
             self.h = None
 
 
