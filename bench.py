@@ -429,27 +429,57 @@ def main():
     step_bytes = world * LAYERS * CTX * BYTES_PER_TOKEN[8]
     value = step_bytes / ms / 1e6  # GB/s
 
-    # ---- end to end through the C ABI with host buffers: per layer the token's q,
-    # q_and_gate and new K/V rows come from pinned host memory, the row is appended
-    # (quantise-on-append), attention runs, and the output goes back to the host.
-    h_q = torch.randn(HEADS * DIM).pin_memory()
-    h_qg = torch.randn(HEADS * 2 * DIM).pin_memory()
-    h_k, h_v = torch.randn(ROW).pin_memory(), torch.randn(ROW).pin_memory()
-    h_out = torch.zeros(HEADS * DIM).pin_memory()
-    d_k, d_v = torch.zeros(ROW, device="cuda"), torch.zeros(ROW, device="cuda")
-    h2d = LAYERS * 4 * (h_q.numel() + h_qg.numel() + 2 * ROW)
-    d2h = LAYERS * 4 * h_out.numel()
+    # ---- end to end through the C ABI with host buffers.  Per step the token's raw q_and_gate, k and v
+    # of every layer sit in one pinned host buffer; the step uploads them, and per layer runs
+    # attention prep (q/k norm + RoPE, the new K/V row quantised into the cache) and the attention,
+    # then reads every layer's output back and synchronises.  With no library collective inside,
+    # the whole step -- both copies included -- is recorded once in a Plan (the reference's
+    # record-once / replay-per-token runtime) and replayed with one graph launch.
+    per_layer = HEADS * 2 * DIM + 2 * ROW
+    h_in = torch.randn(LAYERS * per_layer).pin_memory()
+    d_in = torch.zeros(LAYERS * per_layer, device="cuda")
+    d_q = torch.zeros(LAYERS * HEADS * DIM, device="cuda")
+    d_out = torch.zeros(LAYERS * HEADS * DIM, device="cuda")
+    h_out = torch.zeros(LAYERS * HEADS * DIM).pin_memory()
+    q_norm, k_norm = torch.ones(DIM, device="cuda"), torch.ones(DIM, device="cuda")
+    prep = sa.PrepParams(HEADS, KV, DIM, 64, 1.0e7, 1.0e-6)
+    h2d, d2h = 4 * h_in.numel(), 4 * h_out.numel()
 
-    def e2e_step():
-        for c in caches:
-            q.copy_(h_q, non_blocking=True)
-            qg.copy_(h_qg, non_blocking=True)
-            d_k.copy_(h_k, non_blocking=True)
-            d_v.copy_(h_v, non_blocking=True)
-            c.store(d_k, d_v, params, rows=1, stream=stream)
-            attend(c)
-            h_out.copy_(out, non_blocking=True)
-        stream.synchronize()  # the caller reads the result
+    def layer_views(l):
+        base = l * per_layer
+        return (d_in[base:base + HEADS * 2 * DIM], d_in[base + HEADS * 2 * DIM:base + HEADS * 2 * DIM + ROW],
+                d_in[base + HEADS * 2 * DIM + ROW:base + per_layer], d_q[l * HEADS * DIM:(l + 1) * HEADS * DIM],
+                d_out[l * HEADS * DIM:(l + 1) * HEADS * DIM])
+
+    def e2e_body(pp, st):
+        d_in.copy_(h_in, non_blocking=True)
+        for l, c in enumerate(caches):
+            lqg, lk, lv, lq, lout = layer_views(l)
+            sa.attention_prep(prep, 1, lqg, lk, lv, q_norm, k_norm, lq, sa.F32, c, params=pp, stream=st)
+            if world == 1:
+                op.record_cache(1, lq, c, lqg, lout, pp, stream=st)
+            elif group is not None:
+                op.publish_cache(1, lq, c, group, pp, row_step=0, stream=st)
+                group.collect(1, lqg, lout, stream=st)
+            else:
+                op.partial_cache(1, lq, c, part, pp, row_step=0, stream=st)
+                dist.all_gather_into_tensor(gathered, part)
+                sa.merge_partials(dev, gathered, world, 1, HEADS, lqg, lout, stream=st)
+        h_out.copy_(d_out, non_blocking=True)
+
+    if world == 1 or group is not None:
+        plan = sa.Plan(dev)
+        with torch.cuda.stream(torch.cuda.ExternalStream(plan.stream)):
+            with plan.recording():
+                e2e_body(plan.params, plan.stream)
+
+        def e2e_step():
+            plan.set_params(0, CTX - 1)
+            plan.run()  # one graph launch, then the wait: the caller reads the result
+    else:
+        def e2e_step():
+            e2e_body(params, stream)
+            stream.synchronize()
 
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
