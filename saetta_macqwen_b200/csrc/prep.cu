@@ -102,29 +102,36 @@ __device__ __forceinline__ void store8(void *dst, size_t at, const float (&x)[8]
     }
 }
 
-__global__ void __launch_bounds__(1024) attention_prep_kernel(const PrepArgs a) {
+__global__ void __launch_bounds__(1024, 2) attention_prep_kernel(const PrepArgs a) {
     __shared__ float sn[kPrepMaxHalf], cs[kPrepMaxHalf];
     const uint32_t row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t position = (a.params ? a.params->position : a.pos) + row;
-    if (threadIdx.x < a.half_dims) {
-        const double angle = double(position) * a.freq[threadIdx.x];
-        double s, c;
-        sincos(angle, &s, &c);
-        sn[threadIdx.x] = float(s), cs[threadIdx.x] = float(c);
-    }
-    __syncthreads();
-
     // warps 0..heads-1: query heads; then kv_heads key heads; then kv_heads value heads
     const bool is_q = warp < a.heads, is_k = !is_q && warp < a.heads + a.kv_heads;
     const uint32_t j = is_q ? warp : is_k ? warp - a.heads : warp - a.heads - a.kv_heads;
     const float *src = is_q   ? a.q_and_gate + (size_t(row) * a.heads + j) * 2 * kDim
                        : is_k ? a.k + (size_t(row) * a.kv_heads + j) * kDim
                               : a.v + (size_t(row) * a.kv_heads + j) * kDim;
-    float x[8];
-    {
-        const float4 v0 = reinterpret_cast<const float4 *>(src)[lane * 2], v1 = reinterpret_cast<const float4 *>(src)[lane * 2 + 1];
-        x[0] = v0.x, x[1] = v0.y, x[2] = v0.z, x[3] = v0.w, x[4] = v1.x, x[5] = v1.y, x[6] = v1.z, x[7] = v1.w;
+    // the loads go out first, so that the sines and cosines below are computed while they are in flight
+    const float4 v0 = reinterpret_cast<const float4 *>(src)[lane * 2], v1 = reinterpret_cast<const float4 *>(src)[lane * 2 + 1];
+    float wn[8];
+    if (is_q || is_k) {
+        const float4 *w = reinterpret_cast<const float4 *>((is_q ? a.q_norm : a.k_norm) + lane * 8);
+        const float4 w0 = w[0], w1 = w[1];
+        wn[0] = w0.x, wn[1] = w0.y, wn[2] = w0.z, wn[3] = w0.w, wn[4] = w1.x, wn[5] = w1.y, wn[6] = w1.z, wn[7] = w1.w;
     }
+    if (threadIdx.x < a.half_dims) {
+        // angle in f64 as the CPU forms it, brought into [-pi, pi] in f64 (2 pi in two pieces), then the
+        // f32 sine and cosine of the remainder: within 2 ulp of rounding the f64 functions
+        const double angle = double(position) * a.freq[threadIdx.x];
+        const double turns = rint(angle * 0.15915494309189535);
+        const double rem = fma(-turns, 2.4492935982947064e-16, fma(-turns, 6.283185307179586, angle));
+        float s, c;
+        sincosf(float(rem), &s, &c);
+        sn[threadIdx.x] = s, cs[threadIdx.x] = c;
+    }
+    __syncthreads();
+    float x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     if (is_q || is_k) {
         float ss = 0.f;
 #pragma unroll
@@ -132,9 +139,8 @@ __global__ void __launch_bounds__(1024) attention_prep_kernel(const PrepArgs a) 
 #pragma unroll
         for (int off = 16; off; off >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, off));
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(kDim)), a.eps)));
-        const float *w = (is_q ? a.q_norm : a.k_norm) + lane * 8;
 #pragma unroll
-        for (int e = 0; e < 8; e++) x[e] = __fmul_rn(x[e], __fmul_rn(scale, w[e]));
+        for (int e = 0; e < 8; e++) x[e] = __fmul_rn(x[e], __fmul_rn(scale, wn[e]));
         // RoPE: value i < half pairs with i + half.  Lanes whose dims lie below 2*half take part.
         const uint32_t half = a.half_dims; // a multiple of 8
         const uint32_t d0 = lane * 8;
