@@ -102,6 +102,22 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// 256-bit global accesses (one full 32-byte sector per thread); addresses 32-byte aligned.
+struct alignas(32) Float8 {
+    float v[8];
+};
+__device__ __forceinline__ Float8 ld_global_v8(const float *p) {
+    Float8 r;
+    asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]), "=f"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ void st_global_v8(float *p, const Float8 &r) {
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(r.v[0]), "f"(r.v[1]), "f"(r.v[2]),
+                 "f"(r.v[3]), "f"(r.v[4]), "f"(r.v[5]), "f"(r.v[6]), "f"(r.v[7])
+                 : "memory");
+}
 __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -470,15 +486,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 for (int j = 0; j < 8; j++) prefetch_l2(gpf + j * 128);
             }
             {   // this thread's Q row into tensor memory (two values per column), once the MMAs
-                // of the tile before no longer read the old one
-                PF_T0();
-                if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
-                tc_fence_after();
+                // of the tile before no longer read the old one.  The row does not depend on that wait:
+                // its first quarter is fetched into registers and the rest pulled into L2 before it.
                 const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim);
                 // loads of the next 64 values are issued before the store of the current ones
                 uint4 qv[2][8];
+                if (row_live) {
 #pragma unroll
-                for (int k = 0; k < 8; k++) qv[0][k] = row_live ? qrow[k] : make_uint4(0u, 0u, 0u, 0u);
+                    for (int j = 1; j < 4; j++) prefetch_l2(reinterpret_cast<const char *>(qrow) + j * 128);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) qv[0][j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
+                PF_T0();
+                if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+                tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     if (c + 1 < 4) {
@@ -509,11 +530,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             // The gate values do not depend on O: the first 32 are requested before O is final,
             // and each later chunk one step ahead of its use (two register buffers).
             const bool gated = row_live && p.out;
-            const float4 *gp = reinterpret_cast<const float4 *>(p.q_and_gate + (gated ? rh * 2 * kDim + kDim : 0));
-            float4 gq[2][8];
+            // (256-bit loads and stores: a thread's accesses are whole 32-byte sectors of its row)
+            const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim : 0);
+            Float8 gq[2][4];
             if (gated) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) gq[0][j] = gp[j];
+                for (int j = 0; j < 4; j++) gq[0][j] = ld_global_v8(gp + j * 8);
             }
             PF_T0();
             if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
@@ -526,7 +548,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             for (int ch = 0; ch < 8; ch++) {
                 if (gated && ch + 1 < 8) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) gq[(ch + 1) & 1][j] = gp[(ch + 1) * 8 + j];
+                    for (int j = 0; j < 4; j++) gq[(ch + 1) & 1][j] = ld_global_v8(gp + (ch + 1) * 32 + j * 8);
                 }
                 const int c = ch * 32;
                 uint32_t o[32];
@@ -534,16 +556,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 tmem_wait_ld();
                 if (!row_live) continue;
                 if (p.out) {
-                    float4 *op = reinterpret_cast<float4 *>(p.out + rh * kDim + c);
+                    float *op = p.out + rh * kDim + c;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const float4 gt = gq[ch & 1][j];
-                        float4 v;
-                        v.x = __uint_as_float(o[4 * j]) * __fdividef(inv_l, 1.f + __expf(-gt.x));
-                        v.y = __uint_as_float(o[4 * j + 1]) * __fdividef(inv_l, 1.f + __expf(-gt.y));
-                        v.z = __uint_as_float(o[4 * j + 2]) * __fdividef(inv_l, 1.f + __expf(-gt.z));
-                        v.w = __uint_as_float(o[4 * j + 3]) * __fdividef(inv_l, 1.f + __expf(-gt.w));
-                        op[j] = v;
+                    for (int j = 0; j < 4; j++) {
+                        Float8 v;
+#pragma unroll
+                        for (int e = 0; e < 8; e++)
+                            v.v[e] = __uint_as_float(o[8 * j + e]) * __fdividef(inv_l, 1.f + __expf(-gq[ch & 1][j].v[e]));
+                        st_global_v8(op + j * 8, v);
                     }
                 } else {
                     float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
