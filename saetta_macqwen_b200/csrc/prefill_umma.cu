@@ -49,7 +49,8 @@ constexpr int kBN = 64;       // keys per block
 constexpr int kKChunk = kBN * 128;  // bytes of one 64-dim slab of a K or V block
 constexpr int kKBytes = 4 * kKChunk;
 constexpr int kPfStages = 3;
-constexpr int kPfThreads = 352; // TMA warp, S-MMA warp, 4 softmax warps, 4 tile I/O warps, P V-MMA warp
+constexpr int kPfThreads = 512; // four warpgroups: softmax; tile I/O, first halves of the rows; tile I/O, second halves;
+                                // TMA warp, S-MMA warp, P V-MMA warp and a spare
 constexpr int kPfSmem = 2 * kPfStages * kKBytes + 1024 /*align*/ + 256 /*barriers*/ + 2 * 2 * kBM * 4 /*l, m per row, two tiles*/;
 constexpr int kTmemO = 0, kTmemQ = 256, kTmemS = 384; // TMEM columns: O, Q (2 values per column), S/P buffers
 constexpr float kLog2ePf = 1.4426950408889634f;
@@ -226,7 +227,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 4), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 4);
+        mbar_init(q_full, 8), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 8);
         for (int s = 0; s < kPfStages; s++)
             mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
         for (int s = 0; s < 2; s++)
@@ -235,7 +236,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         *never_set = 0;
         mbar_fence_init();
     }
-    if (warp == 1) {
+    if (warp == 13) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -250,7 +251,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         *abort_flag = 1;
     };
 
-    if (warp == 0) {
+    // Registers follow the work: the softmax warps hold a 64-wide score row and the tile I/O warps
+    // chunks of O and of the gate, the issuing and copying threads next to nothing.
+    // (Each warpgroup meets its own setmaxnreg, and the code of its roles follows it directly, so
+    // that the compiler allocates each role within its own limit.)
+    if (warp >= 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 12) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t g = 0, tc = 0;
@@ -278,7 +285,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     mbar_wait(&v_full[k % kPfStages], (k / kPfStages) & 1, never_set, 200000u);
                 }
         }
-    } else if (warp == 1) {
+    } else if (warp == 13) {
         // ------------------------------------------------------------ MMA issuer for S = Q K^T
         // Two threads issue MMAs, this one the score products and warp 10 the P V products: one
         // thread alone spends longer issuing the 20 instructions of a block than the tensor
@@ -314,7 +321,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 tc++;
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 14) {
         // ------------------------------------------------------------ MMA issuer for O += P V
         if (lane == 0) {
             const uint32_t idesc_o = (1u << 4) | (p.v_fmt << 7) | (p.v_fmt << 10) | (1u << 16) | (uint32_t(kDim >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
@@ -343,7 +350,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 tc++;
             }
         }
-    } else if (warp < 6) {
+    }
+    } else if (warp < 4) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
         // ------------------------------------------------------------ softmax and correction
         const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
@@ -441,12 +450,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (lane == 0) mbar_arrive(&lm_full[tc & 1]);
             tc++;
         }
-    } else if (warp < 10) {
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
         // ------------------------------------------------------------ tile I/O: Q rows in, results out
         // Per tile these warps write its Q rows into tensor memory and, at its end, scale and gate
         // O out to memory.  The Q rows of tile k+1 go in as soon as the last S of tile k has been
         // computed, before tile k's epilogue, so the MMA warp never waits for a tile change.
-        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t quarter = warp & 3, row = quarter * 32 + lane, half = warp >= 8 ? 1u : 0u;
         const uint32_t lane_addr = (quarter * 32) << 16;
         struct RowOf {
             uint32_t tok;
@@ -470,56 +480,48 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 const RowOf r = row_of(t);
                 if (r.live && r.part) {
                     float *dst = r.part + r.rh * kPartStride;
-                    for (int d = 0; d < kDim; d++) dst[d] = 0.f;
-                    dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
+                    for (uint32_t d = half * 128; d < half * 128 + 128; d++) dst[d] = 0.f;
+                    if (!half) dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
                 }
             }
             return false;
         };
+        // Two threads per row: the warps of the first tile I/O warpgroup take dims 0..127 of Q, the gate
+        // and O, those of the second dims 128..255.
         auto load_q = [&](const PfTile &t, uint32_t k) -> bool {
             const RowOf r = row_of(t);
             const bool row_live = r.live;
             const size_t rh = r.rh;
-            if (row_live && p.out) { // pull this row's gate values towards L2 for the epilogue
-                const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim);
+            if (row_live && p.out) { // pull this half row's gate values towards L2 for the epilogue
+                const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim + half * 128);
 #pragma unroll
-                for (int j = 0; j < 8; j++) prefetch_l2(gpf + j * 128);
+                for (int j = 0; j < 4; j++) prefetch_l2(gpf + j * 128);
             }
-            {   // this thread's Q row into tensor memory (two values per column), once the MMAs
-                // of the tile before no longer read the old one.  The row does not depend on that wait:
-                // its first quarter is fetched into registers and the rest pulled into L2 before it.
-                const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim);
-                // loads of the next 64 values are issued before the store of the current ones
-                uint4 qv[2][8];
-                if (row_live) {
+            // this thread's half of its Q row into tensor memory (two values per column), once the
+            // MMAs of the tile before no longer read the old one.  The row does not depend on that
+            // wait: it is fetched into registers before it.
+            const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim + half * 128);
+            uint4 qv[16];
 #pragma unroll
-                    for (int j = 1; j < 4; j++) prefetch_l2(reinterpret_cast<const char *>(qrow) + j * 128);
+            for (int j = 0; j < 16; j++) qv[j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
+            PF_T0();
+            if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t w[32];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint4 v = qv[c * 8 + j];
+                    w[4 * j] = v.x, w[4 * j + 1] = v.y, w[4 * j + 2] = v.z, w[4 * j + 3] = v.w;
                 }
-#pragma unroll
-                for (int j = 0; j < 8; j++) qv[0][j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
-                PF_T0();
-                if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
-                tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    if (c + 1 < 4) {
-#pragma unroll
-                        for (int k = 0; k < 8; k++) qv[(c + 1) & 1][k] = row_live ? qrow[(c + 1) * 8 + k] : make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    uint32_t w[32];
-#pragma unroll
-                    for (int k = 0; k < 8; k++) {
-                        const uint4 v = qv[c & 1][k];
-                        w[4 * k] = v.x, w[4 * k + 1] = v.y, w[4 * k + 2] = v.z, w[4 * k + 3] = v.w;
-                    }
-                    tmem_st32(tmem_q + lane_addr + c * 32, w);
-                }
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(q_full);
-                if (quarter == 0) { PF_ADD(11); }
+                tmem_st32(tmem_q + lane_addr + half * 64 + c * 32, w);
             }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
+            if (quarter == 0 && !half) { PF_ADD(11); }
             return true;
         };
         auto epilogue = [&](const PfTile &t, uint32_t k) -> bool {
@@ -529,9 +531,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             float *part = r.part;
             // The gate values do not depend on O: the first 32 are requested before O is final,
             // and each later chunk one step ahead of its use (two register buffers).
-            const bool gated = row_live && p.out;
             // (256-bit loads and stores: a thread's accesses are whole 32-byte sectors of its row)
-            const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim : 0);
+            const bool gated = row_live && p.out;
+            const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim + half * 128 : 0);
             Float8 gq[2][4];
             if (gated) {
 #pragma unroll
@@ -541,19 +543,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             const float l = row_l[(k & 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
             if (!mbar_wait(o_final, k & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
-            if (quarter == 0) { PF_ADD(9); }
+            if (quarter == 0 && !half) { PF_ADD(9); }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                if (gated && ch + 1 < 8) {
+            for (int ch = 0; ch < 4; ch++) {
+                if (gated && ch + 1 < 4) {
 #pragma unroll
                     for (int j = 0; j < 4; j++) gq[(ch + 1) & 1][j] = ld_global_v8(gp + (ch + 1) * 32 + j * 8);
                 }
-                const int c = ch * 32;
+                const int c = half * 128 + ch * 32;
                 uint32_t o[32];
                 tmem_ld32(tmem_o + lane_addr + c, o);
                 tmem_wait_ld();
+                if (ch == 3) { // O has left tensor memory: the next tile's P V products may start
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_empty);
+                }
                 if (!row_live) continue;
                 if (p.out) {
                     float *op = p.out + rh * kDim + c;
@@ -573,14 +580,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                                             __uint_as_float(o[4 * j + 2]), __uint_as_float(o[4 * j + 3]));
                 }
             }
-            if (row_live && part) {
+            if (row_live && part && !half) {
                 part[rh * kPartStride + kPartM] = m_ref;
                 part[rh * kPartStride + kPartL] = l;
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty);
-            if (quarter == 0) { PF_ADD(10); }
+            if (quarter == 0 && !half) { PF_ADD(10); }
             return true;
         };
         uint32_t round = 0, k = 0;
@@ -598,7 +602,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    if (warp == 13) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
 // ----------------------------------------------------------------- host side
