@@ -12,7 +12,10 @@
 //  * A tile is 128 query rows = 16 tokens x 8 heads of one kv head (row =
 //    token*8 + head, the reference's GQA packing), so one K/V block feeds all
 //    eight heads.  Persistent CTAs walk the tiles heaviest first.
-//  * Warp 0 streams 64-key K and V blocks into shared memory with TMA tensor
+//  * Sixteen warps in four warpgroups, registers moved between them with setmaxnreg: the
+//    softmax warps (0..3, 168 registers), two tile I/O groups (4..7 and 8..11, 152) and the
+//    copying / issuing warps (12..14, 40).
+//  * Warp 12 streams 64-key K and V blocks into shared memory with TMA tensor
 //    copies (128-byte swizzle, three stages each).
 //  * Both left-hand operands live in tensor memory, not shared memory: the Q
 //    tile (written once per tile with tcgen05.st) and P (written over the S
@@ -20,18 +23,21 @@
 //    only the TMA writes and the K / V operand reads, which is what lets the
 //    MMA pipe run near its rate.  TMEM: O 256 columns, Q 128, two S/P buffers of 64.
 //  * Two threads issue tcgen05.mma, because one thread needs longer to issue a
-//    block's 20 instructions than the tensor pipe needs to run them: warp 1
+//    block's 20 instructions than the tensor pipe needs to run them: warp 13
 //    issues S = Q K^T (128x64x256, A from TMEM), up to two blocks ahead, and
-//    warp 10 issues O += P V (128x256x64, A from TMEM, V read MN-major straight
+//    warp 14 issues O += P V (128x256x64, A from TMEM, V read MN-major straight
 //    from its [key][dim] rows).  An S buffer is reused for block j+2 once the
 //    P V product of block j has completed.
-//  * Warps 2..5 (one TMEM lane = one row per thread) read S with tcgen05.ld, do
-//    the online softmax in log2 units, write P in V's 16-bit type back to TMEM,
-//    and only rescale O in TMEM when the running maximum has grown by more than
-//    2^8.  Warps 6..9 move tiles in and out: the Q rows of the next tile into
-//    TMEM as soon as the last S of the current one is done, then the current
-//    tile's epilogue, so a tile change does not stall the MMAs.  The epilogue divides by l and applies
-//    the sigmoid gate, or leaves (O, m, l) partials for a merge (across GPUs, or across the
+//  * The softmax warps (one TMEM lane = one row per thread) read S with
+//    tcgen05.ld, do the online softmax in log2 units, write P in V's 16-bit type
+//    back to TMEM, and only rescale O in TMEM when the running maximum has grown
+//    by more than 2^8.  The tile I/O warps move tiles in and out, two threads per
+//    row (dims 0..127 and 128..255): the Q rows of the next tile are fetched into
+//    registers early and go into TMEM as soon as the last S of the current tile
+//    is done, then comes the current tile's epilogue, which frees O as soon as it
+//    has read it, so a tile change stalls the MMAs as little as possible.  The
+//    epilogue divides by l and applies the sigmoid gate (256-bit loads and
+//    stores), or leaves (O, m, l) partials for a merge (across GPUs, or across the
 //    two key halves a long-context tile is cut into).
 //  * All mbarrier waits are bounded; a wait that gives up sets the status word
 //    and the CTA-wide abort flag, every role leaves its loop, and TMEM is freed.
@@ -287,7 +293,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         }
     } else if (warp == 13) {
         // ------------------------------------------------------------ MMA issuer for S = Q K^T
-        // Two threads issue MMAs, this one the score products and warp 10 the P V products: one
+        // Two threads issue MMAs, this one the score products and warp 14 the P V products: one
         // thread alone spends longer issuing the 20 instructions of a block than the tensor
         // pipe needs to run them.  An S buffer is reused two blocks later, once the P V product
         // that read P out of it has completed (pv_done).
