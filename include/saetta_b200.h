@@ -323,8 +323,20 @@ int saetta_peer_merge(saetta_peer_group *g, size_t rows, const float *q_and_gate
                       void *stream);
 int saetta_peer_collect(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev,
                         float *out_dev, void *stream);
+/* For many rows (a prefill chunk's partial in the staging buffer): rank j finalises rows
+ * [j*rows/world, (j+1)*rows/world) only (saetta_peer_slice), so every rank sends each peer just that
+ * peer's slice and writes just its own rows of out_dev [rows][heads][256]; q_and_gate_dev is indexed by
+ * the global row. */
+int saetta_peer_merge_sliced(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev,
+                             float *out_dev, void *stream);
+int saetta_peer_slice(const saetta_peer_group *g, size_t rows, size_t *row_lo, size_t *row_hi);
 /* saetta_decode_partial_cache with the partial published to the group instead
  * of written to a buffer (m rows, heads as the group was made for). */
+/* saetta_decode_batch_record on one shard of every sequence: sequence i's partial is row i of the
+ * exchange (n <= the group's rows_max); follow with saetta_peer_collect(g, n, ...). */
+int saetta_decode_batch_publish(saetta_decode_batch *op, size_t n, saetta_kv_cache *const *caches,
+                                const uint32_t *kv_lens_host, const float *q_dev,
+                                saetta_peer_group *group, void *stream);
 int saetta_decode_publish_cache(saetta_decode *op, size_t m, const float *q_dev,
                                 const saetta_kv_cache *cache, saetta_peer_group *group,
                                 uint32_t row_step, const saetta_token_params *params_dev,

@@ -133,6 +133,9 @@ SYMBOLS = {
     "saetta_peer_group_staging": (_P, [_P]),
     "saetta_peer_merge": (_I, [_P, _Z, _P, _P, _P]),
     "saetta_peer_collect": (_I, [_P, _Z, _P, _P, _P]),
+    "saetta_peer_merge_sliced": (_I, [_P, _Z, _P, _P, _P]),
+    "saetta_peer_slice": (_I, [_P, _Z, C.POINTER(_Z), C.POINTER(_Z)]),
+    "saetta_decode_batch_publish": (_I, [_P, _Z, _P, _P, _P, _P, _P]),
     "saetta_decode_publish_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P]),
     "saetta_peer_group_status": (_I, [_P, _P, C.POINTER(_U32)]),
     "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
@@ -389,6 +392,13 @@ class DecodeBatch:
         _check(lib().saetta_decode_batch_record(self.h, n, arr, lens, ptr(q), ptr(q_and_gate), ptr(out),
                                                 _stream(stream)))
 
+    def publish(self, caches, kv_lens, q, group, stream=None):
+        """record() on this rank's shard of every sequence, the partials stored into the peers' mailboxes."""
+        n = len(caches)
+        arr = (C.c_void_p * n)(*[c.h for c in caches])
+        lens = (C.c_uint32 * n)(*[int(x) for x in kv_lens])
+        _check(lib().saetta_decode_batch_publish(self.h, n, arr, lens, ptr(q), group.h, _stream(stream)))
+
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:
             _lib.saetta_decode_batch_destroy(self.h)
@@ -435,6 +445,16 @@ class PeerGroup:
     def merge(self, rows, q_and_gate, out, stream=None):
         """Publishes the partial in `staging`, then collects."""
         _check(lib().saetta_peer_merge(self.h, rows, ptr(q_and_gate), ptr(out), _stream(stream)))
+
+    def merge_sliced(self, rows, q_and_gate, out, stream=None):
+        """Publishes to every rank its slice of the rows of the partial in `staging`, then finalises this rank's slice."""
+        _check(lib().saetta_peer_merge_sliced(self.h, rows, ptr(q_and_gate), ptr(out), _stream(stream)))
+
+    def slice(self, rows):
+        """The rows this rank finalises in merge_sliced: (lo, hi)."""
+        lo, hi = C.c_size_t(), C.c_size_t()
+        _check(lib().saetta_peer_slice(self.h, rows, C.byref(lo), C.byref(hi)))
+        return lo.value, hi.value
 
     def collect(self, rows, q_and_gate, out, stream=None):
         """Waits for every rank's published partial, merges and gates."""

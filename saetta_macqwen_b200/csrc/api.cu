@@ -697,10 +697,11 @@ void saetta_decode_batch_destroy(saetta_decode_batch *op) {
     delete op;
 }
 
-int saetta_decode_batch_record(saetta_decode_batch *op, size_t n, saetta_kv_cache *const *caches,
-                               const uint32_t *kv_lens_host, const float *q_dev, const float *q_and_gate_dev,
-                               float *out_dev, void *stream) {
-    if (!op || !caches || !kv_lens_host || !q_dev || !q_and_gate_dev || !out_dev)
+// With `group` the merged partial of every sequence is published to the peers instead of gated into out.
+static int batch_run(saetta_decode_batch *op, size_t n, saetta_kv_cache *const *caches, const uint32_t *kv_lens_host,
+                     const float *q_dev, const float *q_and_gate_dev, float *out_dev, saetta_peer_group *group,
+                     void *stream) {
+    if (!op || !caches || !kv_lens_host || !q_dev || (!group && (!q_and_gate_dev || !out_dev)))
         return fail(SAETTA_ERR_BAD_ARG, "decode batch: null pointer");
     if (!n || n > op->max_seqs) return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: more sequences than the op was made for");
     const int bits = caches[0] ? caches[0]->bits : 0;
@@ -709,7 +710,8 @@ int saetta_decode_batch_record(saetta_decode_batch *op, size_t n, saetta_kv_cach
     for (size_t i = 0; i < n; i++) {
         if (!caches[i] || caches[i]->bits != bits || caches[i]->kv_heads != 2)
             return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: caches differ in format");
-        if (!kv_lens_host[i] || kv_lens_host[i] > caches[i]->capacity)
+        // (a shard of a short sequence may be empty: its partial is m = -inf, l = 0)
+        if ((!kv_lens_host[i] && !group) || kv_lens_host[i] > caches[i]->capacity)
             return fail(SAETTA_ERR_BAD_SHAPE, "decode batch: kv_len outside the cache");
         total_tiles += (kv_lens_host[i] + 31) / 32;
     }
@@ -763,7 +765,24 @@ int saetta_decode_batch_record(saetta_decode_batch *op, size_t n, saetta_kv_cach
     auto *seq_first_dev = cta_first_dev + op->ctas + 1;
     if (int rc = launch_decode_quant_batched(bits, segs_dev, cta_first_dev, op->ctas, q_dev, op->parts, op->status, st))
         return rc;
-    return launch_merge_frag(op->parts, nseg, seq_first_dev, uint32_t(n), 2, q_and_gate_dev, out_dev, nullptr, st);
+    return launch_merge_frag(op->parts, nseg, seq_first_dev, uint32_t(n), 2, q_and_gate_dev, out_dev,
+                             group ? group->staging : nullptr, st, group ? &group->push : nullptr);
+}
+
+int saetta_decode_batch_record(saetta_decode_batch *op, size_t n, saetta_kv_cache *const *caches,
+                               const uint32_t *kv_lens_host, const float *q_dev, const float *q_and_gate_dev,
+                               float *out_dev, void *stream) {
+    return batch_run(op, n, caches, kv_lens_host, q_dev, q_and_gate_dev, out_dev, nullptr, stream);
+}
+
+int saetta_decode_batch_publish(saetta_decode_batch *op, size_t n, saetta_kv_cache *const *caches,
+                                const uint32_t *kv_lens_host, const float *q_dev, saetta_peer_group *group,
+                                void *stream) {
+    if (!group) return fail(SAETTA_ERR_BAD_ARG, "decode batch publish: null pointer");
+    if (!group->connected) return fail(SAETTA_ERR_BAD_ARG, "decode batch publish: the group is not connected");
+    if (op && (group->device != op->device || op->heads != group->heads || n > group->rows_max))
+        return fail(SAETTA_ERR_BAD_SHAPE, "decode batch publish: the group was made for another shape or device");
+    return batch_run(op, n, caches, kv_lens_host, q_dev, nullptr, nullptr, group, stream);
 }
 
 // ------------------------------------------------------------------ prefill

@@ -51,6 +51,7 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
     const uint32_t head = 2 * (lane & 3) + (r & 1);
 
     float acc = 0.f;
+    if (tid < 8) M_s[tid] = -INFINITY, L_s[tid] = 0.f; // what a row without parts (an empty shard) merges to
     for (uint32_t c0 = p0; c0 < p1; c0 += kMergeMaxParts) { // one pass unless a sequence has > 512 parts
         const uint32_t n = min(p1 - c0, uint32_t(kMergeMaxParts));
         __syncthreads();

@@ -25,6 +25,7 @@
 // collecting kernel the other way round, so no kernel reads a word that one of
 // its own blocks writes.  The wait is bounded: after the limit the kernel sets
 // a status bit and leaves.
+#include <algorithm>
 #include <cstring>
 #include <new>
 
@@ -46,6 +47,20 @@ publish_kernel(const float *__restrict__ staging, const PeerPush push, uint32_t 
     if (threadIdx.x == 0) *push.seq_sent = s;
 }
 
+// Row-sliced publish: rank j finalises rows [j*rows/world, (j+1)*rows/world), so only that slice of
+// the staging partial goes to rank j's mailbox (at its natural row offset).  grid (blocks, world).
+__global__ void __launch_bounds__(1024)
+publish_rows_kernel(const float *__restrict__ staging, const PeerPush push, uint32_t rows, uint32_t row_floats) {
+    pdl_wait();
+    const uint32_t s = *push.seq_done + 1;
+    const uint32_t j = blockIdx.y;
+    const size_t lo = size_t(rows) * j / push.world * row_floats, hi = size_t(rows) * (j + 1) / push.world * row_floats;
+    unsigned long long *dst = push.parts[j] + (size_t(s & 1) * push.world + push.rank) * push.slot_floats;
+    for (size_t i = lo + size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += size_t(gridDim.x) * blockDim.x)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + i), "l"(peer_word(staging[i], s)) : "memory");
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *push.seq_sent = s;
+}
+
 // Polls one mailbox word until it carries exchange number `s`; false after `limit` polls.
 __device__ __forceinline__ bool peer_poll(const unsigned long long *p, uint32_t s, uint32_t limit, float &v) {
     for (uint32_t n = 0; n < limit; n++) {
@@ -60,16 +75,16 @@ __device__ __forceinline__ bool peer_poll(const unsigned long long *p, uint32_t 
     return false;
 }
 
-// grid (heads, rows), 256 threads = one per dim.  Reads this rank's own mailbox only.
+// grid (heads, rows), 256 threads = one per dim; rows row0 .. row0 + gridDim.y - 1.  Reads this rank's own mailbox only.
 __global__ void __launch_bounds__(256)
 peer_merge_kernel(const unsigned long long *__restrict__ slots, uint32_t world, const uint32_t *seq_sent,
                   uint32_t *seq_done, uint32_t slot_floats, uint32_t heads, const float *__restrict__ q_and_gate,
-                  float *__restrict__ out, uint32_t *status, uint32_t poll_limit) {
+                  float *__restrict__ out, uint32_t *status, uint32_t poll_limit, uint32_t row0) {
     pdl_wait();
     __shared__ float ml_s[kMaxPeers][2];
     __shared__ uint32_t s_bad;
     const uint32_t s = *seq_sent;
-    const uint32_t head = blockIdx.x, row = blockIdx.y, dim = threadIdx.x;
+    const uint32_t head = blockIdx.x, row = row0 + blockIdx.y, dim = threadIdx.x;
     const size_t rh = size_t(row) * heads + head;
     const unsigned long long *base = slots + size_t(s & 1) * world * slot_floats + rh * kPartStride;
     if (threadIdx.x == 0) s_bad = 0;
@@ -191,15 +206,41 @@ static int peer_check(const saetta_peer_group *g, size_t rows, const void *a, co
     return SAETTA_OK;
 }
 
+static int collect_rows(saetta_peer_group *g, size_t row0, size_t rows, const float *q_and_gate_dev, float *out_dev,
+                        cudaStream_t stream) {
+    if (!rows) return SAETTA_OK; // (a rank that owns no row still took part through its publish)
+    uint32_t *words = group_words(g);
+    SAETTA_CUDA(launch_pdl(peer_merge_kernel, dim3(unsigned(g->heads), unsigned(rows)), dim3(256), 0, stream,
+                           (const unsigned long long *)g->mailbox, uint32_t(g->world),
+                           (const uint32_t *)(words + kSeqSentWord), words + kSeqDoneWord, uint32_t(g->slot_floats),
+                           uint32_t(g->heads), q_and_gate_dev, out_dev, words + kStatusWord, 1000000u, uint32_t(row0)));
+    return SAETTA_OK;
+}
+
 int saetta_peer_collect(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev, void *stream) {
     if (int rc = peer_check(g, rows, q_and_gate_dev, out_dev)) return rc;
     DeviceGuard guard(g->device);
-    uint32_t *words = group_words(g);
-    SAETTA_CUDA(launch_pdl(peer_merge_kernel, dim3(unsigned(g->heads), unsigned(rows)), dim3(256), 0, (cudaStream_t)stream,
-                           (const unsigned long long *)g->mailbox, uint32_t(g->world),
-                           (const uint32_t *)(words + kSeqSentWord), words + kSeqDoneWord, uint32_t(g->slot_floats),
-                           uint32_t(g->heads), q_and_gate_dev, out_dev, words + kStatusWord, 1000000u));
+    return collect_rows(g, 0, rows, q_and_gate_dev, out_dev, (cudaStream_t)stream);
+}
+
+int saetta_peer_slice(const saetta_peer_group *g, size_t rows, size_t *row_lo, size_t *row_hi) {
+    if (!g || !row_lo || !row_hi) return fail(SAETTA_ERR_BAD_ARG, "peer slice: null pointer");
+    *row_lo = rows * size_t(g->rank) / size_t(g->world), *row_hi = rows * size_t(g->rank + 1) / size_t(g->world);
     return SAETTA_OK;
+}
+
+int saetta_peer_merge_sliced(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev, void *stream) {
+    if (int rc = peer_check(g, rows, q_and_gate_dev, out_dev)) return rc;
+    if (rows < size_t(g->world)) return fail(SAETTA_ERR_BAD_SHAPE, "peer merge: fewer rows than ranks");
+    DeviceGuard guard(g->device);
+    const uint32_t row_floats = uint32_t(g->heads * kPartStride);
+    const size_t per_rank = (rows / g->world + 1) * row_floats;
+    const unsigned blocks = unsigned(std::min<size_t>(64, (per_rank + 4095) / 4096));
+    SAETTA_CUDA(launch_pdl(publish_rows_kernel, dim3(blocks, unsigned(g->world)), dim3(1024), 0, (cudaStream_t)stream,
+                           (const float *)g->staging, g->push, uint32_t(rows), row_floats));
+    size_t lo, hi;
+    saetta_peer_slice(g, rows, &lo, &hi);
+    return collect_rows(g, lo, hi - lo, q_and_gate_dev, out_dev, (cudaStream_t)stream);
 }
 
 int saetta_peer_merge(saetta_peer_group *g, size_t rows, const float *q_and_gate_dev, float *out_dev, void *stream) {

@@ -12,6 +12,27 @@ pytestmark = pytest.mark.gpu
 HEADS, KV, DIM, ROW = 16, 2, 256, 512
 
 
+def _finish(procs):
+    """Joins the ranks; one that is still waiting for a rank that died is ended, not waited for."""
+    for p in procs:
+        p.join(60)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.terminate()
+        p.join(10)
+    assert not alive and all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+
+
+def _guarded(fn, rank, *args):
+    """Spawn target: runs fn(rank, *args); a rank that raises still reports, so the parent fails at once."""
+    out_q = args[-1]
+    try:
+        fn(rank, *args)
+    except BaseException as e:  # noqa: BLE001 - reported to the parent, which fails the test
+        out_q.put((rank, f"rank {rank} raised {type(e).__name__}: {e}"))
+        raise
+
+
 def _rank(rank, world, port, tokens, m, bits, out_q):
     import torch
     import torch.distributed as dist
@@ -72,13 +93,11 @@ def test_ranks_merge_through_peer_mailboxes(bits, m, world):
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
     port = 29700 + (os.getpid() + 7 * m + world) % 1000
-    procs = [ctx.Process(target=_rank, args=(r, world, port, 3000, m, bits, out_q)) for r in range(world)]
+    procs = [ctx.Process(daemon=True, target=_guarded, args=(_rank, r, world, port, 3000, m, bits, out_q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [out_q.get(timeout=240) for _ in procs]
-    for p in procs:
-        p.join(60)
-        assert p.exitcode == 0
+    results = [out_q.get(timeout=120) for _ in procs]
+    _finish(procs)
     for rank, err in results:
         assert err < 2e-3, (rank, err)
 
@@ -146,12 +165,143 @@ def test_collect_gives_up_when_a_peer_stays_away():
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
     port = 29700 + (os.getpid() + 555) % 1000
-    procs = [ctx.Process(target=_rank_with_absent_peer, args=(r, 2, port, out_q)) for r in range(2)]
+    procs = [ctx.Process(daemon=True, target=_guarded, args=(_rank_with_absent_peer, r, 2, port, out_q)) for r in range(2)]
     for p in procs:
         p.start()
-    results = dict(out_q.get(timeout=240) for _ in procs)
-    for p in procs:
-        p.join(60)
-        assert p.exitcode == 0
+    results = dict(out_q.get(timeout=120) for _ in procs)
+    _finish(procs)
     assert results[0] == ("timeout", True), results
     assert results[1] == ("ok", True), results
+
+
+def _rank_prefill(rank, world, port, out_q):
+    """A prefill chunk with the keys split over the ranks: partial over this rank's key range, row-sliced
+    exchange, every rank finalises its slice of the chunk's rows."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    import saetta_macqwen_b200 as sa
+    from oracle import oracle as o
+
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+
+    pos, tokens = 900, 72
+    total = pos + tokens
+    rb = lambda x: o.round_bf16(x)
+    q = rb(o.normal(tokens * HEADS * DIM, 1))
+    k, v = rb(o.normal(total * ROW, 2)), rb(o.normal(total * ROW, 3))
+    qg = o.normal(tokens * HEADS * 2 * DIM, 4)
+    to_bf16 = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda().to(torch.bfloat16)
+    group = sa.PeerGroup(rank, rank, world, tokens, HEADS, gather)
+    op = sa.AttGemm(rank, 4096, KV)
+    p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
+    cuts = [total * r // world for r in range(world + 1)]  # this rank's keys: [cuts[rank], cuts[rank + 1])
+    out = torch.zeros(tokens * HEADS * DIM, device="cuda")
+    gd = torch.from_numpy(qg).cuda()
+    for _ in range(3):
+        out.zero_()
+        op.partial(to_bf16(q), to_bf16(k), to_bf16(v), None, group.staging, p, cuts[rank], cuts[rank + 1], dtype=sa.BF16)
+        group.merge_sliced(tokens, gd, out)
+        torch.cuda.synchronize()
+        assert group.status() == 0
+    lo, hi = group.slice(tokens)
+    want = o.attention_rows(q, qg, k, v, [pos + i + 1 for i in range(tokens)], threads=4)
+    got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
+    worst = float(np.abs(got[lo:hi] - want[lo:hi]).max())
+    untouched = bool((got[:lo] == 0).all() and (got[hi:] == 0).all())
+    dist.barrier()
+    out_q.put((rank, (worst, untouched, hi - lo)))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_prefill_partials_exchanged_by_row_slices(world):
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    out_q = ctx.Queue()
+    port = 29700 + (os.getpid() + 333 + world) % 1000
+    procs = [ctx.Process(daemon=True, target=_guarded, args=(_rank_prefill, r, world, port, out_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(out_q.get(timeout=120) for _ in procs)
+    _finish(procs)
+    assert sum(r[2] for r in results.values()) == 72
+    for rank, (worst, untouched, _) in results.items():
+        assert worst < 2e-3 and untouched, (rank, worst, untouched)
+
+
+def _rank_batch(rank, world, port, out_q):
+    """Ragged batch decode with every sequence's keys split over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    import saetta_macqwen_b200 as sa
+    from saetta_macqwen_b200 import shard
+    from oracle import oracle as o
+
+    def gather(b):
+        lst = [None] * world
+        dist.all_gather_object(lst, b)
+        return lst
+
+    lens, bits = [700, 64, 2500, 333, 1024], 8
+    n = len(lens)
+    q, qg = o.normal(n * HEADS * DIM, 50), o.normal(n * HEADS * 2 * DIM, 51)
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    caches, mine, refs = [], [], []
+    for i, L in enumerate(lens):
+        k, v = o.normal(L * ROW, 60 + i), o.normal(L * ROW, 80 + i)
+        lo, hi = shard.shard_ranges(L, world)[rank]
+        c = sa.GpuKvCache(rank, bits, max(hi - lo, 128))
+        if hi > lo:  # the 64-token sequence fits in rank 0's shard: rank 1 publishes an empty partial for it
+            c.store_at(dev(k[lo * ROW:hi * ROW]), dev(v[lo * ROW:hi * ROW]), 0, hi - lo)
+        caches.append(c), mine.append(hi - lo), refs.append((o.round_trip(k, bits), o.round_trip(v, bits)))
+    op = sa.DecodeBatch(rank, 8)
+    group = sa.PeerGroup(rank, rank, world, 8, HEADS, gather)
+    out = torch.zeros(n * HEADS * DIM, device="cuda")
+    qd, gd = dev(q), dev(qg)
+    worst = 0.0
+    for _ in range(3):
+        out.zero_()
+        op.publish(caches, mine, qd, group)
+        group.collect(n, gd, out)
+        torch.cuda.synchronize()
+        assert group.status() == 0
+        got = out.cpu().numpy().reshape(n, HEADS, DIM)
+        for i, L in enumerate(lens):
+            want = o.attention_rows(q.reshape(n, -1)[i], qg.reshape(n, -1)[i], refs[i][0], refs[i][1], [L])
+            worst = max(worst, float(np.abs(got[i] - want[0]).max()))
+    dist.barrier()
+    out_q.put((rank, worst))
+    dist.destroy_process_group()
+
+
+def test_ragged_batch_split_over_two_ranks():
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    out_q = ctx.Queue()
+    port = 29700 + (os.getpid() + 444) % 1000
+    procs = [ctx.Process(daemon=True, target=_guarded, args=(_rank_batch, r, 2, port, out_q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out_q.get(timeout=120) for _ in procs]
+    _finish(procs)
+    for rank, err in results:
+        assert err < 2e-3, (rank, err)
