@@ -206,6 +206,43 @@ def prefill_point(sa, torch, pos, tokens, steps, warmup, stream, quant_bits=None
     return {"tflops": flops / ms / 1e9, "ms": ms, "flops": flops}
 
 
+def half_point(sa, torch, ctx, layers, steps, warmup, stream):
+    """Decode over a binary16 cache (the reference's default cache format): 2048 bytes per token."""
+    dev = torch.cuda.current_device()
+    caches = [sa.GpuKvCache(dev, 16, ctx, dtype=sa.F16) for _ in range(layers)]
+    x = torch.randn(4096 * ROW, device="cuda")
+    for c in caches:
+        for p0 in range(0, ctx, 4096):
+            c.store_at(x, x.flip(0).contiguous(), p0, min(4096, ctx - p0))
+    op = sa.AttentionRows(dev, HEADS, KV, ctx, 1)
+    q = torch.randn(HEADS * DIM, device="cuda")
+    qg = torch.randn(HEADS * 2 * DIM, device="cuda")
+    out = torch.zeros(HEADS * DIM, device="cuda")
+    params = torch.tensor([0, ctx - 1, ctx, 0], dtype=torch.int32, device="cuda")
+
+    def step():
+        for c in caches:
+            op.record_cache(1, q, c, qg, out, params, stream=stream)
+
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(warmup):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1) / steps / layers
+    assert op.device_status(stream=stream) == 0
+    return {"gbs": ctx * 2048 / ms / 1e6, "us_per_layer": ms * 1e3, "layers": layers}
+
+
 def prep_point(sa, torch, tokens, bits, steps, warmup, stream):
     """GB/s of attention prep fused with the quantised store for one prefill chunk: reads the q halves of
     q_and_gate, k, v (f32), writes q as bf16 and the cache rows.  The inputs of consecutive steps are
@@ -245,6 +282,7 @@ def point_table(sa, torch, stream, s, w):
         "decode_128k_8bit": lambda: decode_point(sa, torch, 131072, 8, 1, 4, s, w, stream),
         "decode_256k_8bit": lambda: decode_point(sa, torch, 262144, 8, 1, 4, s, w, stream),
         "decode_256k_4bit": lambda: decode_point(sa, torch, 262144, 4, 1, 4, s, w, stream),
+        "decode_128k_f16": lambda: half_point(sa, torch, 131072, 4, s, w, stream),
         "verify_m4_32k_8bit": lambda: decode_point(sa, torch, 32768, 8, 4, 10, s, w, stream),
         "batch64_ragged_8bit": lambda: batch_point(sa, torch, 8, min(s, 3), 2, stream),
         "batch64_ragged_4bit": lambda: batch_point(sa, torch, 4, min(s, 3), 2, stream),
@@ -508,7 +546,7 @@ def main():
         torch.cuda.empty_cache()
         s, w = max(5, args.steps // 2), 3
         table = point_table(sa, torch, stream, s, w)
-        for name in ["decode_32k_8bit", "decode_128k_8bit", "decode_256k_4bit", "verify_m4_32k_8bit",
+        for name in ["decode_32k_8bit", "decode_128k_8bit", "decode_256k_4bit", "decode_128k_f16", "verify_m4_32k_8bit",
                      "batch64_ragged_8bit", "batch64_ragged_4bit", "prep_store_4k_8bit", "prefill_4k_pos0_bf16",
                      "prefill_4k_pos32k_8bit", "prefill_4k_pos128k_8bit"]:
             fn = table[name]

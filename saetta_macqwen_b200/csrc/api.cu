@@ -52,6 +52,7 @@ static int configure_device(int device) {
     static bool done[64] = {};
     if (device >= 0 && device < 64 && done[device]) return SAETTA_OK;
     int rc = decode_quant_configure(device);
+    if (!rc) rc = decode_half_configure(device);
     if (!rc) rc = decode_exact_configure(device);
     if (!rc) rc = prefill_configure(device);
     if (!rc && device >= 0 && device < 64) done[device] = true;
@@ -546,6 +547,14 @@ static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView 
         if (kv.kv_heads != 2) return fail(SAETTA_ERR_UNSUPPORTED, "quantised decode attention is built for 2 kv heads");
         if (int rc = launch_decode_quant(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
                                          uint32_t(kv_capacity), params, st))
+            return rc;
+        return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
+                                 part_out, st, group ? &group->push : nullptr);
+    }
+    if (kv.bits == 16 && kv.dtype == SAETTA_F16 && kv.kv_heads == 2 && aligned16(kv.k) && aligned16(kv.v)) {
+        // the reference's own cache format: tensor-core kernel, partials and merge as for the quantised cache
+        if (int rc = launch_decode_half(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
+                                        uint32_t(kv_capacity), params, st))
             return rc;
         return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
                                  part_out, st, group ? &group->push : nullptr);

@@ -1,0 +1,342 @@
+// Split-KV decode / MTP-verify attention over a binary16 KV cache, on the tensor cores.
+//
+// Stands in for attention_partial_mma (kernels/attention.metal:127-236) and
+// attention_partial_rows<16> (kernels/attention_rows.metal:108-292) of the
+// reference, whose default cache holds half rows [capacity][kv_heads][256]; the
+// merge over parts is in merge.cu.  Same shape as the quantised kernel next door
+// (decode_quant.cu), minus the dequantisation:
+//
+//  * One persistent CTA per SM owns a contiguous range of 32-token tiles.  A
+//    producer warp streams each tile into a ring of shared-memory stages with
+//    bulk (TMA engine) copies, one per token row and side, signalled on
+//    mbarriers.  Rows land 1088 (keys) and 1040 (values) bytes apart instead of
+//    1024, which keeps the operand loads below free of bank conflicts.
+//  * Eight consumer warps each own one kv head and a share of the 16-token
+//    sub-tiles.  Scores: mma.sync m16n8k16 with the 16 rows = high and low halves
+//    of the 8 query heads (the query keeps f32 precision), K straight from shared
+//    memory as the B operand (a lane's 128-bit load is two k-steps; the query
+//    fragments are built for that order of dims).  Values: ldmatrix.trans turns
+//    [token][dim] rows into the A fragments of O^T[dim][head] += V^T P^T.
+//  * Online softmax and the end-of-range merge as in the quantised kernel; the
+//    partials leave in the same fragment order, so merge.cu and the exchange
+//    across GPUs serve both.
+//  * One query row per pass: m rows are m passes (gridDim.y), each reading the
+//    cache again.  Every wait on an mbarrier is bounded.
+#include <algorithm>
+
+#include "host.hpp"
+
+namespace saetta {
+
+namespace half_decode {
+
+constexpr int kTile = 32;   // tokens per stage
+constexpr int kSub = 16;    // tokens per MMA sub-tile
+constexpr int kWarps = 8;   // consumer warps
+constexpr int kThreads = (kWarps + 4) * 32;
+constexpr int kKv = 2;
+constexpr int kRowBytes = kKv * kDim * 2;   // one token of one side in the cache
+constexpr int kKRow = kRowBytes + 64;       // shared-memory pitch of key rows
+constexpr int kVRow = kRowBytes + 16;       // ... and of value rows
+constexpr int kStageBytes = kTile * (kKRow + kVRow);
+constexpr int kStages = 3;
+constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in the merge kernel's fragment order
+constexpr int kPartKv = kFragFloats + 16;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescale = 8.0f;
+constexpr int kPrefetchTiles = 2;
+constexpr int kSmem = kStages * kStageBytes + kWarps * 16 * 4 + 2 * kStages * 8 + 16;
+static_assert(kWarps * kFragFloats * 4 <= kStages * kStageBytes, "the end-of-range merge parks in the ring");
+
+struct Args {
+    const uint8_t *k, *v; // [capacity][2][256] binary16
+    const float *q;       // [m][16][256]
+    float *parts;         // [part][m][kv][kPartKv]
+    uint32_t *status;
+    const saetta_token_params *params;
+    uint32_t m, row_step, capacity;
+};
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem_row)));
+}
+
+__global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *stages = smem;
+    float *ml = reinterpret_cast<float *>(smem + kStages * kStageBytes); // [warp][m of 8 heads, l of 8 heads]
+    uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 16);
+    uint64_t *empty = full + kStages;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + kStages);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kWarps);
+        }
+        abort_flag[0] = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const uint32_t row = blockIdx.y; // the query row of this pass
+    auto range = [&](uint32_t kv_len, uint32_t &tb, uint32_t &te, uint32_t &n_row) {
+        n_row = min(kv_len + row * a.row_step, a.capacity); // keys this row sees
+        const uint32_t tiles = (n_row + kTile - 1) / kTile;
+        tb = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
+        te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
+    };
+    // While the kernel before this one drains, pull the head of this CTA's range into L2 (the range
+    // comes from a possibly stale kv_len: a hint only, everything is read again after the wait).
+    if (warp == kWarps && lane == 0) {
+        uint32_t tb, te, n_row;
+        range(*reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len), tb, te, n_row);
+        const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
+        for (uint32_t t = 0; t < nt; t++) {
+            l2_prefetch(a.k + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
+            l2_prefetch(a.v + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
+        }
+    }
+    pdl_wait();              // q, the token parameters and the cache may come from the kernel before
+    pdl_launch_dependents(); // the merge kernel may be scheduled as SMs free up; it waits for this grid
+    uint32_t tile_begin, tile_end, n_row;
+    range(a.params->kv_len, tile_begin, tile_end, n_row);
+
+    if (warp >= kWarps) {
+        // ---------------------------------------------------------------- producer
+        // (same register budget rule as in decode_quant.cu: 128 x (168 - 40) = 256 x (232 - 168))
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp != kWarps) return;
+        uint32_t it = 0;
+        for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
+            const uint32_t st = it % kStages, round = it / kStages;
+            if (!mbar_wait(&empty[st], (round & 1) ^ 1, abort_flag)) {
+                if (lane == 0) {
+                    atomicOr(a.status, kStatusEmptyTimeout);
+                    *abort_flag = 1;
+                }
+                break;
+            }
+            uint8_t *dst = stages + st * kStageBytes;
+            if (lane == 0) mbar_expect_tx(&full[st], 2 * kTile * kRowBytes);
+            __syncwarp();
+            // lane = token of the tile: its key row and its value row
+            const size_t tok = size_t(t) * kTile + lane;
+            bulk_g2s(dst + lane * kKRow, a.k + tok * kRowBytes, kRowBytes, &full[st]);
+            bulk_g2s(dst + kTile * kKRow + lane * kVRow, a.v + tok * kRowBytes, kRowBytes, &full[st]);
+            __syncwarp();
+        }
+        // Leave only once every copy this warp issued has landed (bounded): the shared memory must
+        // not be handed to another CTA with copies in flight.
+        const uint32_t issued = it;
+        for (uint32_t k = issued > kStages ? issued - kStages : 0; k < issued; k++)
+            mbar_wait(&full[k % kStages], (k / kStages) & 1, abort_flag, 2000000u);
+        return;
+    }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+
+    // -------------------------------------------------------------------- consumers
+    constexpr int NSLOT = kWarps / kKv; // warps sharing one kv head
+    const int kv = warp & 1, slot = warp >> 1;
+    const int g = lane >> 2, i = lane & 3;
+
+    // Query fragments of head kv*8+g, scaled by log2(e)/16, split into two halves.  k-step ks covers,
+    // for lane i, dims 32*(ks/2) + 8*i + 4*(ks%2) + {0,1 | 2,3}: what a 128-bit load of K holds.
+    uint32_t qh[16][2], ql[16][2];
+    {
+        const float *qp = a.q + ((size_t(row) * 16) + kv * 8 + g) * kDim;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const float4 v0 = *reinterpret_cast<const float4 *>(qp + b * 32 + i * 8);
+            const float4 v1 = *reinterpret_cast<const float4 *>(qp + b * 32 + i * 8 + 4);
+            const float x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            float hi[8], lo[8];
+#pragma unroll
+            for (int d = 0; d < 8; d++) {
+                const float s = x[d] * (kLog2e * 0.0625f);
+                hi[d] = __half2float(__float2half_rn(s));
+                lo[d] = __half2float(__float2half_rn(s - hi[d]));
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    qh[2 * b + j][r] = pack_half2(hi[4 * j + 2 * r], hi[4 * j + 2 * r + 1]);
+                    ql[2 * b + j][r] = pack_half2(lo[4 * j + 2 * r], lo[4 * j + 2 * r + 1]);
+                }
+        }
+    }
+
+    float O[16][4];
+#pragma unroll
+    for (int e = 0; e < 16; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
+    float Mref = -INFINITY, lsum = 0.f; // of head g (this thread's row of the score MMA)
+
+    uint32_t it = 0;
+    for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
+        const uint32_t st = it % kStages, round = it / kStages;
+        if (!mbar_wait(&full[st], round & 1, abort_flag)) {
+            if (lane == 0) {
+                atomicOr(a.status, kStatusFullTimeout);
+                *abort_flag = 1;
+            }
+            break; // skip the tiles, keep the barriers below
+        }
+        const uint8_t *sk = stages + st * kStageBytes + kv * (kDim * 2);
+        const uint8_t *sv = stages + st * kStageBytes + kTile * kKRow + kv * (kDim * 2);
+#pragma unroll 1
+        for (int sub = 0; sub < kTile / kSub; sub++) {
+            const uint32_t q_idx = 2 * (t - tile_begin) + sub;
+            const uint32_t tok0 = t * kTile + sub * kSub; // first token of the sub-tile
+            if ((q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_row) continue;
+            const bool partial = tok0 + kSub > n_row;
+            const int lt = sub * kSub;
+
+            // ------------------------------------------------ scores S[head][token]
+            float S[2][2];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) {
+                const uint8_t *krow = sk + (lt + nt * 8 + g) * kKRow + i * 16; // token g of the 8-token tile
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int b = 0; b < 8; b++) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(krow + b * 64);
+                    mma_f16(acc, qh[2 * b][0], ql[2 * b][0], qh[2 * b][1], ql[2 * b][1], w.x, w.y);
+                    mma_f16(acc, qh[2 * b + 1][0], ql[2 * b + 1][0], qh[2 * b + 1][1], ql[2 * b + 1][1], w.z, w.w);
+                }
+                S[nt][0] = acc[0] + acc[2], S[nt][1] = acc[1] + acc[3];
+                if (partial) { // rows past the end may hold anything: assigned, never computed with
+                    if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
+                    if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
+                }
+            }
+
+            // ------------------------------------------------ online softmax of head g (log2 units)
+            float mx = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const bool need = mx > Mref + kRescale;
+            if (__any_sync(0xffffffffu, need)) {
+                const float f = need ? exp2f(Mref - mx) : 1.f; // exp2f(-inf) = 0 on the first tile
+                if (need) Mref = mx, lsum *= f;
+                // the accumulators' columns are heads 2i, 2i+1: fetch their factors from lanes g = 2i, 2i+1
+                const float f0 = __shfl_sync(0xffffffffu, f, 8 * i), f1 = __shfl_sync(0xffffffffu, f, 8 * i + 4);
+#pragma unroll
+                for (int e = 0; e < 16; e++) O[e][0] *= f0, O[e][1] *= f1, O[e][2] *= f0, O[e][3] *= f1;
+            }
+            const float p00 = exp2f(S[0][0] - Mref), p01 = exp2f(S[0][1] - Mref);
+            const float p10 = exp2f(S[1][0] - Mref), p11 = exp2f(S[1][1] - Mref);
+            lsum += (p00 + p01) + (p10 + p11);
+            // B[k = token][n = head]: the lane's own score columns, no data moves between lanes.  P goes in
+            // as two binary16 halves (what the first rounding dropped is the second operand), so the
+            // value product keeps f32 precision as the score product does; the kernel is bound by the
+            // cache's bytes, the second MMA is free.
+            const uint32_t pb0 = pack_half2(p00, p01), pb1 = pack_half2(p10, p11);
+            const float2 h0 = h2f2(pb0), h1 = h2f2(pb1);
+            const uint32_t pl0 = pack_half2(p00 - h0.x, p01 - h0.y), pl1 = pack_half2(p10 - h1.x, p11 - h1.y);
+
+            // ------------------------------------------------ O^T[dim][head] += V^T P^T
+            // ldmatrix.trans: lanes 8j..8j+7 give the rows of matrix j -- tokens 0..7 (j < 2) or 8..15 of the
+            // sub-tile at dims 0..7 (j even) or 8..15 of the 16-dim slice -- and get back token pairs of one dim.
+            const uint8_t *vrow = sv + (lt + ((lane >> 4) << 3) + (lane & 7)) * kVRow + ((lane >> 3) & 1) * 16;
+            uint32_t mask01 = 0xffffffffu, mask23 = 0xffffffffu;
+            if (partial) {
+                mask01 = (tok0 + 2 * i < n_row ? 0xffffu : 0u) | (tok0 + 2 * i + 1 < n_row ? 0xffff0000u : 0u);
+                mask23 = (tok0 + 2 * i + 8 < n_row ? 0xffffu : 0u) | (tok0 + 2 * i + 9 < n_row ? 0xffff0000u : 0u);
+            }
+#pragma unroll
+            for (int mt = 0; mt < 16; mt++) {
+                uint32_t av[4];
+                ldmatrix_x4_trans(av, vrow + mt * 32);
+                if (partial) av[0] &= mask01, av[1] &= mask01, av[2] &= mask23, av[3] &= mask23;
+                mma_f16(O[mt], av[0], av[1], av[2], av[3], pb0, pb1);
+                mma_f16(O[mt], av[0], av[1], av[2], av[3], pl0, pl1);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+    }
+
+    // ---------------------------------------------------------------- end of range
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+    float Mc2[2], l[2];
+    Mc2[0] = __shfl_sync(0xffffffffu, Mref, 8 * i), Mc2[1] = __shfl_sync(0xffffffffu, Mref, 8 * i + 4);
+    l[0] = __shfl_sync(0xffffffffu, lsum, 8 * i), l[1] = __shfl_sync(0xffffffffu, lsum, 8 * i + 4);
+    // Warps that share a kv head agree on one maximum, scale, and add up in a fixed order (deterministic).
+    if (g == 0) {
+        ml[warp * 16 + 2 * i] = Mc2[0], ml[warp * 16 + 2 * i + 1] = Mc2[1];
+        ml[warp * 16 + 8 + 2 * i] = l[0], ml[warp * 16 + 8 + 2 * i + 1] = l[1];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+    float Mc[2] = {-INFINITY, -INFINITY}, lc[2] = {0.f, 0.f};
+#pragma unroll
+    for (int sl = 0; sl < NSLOT; sl++) {
+        const int w = (sl << 1) | kv;
+        Mc[0] = fmaxf(Mc[0], ml[w * 16 + 2 * i]);
+        Mc[1] = fmaxf(Mc[1], ml[w * 16 + 2 * i + 1]);
+    }
+#pragma unroll
+    for (int sl = 0; sl < NSLOT; sl++) {
+        const int w = (sl << 1) | kv;
+        const float m0 = ml[w * 16 + 2 * i], m1 = ml[w * 16 + 2 * i + 1];
+        lc[0] += m0 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i] * exp2f(m0 - Mc[0]);
+        lc[1] += m1 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i + 1] * exp2f(m1 - Mc[1]);
+    }
+    const float f0 = Mc2[0] == -INFINITY ? 0.f : exp2f(Mc2[0] - Mc[0]);
+    const float f1 = Mc2[1] == -INFINITY ? 0.f : exp2f(Mc2[1] - Mc[1]);
+    // After the barrier above no warp reads the copy ring any more (a producer that gave up has raised
+    // the status word; the result is void then): every warp parks its scaled accumulators there in
+    // the merge kernel's fragment order -- head h, dim d at (4*mt + c)*32 + 4*((d >> 3) & 7) + (h >> 1),
+    // mt = 4*(d >> 6) + (d & 3), c = (h & 1) + ((d >> 1) & 2) -- and then each warp adds up its share.
+    float *ring = reinterpret_cast<float *>(stages);
+    {
+        float *mine = ring + warp * kFragFloats + i;
+#pragma unroll
+        for (int mt = 0; mt < 16; mt++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) { // head 2i + (c & 1), dim 16*mt + g + 8*(c >> 1)
+                const int mtq = 4 * (mt >> 2) + (g & 3), cq = (c & 1) + 2 * ((g >> 2) & 1);
+                mine[(4 * mtq + cq) * 32 + 4 * ((2 * mt + (c >> 1)) & 7)] = O[mt][c] * ((c & 1) ? f1 : f0);
+            }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+    float *dst = a.parts + ((size_t(blockIdx.x) * a.m + row) * kKv + kv) * kPartKv;
+    constexpr int per = 64 / NSLOT;
+#pragma unroll
+    for (int r = 0; r < per; r++) {
+        float v = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < NSLOT; sl++) v += ring[((sl << 1) | kv) * kFragFloats + (slot * per + r) * 32 + lane];
+        dst[(slot * per + r) * 32 + lane] = v;
+    }
+    if (slot == 0 && g == 0) {
+        dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
+        dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+    }
+}
+
+} // namespace half_decode
+
+int decode_half_configure(int device) {
+    (void)device;
+    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     half_decode::kSmem));
+    return SAETTA_OK;
+}
+
+int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t *status, uint32_t m, uint32_t row_step,
+                       int splits, uint32_t capacity, const saetta_token_params *params, cudaStream_t stream) {
+    half_decode::Args a{};
+    a.k = static_cast<const uint8_t *>(kv.k), a.v = static_cast<const uint8_t *>(kv.v);
+    a.q = q, a.parts = parts, a.status = status, a.params = params;
+    a.m = m, a.row_step = row_step, a.capacity = capacity;
+    const int ctas = splits; // one part per CTA, as many as the merge will read; CTAs past the last tile leave an empty part
+    SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel, dim3(ctas, m), dim3(half_decode::kThreads), half_decode::kSmem,
+                           stream, a));
+    return SAETTA_OK;
+}
+
+} // namespace saetta

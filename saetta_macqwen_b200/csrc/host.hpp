@@ -164,6 +164,11 @@ int decode_quant_static(int device, const KvView &kv, size_t capacity, const flo
                         const float *q_and_gate, float *out, const saetta_token_params *params,
                         cudaStream_t stream);
 
+// decode_half.cu: tensor-core split-KV over binary16 rows (2 kv heads); partials in decode_quant.cu's format.
+int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t *status, uint32_t m, uint32_t row_step,
+                       int splits, uint32_t capacity, const saetta_token_params *params, cudaStream_t stream);
+int decode_half_configure(int device);
+
 // decode_exact.cu: f32 arithmetic over f32 / 16-bit rows.
 int launch_decode_exact(const KvView &kv, const float *q, float *parts, uint32_t m,
                         uint32_t row_step, int splits, uint32_t capacity,
