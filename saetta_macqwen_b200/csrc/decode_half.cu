@@ -20,8 +20,10 @@
 //  * Online softmax and the end-of-range merge as in the quantised kernel; the
 //    partials leave in the same fragment order, so merge.cu and the exchange
 //    across GPUs serve both.
-//  * One query row per pass: m rows are m passes (gridDim.y), each reading the
-//    cache again.  Every wait on an mbarrier is bounded.
+//  * One query row per pass, or -- for several rows -- two, which then share every
+//    load of the cache: the 16 MMA rows are the two rows' heads (queries rounded to
+//    binary16, P a single operand).  m rows are ceil(m/2) passes (gridDim.y).
+//    Every wait on an mbarrier is bounded.
 #include <algorithm>
 
 #include "host.hpp"
@@ -45,8 +47,8 @@ constexpr int kPartKv = kFragFloats + 16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;
 constexpr int kPrefetchTiles = 2;
-constexpr int kSmem = kStages * kStageBytes + kWarps * 16 * 4 + 2 * kStages * 8 + 16;
-static_assert(kWarps * kFragFloats * 4 <= kStages * kStageBytes, "the end-of-range merge parks in the ring");
+constexpr int kSmem = kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 16;
+static_assert(kWarps * 2 * kFragFloats * 4 <= kStages * kStageBytes, "the end-of-range merge parks in the ring");
 
 struct Args {
     const uint8_t *k, *v; // [capacity][2][256] binary16
@@ -63,11 +65,12 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
                  : "r"(smem_u32(smem_row)));
 }
 
+template <int NR>
 __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *stages = smem;
     float *ml = reinterpret_cast<float *>(smem + kStages * kStageBytes); // [warp][m of 8 heads, l of 8 heads]
-    uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 16);
+    uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
     uint64_t *empty = full + kStages;
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + kStages);
 
@@ -81,18 +84,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
         mbar_fence_init();
     }
     __syncthreads();
-    const uint32_t row = blockIdx.y; // the query row of this pass
-    auto range = [&](uint32_t kv_len, uint32_t &tb, uint32_t &te, uint32_t &n_row) {
-        n_row = min(kv_len + row * a.row_step, a.capacity); // keys this row sees
-        const uint32_t tiles = (n_row + kTile - 1) / kTile;
+    const uint32_t row0 = blockIdx.y * NR; // the first query row of this pass
+    auto range = [&](uint32_t kv_len, uint32_t &tb, uint32_t &te, uint32_t &n_any) {
+        const uint32_t last = min(row0 + NR, a.m) - 1; // the pass's last live row sees the most keys
+        n_any = min(kv_len + last * a.row_step, a.capacity);
+        const uint32_t tiles = (n_any + kTile - 1) / kTile;
         tb = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
         te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
     };
     // While the kernel before this one drains, pull the head of this CTA's range into L2 (the range
     // comes from a possibly stale kv_len: a hint only, everything is read again after the wait).
     if (warp == kWarps && lane == 0) {
-        uint32_t tb, te, n_row;
-        range(*reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len), tb, te, n_row);
+        uint32_t tb, te, n_hint;
+        range(*reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len), tb, te, n_hint);
         const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
         for (uint32_t t = 0; t < nt; t++) {
             l2_prefetch(a.k + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
@@ -101,8 +105,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
     }
     pdl_wait();              // q, the token parameters and the cache may come from the kernel before
     pdl_launch_dependents(); // the merge kernel may be scheduled as SMs free up; it waits for this grid
-    uint32_t tile_begin, tile_end, n_row;
-    range(a.params->kv_len, tile_begin, tile_end, n_row);
+    uint32_t tile_begin, tile_end, n_any;
+    range(a.params->kv_len, tile_begin, tile_end, n_any);
+    uint32_t n_row[NR]; // keys each row of the pass sees (0 for a row past m)
+    uint32_t n_all = n_any;
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+        n_row[r] = row0 + r < a.m ? min(a.params->kv_len + (row0 + r) * a.row_step, a.capacity) : 0u;
+        if (row0 + r < a.m) n_all = min(n_all, n_row[r]);
+    }
 
     if (warp >= kWarps) {
         // ---------------------------------------------------------------- producer
@@ -142,11 +153,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
     const int kv = warp & 1, slot = warp >> 1;
     const int g = lane >> 2, i = lane & 3;
 
-    // Query fragments of head kv*8+g, scaled by log2(e)/16, split into two halves.  k-step ks covers,
-    // for lane i, dims 32*(ks/2) + 8*i + 4*(ks%2) + {0,1 | 2,3}: what a 128-bit load of K holds.
+    // Query fragments of head kv*8+g, scaled by log2(e)/16.  One row per pass: split into two halves, the
+    // 16 MMA rows are the heads' high and low halves.  Two rows: rows 0..7 are the first row's heads,
+    // 8..15 the second's, rounded to binary16.  k-step ks covers, for lane i, dims
+    // 32*(ks/2) + 8*i + 4*(ks%2) + {0,1 | 2,3}: what a 128-bit load of K holds.
     uint32_t qh[16][2], ql[16][2];
-    {
-        const float *qp = a.q + ((size_t(row) * 16) + kv * 8 + g) * kDim;
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+        const uint32_t qrow = row0 + r < a.m ? row0 + r : 0;
+        const float *qp = a.q + ((size_t(qrow) * 16) + kv * 8 + g) * kDim;
 #pragma unroll
         for (int b = 0; b < 8; b++) {
             const float4 v0 = *reinterpret_cast<const float4 *>(qp + b * 32 + i * 8);
@@ -162,17 +177,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
 #pragma unroll
             for (int j = 0; j < 2; j++)
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    qh[2 * b + j][r] = pack_half2(hi[4 * j + 2 * r], hi[4 * j + 2 * r + 1]);
-                    ql[2 * b + j][r] = pack_half2(lo[4 * j + 2 * r], lo[4 * j + 2 * r + 1]);
+                for (int e = 0; e < 2; e++) {
+                    if (r == 0) qh[2 * b + j][e] = pack_half2(hi[4 * j + 2 * e], hi[4 * j + 2 * e + 1]);
+                    if (NR == 1) ql[2 * b + j][e] = pack_half2(lo[4 * j + 2 * e], lo[4 * j + 2 * e + 1]);
+                    if (NR == 2 && r == 1) ql[2 * b + j][e] = pack_half2(hi[4 * j + 2 * e], hi[4 * j + 2 * e + 1]);
                 }
         }
     }
 
-    float O[16][4];
+    float O[NR][16][4];
+    float Mref[NR], lsum[NR]; // of head g (this thread's row of the score MMA), per query row
 #pragma unroll
-    for (int e = 0; e < 16; e++) O[e][0] = O[e][1] = O[e][2] = O[e][3] = 0.f;
-    float Mref = -INFINITY, lsum = 0.f; // of head g (this thread's row of the score MMA)
+    for (int r = 0; r < NR; r++) {
+#pragma unroll
+        for (int e = 0; e < 16; e++) O[r][e][0] = O[r][e][1] = O[r][e][2] = O[r][e][3] = 0.f;
+        Mref[r] = -INFINITY, lsum[r] = 0.f;
+    }
 
     uint32_t it = 0;
     for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
@@ -190,12 +210,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
         for (int sub = 0; sub < kTile / kSub; sub++) {
             const uint32_t q_idx = 2 * (t - tile_begin) + sub;
             const uint32_t tok0 = t * kTile + sub * kSub; // first token of the sub-tile
-            if ((q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_row) continue;
-            const bool partial = tok0 + kSub > n_row;
+            if ((q_idx % NSLOT) != uint32_t(slot) || tok0 >= n_any) continue;
+            const bool partial = tok0 + kSub > n_all;
             const int lt = sub * kSub;
 
-            // ------------------------------------------------ scores S[head][token]
-            float S[2][2];
+            // ------------------------------------------------ scores S[row][head][token]
+            float S[NR][2][2];
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
                 const uint8_t *krow = sk + (lt + nt * 8 + g) * kKRow + i * 16; // token g of the 8-token tile
@@ -206,53 +226,68 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
                     mma_f16(acc, qh[2 * b][0], ql[2 * b][0], qh[2 * b][1], ql[2 * b][1], w.x, w.y);
                     mma_f16(acc, qh[2 * b + 1][0], ql[2 * b + 1][0], qh[2 * b + 1][1], ql[2 * b + 1][1], w.z, w.w);
                 }
-                S[nt][0] = acc[0] + acc[2], S[nt][1] = acc[1] + acc[3];
+                if (NR == 1) {
+                    S[0][nt][0] = acc[0] + acc[2], S[0][nt][1] = acc[1] + acc[3];
+                } else {
+                    S[0][nt][0] = acc[0], S[0][nt][1] = acc[1], S[NR - 1][nt][0] = acc[2], S[NR - 1][nt][1] = acc[3];
+                }
                 if (partial) { // rows past the end may hold anything: assigned, never computed with
-                    if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
-                    if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
+#pragma unroll
+                    for (int r = 0; r < NR; r++) {
+                        if (tok0 + nt * 8 + 2 * i >= n_row[r]) S[r][nt][0] = -INFINITY;
+                        if (tok0 + nt * 8 + 2 * i + 1 >= n_row[r]) S[r][nt][1] = -INFINITY;
+                    }
                 }
             }
 
             // ------------------------------------------------ online softmax of head g (log2 units)
-            float mx = fmaxf(fmaxf(S[0][0], S[0][1]), fmaxf(S[1][0], S[1][1]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const bool need = mx > Mref + kRescale;
-            if (__any_sync(0xffffffffu, need)) {
-                const float f = need ? exp2f(Mref - mx) : 1.f; // exp2f(-inf) = 0 on the first tile
-                if (need) Mref = mx, lsum *= f;
-                // the accumulators' columns are heads 2i, 2i+1: fetch their factors from lanes g = 2i, 2i+1
-                const float f0 = __shfl_sync(0xffffffffu, f, 8 * i), f1 = __shfl_sync(0xffffffffu, f, 8 * i + 4);
+            uint32_t pb[NR][2], pl[2];
 #pragma unroll
-                for (int e = 0; e < 16; e++) O[e][0] *= f0, O[e][1] *= f1, O[e][2] *= f0, O[e][3] *= f1;
+            for (int r = 0; r < NR; r++) {
+                float mx = fmaxf(fmaxf(S[r][0][0], S[r][0][1]), fmaxf(S[r][1][0], S[r][1][1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const bool need = mx > Mref[r] + kRescale;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float f = need ? exp2f(Mref[r] - mx) : 1.f; // exp2f(-inf) = 0 on the first tile
+                    if (need) Mref[r] = mx, lsum[r] *= f;
+                    // the accumulators' columns are heads 2i, 2i+1: fetch their factors from lanes g = 2i, 2i+1
+                    const float f0 = __shfl_sync(0xffffffffu, f, 8 * i), f1 = __shfl_sync(0xffffffffu, f, 8 * i + 4);
+#pragma unroll
+                    for (int e = 0; e < 16; e++) O[r][e][0] *= f0, O[r][e][1] *= f1, O[r][e][2] *= f0, O[r][e][3] *= f1;
+                }
+                const float mu = Mref[r] == -INFINITY ? 0.f : Mref[r]; // a row with no key yet: every p is 0
+                const float p00 = exp2f(S[r][0][0] - mu), p01 = exp2f(S[r][0][1] - mu);
+                const float p10 = exp2f(S[r][1][0] - mu), p11 = exp2f(S[r][1][1] - mu);
+                lsum[r] += (p00 + p01) + (p10 + p11);
+                // B[k = token][n = head]: the lane's own score columns, no data moves between lanes.
+                pb[r][0] = pack_half2(p00, p01), pb[r][1] = pack_half2(p10, p11);
+                if (NR == 1) {
+                    // One row: P goes in as two binary16 halves (what the first rounding dropped is the
+                    // second operand), so the value product keeps f32 precision as the score product
+                    // does; the kernel is bound by the cache's bytes, the second MMA is free.
+                    const float2 h0 = h2f2(pb[0][0]), h1 = h2f2(pb[0][1]);
+                    pl[0] = pack_half2(p00 - h0.x, p01 - h0.y), pl[1] = pack_half2(p10 - h1.x, p11 - h1.y);
+                }
             }
-            const float p00 = exp2f(S[0][0] - Mref), p01 = exp2f(S[0][1] - Mref);
-            const float p10 = exp2f(S[1][0] - Mref), p11 = exp2f(S[1][1] - Mref);
-            lsum += (p00 + p01) + (p10 + p11);
-            // B[k = token][n = head]: the lane's own score columns, no data moves between lanes.  P goes in
-            // as two binary16 halves (what the first rounding dropped is the second operand), so the
-            // value product keeps f32 precision as the score product does; the kernel is bound by the
-            // cache's bytes, the second MMA is free.
-            const uint32_t pb0 = pack_half2(p00, p01), pb1 = pack_half2(p10, p11);
-            const float2 h0 = h2f2(pb0), h1 = h2f2(pb1);
-            const uint32_t pl0 = pack_half2(p00 - h0.x, p01 - h0.y), pl1 = pack_half2(p10 - h1.x, p11 - h1.y);
 
             // ------------------------------------------------ O^T[dim][head] += V^T P^T
             // ldmatrix.trans: lanes 8j..8j+7 give the rows of matrix j -- tokens 0..7 (j < 2) or 8..15 of the
             // sub-tile at dims 0..7 (j even) or 8..15 of the 16-dim slice -- and get back token pairs of one dim.
             const uint8_t *vrow = sv + (lt + ((lane >> 4) << 3) + (lane & 7)) * kVRow + ((lane >> 3) & 1) * 16;
             uint32_t mask01 = 0xffffffffu, mask23 = 0xffffffffu;
-            if (partial) {
-                mask01 = (tok0 + 2 * i < n_row ? 0xffffu : 0u) | (tok0 + 2 * i + 1 < n_row ? 0xffff0000u : 0u);
-                mask23 = (tok0 + 2 * i + 8 < n_row ? 0xffffu : 0u) | (tok0 + 2 * i + 9 < n_row ? 0xffff0000u : 0u);
+            if (partial) { // what lies past the longest row may be anything: keep it out of 0 * x
+                mask01 = (tok0 + 2 * i < n_any ? 0xffffu : 0u) | (tok0 + 2 * i + 1 < n_any ? 0xffff0000u : 0u);
+                mask23 = (tok0 + 2 * i + 8 < n_any ? 0xffffu : 0u) | (tok0 + 2 * i + 9 < n_any ? 0xffff0000u : 0u);
             }
 #pragma unroll
             for (int mt = 0; mt < 16; mt++) {
                 uint32_t av[4];
                 ldmatrix_x4_trans(av, vrow + mt * 32);
                 if (partial) av[0] &= mask01, av[1] &= mask01, av[2] &= mask23, av[3] &= mask23;
-                mma_f16(O[mt], av[0], av[1], av[2], av[3], pb0, pb1);
-                mma_f16(O[mt], av[0], av[1], av[2], av[3], pl0, pl1);
+#pragma unroll
+                for (int r = 0; r < NR; r++) mma_f16(O[r][mt], av[0], av[1], av[2], av[3], pb[r][0], pb[r][1]);
+                if (NR == 1) mma_f16(O[0][mt], av[0], av[1], av[2], av[3], pl[0], pl[1]);
             }
         }
         __syncwarp();
@@ -260,61 +295,71 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
     }
 
     // ---------------------------------------------------------------- end of range
-    lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-    lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-    float Mc2[2], l[2];
-    Mc2[0] = __shfl_sync(0xffffffffu, Mref, 8 * i), Mc2[1] = __shfl_sync(0xffffffffu, Mref, 8 * i + 4);
-    l[0] = __shfl_sync(0xffffffffu, lsum, 8 * i), l[1] = __shfl_sync(0xffffffffu, lsum, 8 * i + 4);
-    // Warps that share a kv head agree on one maximum, scale, and add up in a fixed order (deterministic).
-    if (g == 0) {
-        ml[warp * 16 + 2 * i] = Mc2[0], ml[warp * 16 + 2 * i + 1] = Mc2[1];
-        ml[warp * 16 + 8 + 2 * i] = l[0], ml[warp * 16 + 8 + 2 * i + 1] = l[1];
+    // Warps that share a kv head agree on one maximum per row, scale, and add up in a fixed order
+    // (deterministic).  After the first barrier no warp reads the copy ring any more (a producer that
+    // gave up has raised the status word; the result is void then): every warp parks its scaled
+    // accumulators there in the merge kernel's fragment order -- head h, dim d at
+    // (4*mt + c)*32 + 4*((d >> 3) & 7) + (h >> 1), mt = 4*(d >> 6) + (d & 3), c = (h & 1) + ((d >> 1) & 2)
+    // -- and then each warp adds up its share.
+    float Mc2[NR][2], l[NR][2];
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+        lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
+        lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 2);
+        Mc2[r][0] = __shfl_sync(0xffffffffu, Mref[r], 8 * i), Mc2[r][1] = __shfl_sync(0xffffffffu, Mref[r], 8 * i + 4);
+        l[r][0] = __shfl_sync(0xffffffffu, lsum[r], 8 * i), l[r][1] = __shfl_sync(0xffffffffu, lsum[r], 8 * i + 4);
+        if (g == 0) {
+            float *m = ml + (warp * NR + r) * 16;
+            m[2 * i] = Mc2[r][0], m[2 * i + 1] = Mc2[r][1];
+            m[8 + 2 * i] = l[r][0], m[8 + 2 * i + 1] = l[r][1];
+        }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
-    float Mc[2] = {-INFINITY, -INFINITY}, lc[2] = {0.f, 0.f};
-#pragma unroll
-    for (int sl = 0; sl < NSLOT; sl++) {
-        const int w = (sl << 1) | kv;
-        Mc[0] = fmaxf(Mc[0], ml[w * 16 + 2 * i]);
-        Mc[1] = fmaxf(Mc[1], ml[w * 16 + 2 * i + 1]);
-    }
-#pragma unroll
-    for (int sl = 0; sl < NSLOT; sl++) {
-        const int w = (sl << 1) | kv;
-        const float m0 = ml[w * 16 + 2 * i], m1 = ml[w * 16 + 2 * i + 1];
-        lc[0] += m0 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i] * exp2f(m0 - Mc[0]);
-        lc[1] += m1 == -INFINITY ? 0.f : ml[w * 16 + 8 + 2 * i + 1] * exp2f(m1 - Mc[1]);
-    }
-    const float f0 = Mc2[0] == -INFINITY ? 0.f : exp2f(Mc2[0] - Mc[0]);
-    const float f1 = Mc2[1] == -INFINITY ? 0.f : exp2f(Mc2[1] - Mc[1]);
-    // After the barrier above no warp reads the copy ring any more (a producer that gave up has raised
-    // the status word; the result is void then): every warp parks its scaled accumulators there in
-    // the merge kernel's fragment order -- head h, dim d at (4*mt + c)*32 + 4*((d >> 3) & 7) + (h >> 1),
-    // mt = 4*(d >> 6) + (d & 3), c = (h & 1) + ((d >> 1) & 2) -- and then each warp adds up its share.
+    float Mc[NR][2], lc[NR][2];
     float *ring = reinterpret_cast<float *>(stages);
-    {
-        float *mine = ring + warp * kFragFloats + i;
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+        Mc[r][0] = Mc[r][1] = -INFINITY, lc[r][0] = lc[r][1] = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < NSLOT; sl++) {
+            const float *m = ml + ((((sl << 1) | kv)) * NR + r) * 16;
+            Mc[r][0] = fmaxf(Mc[r][0], m[2 * i]), Mc[r][1] = fmaxf(Mc[r][1], m[2 * i + 1]);
+        }
+#pragma unroll
+        for (int sl = 0; sl < NSLOT; sl++) {
+            const float *m = ml + ((((sl << 1) | kv)) * NR + r) * 16;
+            const float m0 = m[2 * i], m1 = m[2 * i + 1];
+            lc[r][0] += m0 == -INFINITY ? 0.f : m[8 + 2 * i] * exp2f(m0 - Mc[r][0]);
+            lc[r][1] += m1 == -INFINITY ? 0.f : m[8 + 2 * i + 1] * exp2f(m1 - Mc[r][1]);
+        }
+        const float f0 = Mc2[r][0] == -INFINITY ? 0.f : exp2f(Mc2[r][0] - Mc[r][0]);
+        const float f1 = Mc2[r][1] == -INFINITY ? 0.f : exp2f(Mc2[r][1] - Mc[r][1]);
+        float *mine = ring + (warp * NR + r) * kFragFloats + i;
 #pragma unroll
         for (int mt = 0; mt < 16; mt++)
 #pragma unroll
             for (int c = 0; c < 4; c++) { // head 2i + (c & 1), dim 16*mt + g + 8*(c >> 1)
                 const int mtq = 4 * (mt >> 2) + (g & 3), cq = (c & 1) + 2 * ((g >> 2) & 1);
-                mine[(4 * mtq + cq) * 32 + 4 * ((2 * mt + (c >> 1)) & 7)] = O[mt][c] * ((c & 1) ? f1 : f0);
+                mine[(4 * mtq + cq) * 32 + 4 * ((2 * mt + (c >> 1)) & 7)] = O[r][mt][c] * ((c & 1) ? f1 : f0);
             }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
-    float *dst = a.parts + ((size_t(blockIdx.x) * a.m + row) * kKv + kv) * kPartKv;
-    constexpr int per = 64 / NSLOT;
 #pragma unroll
-    for (int r = 0; r < per; r++) {
-        float v = 0.f;
+    for (int r = 0; r < NR; r++) {
+        if (row0 + r >= a.m) continue;
+        float *dst = a.parts + ((size_t(blockIdx.x) * a.m + row0 + r) * kKv + kv) * kPartKv;
+        constexpr int per = 64 / NSLOT;
 #pragma unroll
-        for (int sl = 0; sl < NSLOT; sl++) v += ring[((sl << 1) | kv) * kFragFloats + (slot * per + r) * 32 + lane];
-        dst[(slot * per + r) * 32 + lane] = v;
-    }
-    if (slot == 0 && g == 0) {
-        dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
-        dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+        for (int k = 0; k < per; k++) {
+            float v = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < NSLOT; sl++) v += ring[((((sl << 1) | kv)) * NR + r) * kFragFloats + (slot * per + k) * 32 + lane];
+            dst[(slot * per + k) * 32 + lane] = v;
+        }
+        if (slot == 0 && g == 0) {
+            dst[kFragFloats + 2 * i] = Mc[r][0], dst[kFragFloats + 2 * i + 1] = Mc[r][1];
+            dst[kFragFloats + 8 + 2 * i] = lc[r][0], dst[kFragFloats + 8 + 2 * i + 1] = lc[r][1];
+        }
     }
 }
 
@@ -322,7 +367,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
 
 int decode_half_configure(int device) {
     (void)device;
-    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     half_decode::kSmem));
+    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      half_decode::kSmem));
     return SAETTA_OK;
 }
@@ -334,8 +381,12 @@ int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t 
     a.q = q, a.parts = parts, a.status = status, a.params = params;
     a.m = m, a.row_step = row_step, a.capacity = capacity;
     const int ctas = splits; // one part per CTA, as many as the merge will read; CTAs past the last tile leave an empty part
-    SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel, dim3(ctas, m), dim3(half_decode::kThreads), half_decode::kSmem,
-                           stream, a));
+    if (m == 1)
+        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1>, dim3(ctas, 1), dim3(half_decode::kThreads),
+                               half_decode::kSmem, stream, a));
+    else // two rows per pass share every load of the cache
+        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<2>, dim3(ctas, (m + 1) / 2), dim3(half_decode::kThreads),
+                               half_decode::kSmem, stream, a));
     return SAETTA_OK;
 }
 

@@ -64,6 +64,28 @@ def test_plain_cache_matches_cpu_at_several_lengths(oracle, dtype):
         assert rel_rms(got, want) < 5e-6, (dtype, n, rel_rms(got, want))
 
 
+@pytest.mark.parametrize("m", [1, 3])
+def test_half_cache_long_context(oracle, m):
+    """A binary16 cache long enough that every CTA walks several tiles and its copy ring wraps:
+    one row (f32-exact: 5e-6) and three rows (two passes, rows rounded to binary16)."""
+    tokens = 40000 + m - 1
+    capacity = (tokens + 127) // 128 * 128
+    keys, values = oracle.round_f16(oracle.normal(tokens * ROW, 21)), oracle.round_f16(oracle.normal(tokens * ROW, 22))
+    q, qg = oracle.normal(m * HEADS * DIM, 23), oracle.normal(m * HEADS * 2 * DIM, 24)
+    cache = sa.GpuKvCache(0, 16, capacity, dtype=sa.F16)
+    cache.store_at(dev(keys), dev(values), 0, tokens)
+    op = sa.AttentionRows(0, HEADS, KV, capacity, 4)
+    pos = tokens - m
+    got = run(op, m, q, qg, pos, cache=cache)
+    want = oracle.attention_rows(q, qg, keys, values, [pos + r + 1 for r in range(m)], threads=8)
+    if m == 1:
+        assert rel_rms(got, want) < 5e-6, rel_rms(got, want)
+    else:
+        assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3, (max_abs(got, want), rel_rms(got, want))
+    again = run(op, m, q, qg, pos, cache=cache)
+    assert np.array_equal(got, again)  # fixed summation order: replays are bit-identical
+
+
 @pytest.mark.parametrize("bits", [8, 4])
 def test_quantized_matches_cpu(oracle, bits):
     capacity = 1024
