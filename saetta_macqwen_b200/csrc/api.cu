@@ -551,8 +551,9 @@ static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView 
         return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
                                  part_out, st, group ? &group->push : nullptr);
     }
-    if (kv.bits == 16 && kv.dtype == SAETTA_F16 && kv.kv_heads == 2 && aligned16(kv.k) && aligned16(kv.v)) {
-        // the reference's own cache format: tensor-core kernel, partials and merge as for the quantised cache
+    if (kv.bits == 16 && kv.kv_heads == 2 && aligned16(kv.k) && aligned16(kv.v)) {
+        // binary16 (the reference's own cache format) or bfloat16 rows: tensor-core kernel, partials and merge as
+        // for the quantised cache
         if (int rc = launch_decode_half(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
                                         uint32_t(kv_capacity), params, st))
             return rc;

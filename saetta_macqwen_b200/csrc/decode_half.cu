@@ -1,4 +1,4 @@
-// Split-KV decode / MTP-verify attention over a binary16 KV cache, on the tensor cores.
+// Split-KV decode / MTP-verify attention over a 16-bit (binary16 or bfloat16) KV cache, on the tensor cores.
 //
 // Stands in for attention_partial_mma (kernels/attention.metal:127-236) and
 // attention_partial_rows<16> (kernels/attention_rows.metal:108-292) of the
@@ -65,8 +65,39 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
                  : "r"(smem_u32(smem_row)));
 }
 
-template <int NR>
+// D += A(16x16, row) * B(16x8, col), bfloat16 operands, f32 accumulate.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Two floats as a pair of 16-bit values of the cache's type, and back.
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    if (BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+    return pack_half2(lo, hi);
+}
+template <bool BF16>
+__device__ __forceinline__ float2 unpack16(uint32_t w) {
+    if (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    return h2f2(w);
+}
+template <bool BF16>
+__device__ __forceinline__ void mma16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if (BF16) mma_bf16(c, a0, a1, a2, a3, b0, b1);
+    else mma_f16(c, a0, a1, a2, a3, b0, b1);
+}
+
+// NR query rows per pass; BF16: the cache holds bfloat16 (one row per pass only: with 8-bit significands
+// both the query and P need their second halves).
+template <int NR, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) {
+    static_assert(NR == 1 || !BF16, "two rows per pass need binary16");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *stages = smem;
     float *ml = reinterpret_cast<float *>(smem + kStages * kStageBytes); // [warp][m of 8 heads, l of 8 heads]
@@ -171,16 +202,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
 #pragma unroll
             for (int d = 0; d < 8; d++) {
                 const float s = x[d] * (kLog2e * 0.0625f);
-                hi[d] = __half2float(__float2half_rn(s));
-                lo[d] = __half2float(__float2half_rn(s - hi[d]));
+                hi[d] = unpack16<BF16>(pack16<BF16>(s, 0.f)).x;
+                lo[d] = s - hi[d]; // rounded when packed
             }
 #pragma unroll
             for (int j = 0; j < 2; j++)
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    if (r == 0) qh[2 * b + j][e] = pack_half2(hi[4 * j + 2 * e], hi[4 * j + 2 * e + 1]);
-                    if (NR == 1) ql[2 * b + j][e] = pack_half2(lo[4 * j + 2 * e], lo[4 * j + 2 * e + 1]);
-                    if (NR == 2 && r == 1) ql[2 * b + j][e] = pack_half2(hi[4 * j + 2 * e], hi[4 * j + 2 * e + 1]);
+                    if (r == 0) qh[2 * b + j][e] = pack16<BF16>(hi[4 * j + 2 * e], hi[4 * j + 2 * e + 1]);
+                    if (NR == 1) ql[2 * b + j][e] = pack16<BF16>(lo[4 * j + 2 * e], lo[4 * j + 2 * e + 1]);
+                    if (NR == 2 && r == 1) ql[2 * b + j][e] = pack16<BF16>(hi[4 * j + 2 * e], hi[4 * j + 2 * e + 1]);
                 }
         }
     }
@@ -223,8 +254,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
 #pragma unroll
                 for (int b = 0; b < 8; b++) {
                     const uint4 w = *reinterpret_cast<const uint4 *>(krow + b * 64);
-                    mma_f16(acc, qh[2 * b][0], ql[2 * b][0], qh[2 * b][1], ql[2 * b][1], w.x, w.y);
-                    mma_f16(acc, qh[2 * b + 1][0], ql[2 * b + 1][0], qh[2 * b + 1][1], ql[2 * b + 1][1], w.z, w.w);
+                    mma16<BF16>(acc, qh[2 * b][0], ql[2 * b][0], qh[2 * b][1], ql[2 * b][1], w.x, w.y);
+                    mma16<BF16>(acc, qh[2 * b + 1][0], ql[2 * b + 1][0], qh[2 * b + 1][1], ql[2 * b + 1][1], w.z, w.w);
                 }
                 if (NR == 1) {
                     S[0][nt][0] = acc[0] + acc[2], S[0][nt][1] = acc[1] + acc[3];
@@ -261,13 +292,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
                 const float p10 = exp2f(S[r][1][0] - mu), p11 = exp2f(S[r][1][1] - mu);
                 lsum[r] += (p00 + p01) + (p10 + p11);
                 // B[k = token][n = head]: the lane's own score columns, no data moves between lanes.
-                pb[r][0] = pack_half2(p00, p01), pb[r][1] = pack_half2(p10, p11);
+                pb[r][0] = pack16<BF16>(p00, p01), pb[r][1] = pack16<BF16>(p10, p11);
                 if (NR == 1) {
                     // One row: P goes in as two binary16 halves (what the first rounding dropped is the
                     // second operand), so the value product keeps f32 precision as the score product
                     // does; the kernel is bound by the cache's bytes, the second MMA is free.
-                    const float2 h0 = h2f2(pb[0][0]), h1 = h2f2(pb[0][1]);
-                    pl[0] = pack_half2(p00 - h0.x, p01 - h0.y), pl[1] = pack_half2(p10 - h1.x, p11 - h1.y);
+                    const float2 h0 = unpack16<BF16>(pb[0][0]), h1 = unpack16<BF16>(pb[0][1]);
+                    pl[0] = pack16<BF16>(p00 - h0.x, p01 - h0.y), pl[1] = pack16<BF16>(p10 - h1.x, p11 - h1.y);
                 }
             }
 
@@ -286,8 +317,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
                 ldmatrix_x4_trans(av, vrow + mt * 32);
                 if (partial) av[0] &= mask01, av[1] &= mask01, av[2] &= mask23, av[3] &= mask23;
 #pragma unroll
-                for (int r = 0; r < NR; r++) mma_f16(O[r][mt], av[0], av[1], av[2], av[3], pb[r][0], pb[r][1]);
-                if (NR == 1) mma_f16(O[0][mt], av[0], av[1], av[2], av[3], pl[0], pl[1]);
+                for (int r = 0; r < NR; r++) mma16<BF16>(O[r][mt], av[0], av[1], av[2], av[3], pb[r][0], pb[r][1]);
+                if (NR == 1) mma16<BF16>(O[0][mt], av[0], av[1], av[2], av[3], pl[0], pl[1]);
             }
         }
         __syncwarp();
@@ -367,9 +398,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
 
 int decode_half_configure(int device) {
     (void)device;
-    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      half_decode::kSmem));
-    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     half_decode::kSmem));
+    SAETTA_CUDA(cudaFuncSetAttribute(half_decode::decode_half_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      half_decode::kSmem));
     return SAETTA_OK;
 }
@@ -381,11 +414,14 @@ int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t 
     a.q = q, a.parts = parts, a.status = status, a.params = params;
     a.m = m, a.row_step = row_step, a.capacity = capacity;
     const int ctas = splits; // one part per CTA, as many as the merge will read; CTAs past the last tile leave an empty part
-    if (m == 1)
-        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1>, dim3(ctas, 1), dim3(half_decode::kThreads),
+    if (kv.dtype == SAETTA_BF16)
+        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, true>, dim3(ctas, m), dim3(half_decode::kThreads),
+                               half_decode::kSmem, stream, a));
+    else if (m == 1)
+        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, false>, dim3(ctas, 1), dim3(half_decode::kThreads),
                                half_decode::kSmem, stream, a));
     else // two rows per pass share every load of the cache
-        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<2>, dim3(ctas, (m + 1) / 2), dim3(half_decode::kThreads),
+        SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<2, false>, dim3(ctas, (m + 1) / 2), dim3(half_decode::kThreads),
                                half_decode::kSmem, stream, a));
     return SAETTA_OK;
 }

@@ -60,8 +60,11 @@ def test_plain_cache_matches_cpu_at_several_lengths(oracle, dtype):
         got = run(op, 1, q, qg, n - 1, keys=kd, values=vd, dtype=dtype)
         want = oracle.attention_rows(q, qg, keys, values, [n])
         assert np.isfinite(got).all()
-        assert max_abs(got, want) < 2e-5, (dtype, n, max_abs(got, want))
-        assert rel_rms(got, want) < 5e-6, (dtype, n, rel_rms(got, want))
+        # f32 rows: f32 arithmetic; binary16 rows: two 11-bit halves of q and of P, as good as f32;
+        # bfloat16 rows: two 8-bit halves (16 bits), still 20x inside the 16-bit contract (2e-3 / 1e-3)
+        tol_abs, tol_rms = (2e-4, 5e-5) if dtype == sa.BF16 else (2e-5, 5e-6)
+        assert max_abs(got, want) < tol_abs, (dtype, n, max_abs(got, want))
+        assert rel_rms(got, want) < tol_rms, (dtype, n, rel_rms(got, want))
 
 
 @pytest.mark.parametrize("m", [1, 3])
