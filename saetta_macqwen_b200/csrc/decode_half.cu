@@ -8,9 +8,11 @@
 //
 //  * One persistent CTA per SM owns a contiguous range of 32-token tiles.  A
 //    producer warp streams each tile into a ring of shared-memory stages with
-//    bulk (TMA engine) copies, one per token row and side, signalled on
-//    mbarriers.  Rows land 1088 (keys) and 1040 (values) bytes apart instead of
-//    1024, which keeps the operand loads below free of bank conflicts.
+//    TMA tensor copies signalled on mbarriers: per side eight slabs of 32 tokens
+//    x 64 dims (128-byte rows, 128-byte swizzle), so that neither the key loads
+//    nor ldmatrix below meet bank conflicts.  (One bulk copy per token row into
+//    padded rows was tried first: 64 requests of 1 KB per tile held the kernel
+//    at 3.6 TB/s, the TMA unit's rate for small requests.)
 //  * Eight consumer warps each own one kv head and a share of the 16-token
 //    sub-tiles.  Scores: mma.sync m16n8k16 with the 16 rows = high and low halves
 //    of the 8 query heads (the query keeps f32 precision), K straight from shared
@@ -24,6 +26,8 @@
 //    load of the cache: the 16 MMA rows are the two rows' heads (queries rounded to
 //    binary16, P a single operand).  m rows are ceil(m/2) passes (gridDim.y).
 //    Every wait on an mbarrier is bounded.
+#include <cuda.h>
+
 #include <algorithm>
 
 #include "host.hpp"
@@ -38,16 +42,16 @@ constexpr int kWarps = 8;   // consumer warps
 constexpr int kThreads = (kWarps + 4) * 32;
 constexpr int kKv = 2;
 constexpr int kRowBytes = kKv * kDim * 2;   // one token of one side in the cache
-constexpr int kKRow = kRowBytes + 64;       // shared-memory pitch of key rows
-constexpr int kVRow = kRowBytes + 16;       // ... and of value rows
-constexpr int kStageBytes = kTile * (kKRow + kVRow);
+constexpr int kSlab = kTile * 128;          // 32 tokens x 64 dims, 128-byte rows
+constexpr int kSideBytes = kKv * 4 * kSlab; // the tile's keys (or values): slab = kv*4 + dims/64
+constexpr int kStageBytes = 2 * kSideBytes;
 constexpr int kStages = 3;
 constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in the merge kernel's fragment order
 constexpr int kPartKv = kFragFloats + 16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;
 constexpr int kPrefetchTiles = 2;
-constexpr int kSmem = kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 16;
+constexpr int kSmem = 1024 /*align*/ + kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 16;
 static_assert(kWarps * 2 * kFragFloats * 4 <= kStages * kStageBytes, "the end-of-range merge parks in the ring");
 
 struct Args {
@@ -95,10 +99,23 @@ __device__ __forceinline__ void mma16(float (&c)[4], uint32_t a0, uint32_t a1, u
 
 // NR query rows per pass; BF16: the cache holds bfloat16 (one row per pass only: with 8-bit significands
 // both the query and P need their second halves).
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Byte offset, inside a side of a stage, of 16-byte chunk `chunk` (of the 32 of a kv head's row) of token `tok`.
+__device__ __forceinline__ uint32_t swz(uint32_t kv, uint32_t tok, uint32_t chunk) {
+    return (kv * 4 + (chunk >> 3)) * kSlab + tok * 128 + (((chunk & 7) ^ (tok & 7)) << 4);
+}
+
 template <int NR, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) {
+__global__ void __launch_bounds__(kThreads, 1)
+decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Args a) {
     static_assert(NR == 1 || !BF16, "two rows per pass need binary16");
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stages = smem;
     float *ml = reinterpret_cast<float *>(smem + kStages * kStageBytes); // [warp][m of 8 heads, l of 8 heads]
     uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
@@ -162,12 +179,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
                 break;
             }
             uint8_t *dst = stages + st * kStageBytes;
-            if (lane == 0) mbar_expect_tx(&full[st], 2 * kTile * kRowBytes);
+            if (lane == 0) mbar_expect_tx(&full[st], kStageBytes);
             __syncwarp();
-            // lane = token of the tile: its key row and its value row
-            const size_t tok = size_t(t) * kTile + lane;
-            bulk_g2s(dst + lane * kKRow, a.k + tok * kRowBytes, kRowBytes, &full[st]);
-            bulk_g2s(dst + kTile * kKRow + lane * kVRow, a.v + tok * kRowBytes, kRowBytes, &full[st]);
+            // lanes 0..7: the key slabs, 8..15: the value slabs (slab = kv*4 + dims/64)
+            if (lane < 16) {
+                const int sl = lane & 7;
+                tma_load_3d(dst + (lane >> 3) * kSideBytes + sl * kSlab, lane < 8 ? &map_k : &map_v, &full[st], (sl & 3) * 64,
+                            sl >> 2, int(t * kTile));
+            }
             __syncwarp();
         }
         // Leave only once every copy this warp issued has landed (bounded): the shared memory must
@@ -235,8 +254,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
             }
             break; // skip the tiles, keep the barriers below
         }
-        const uint8_t *sk = stages + st * kStageBytes + kv * (kDim * 2);
-        const uint8_t *sv = stages + st * kStageBytes + kTile * kKRow + kv * (kDim * 2);
+        const uint8_t *sk = stages + st * kStageBytes;
+        const uint8_t *sv = sk + kSideBytes;
 #pragma unroll 1
         for (int sub = 0; sub < kTile / kSub; sub++) {
             const uint32_t q_idx = 2 * (t - tile_begin) + sub;
@@ -249,11 +268,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
             float S[NR][2][2];
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
-                const uint8_t *krow = sk + (lt + nt * 8 + g) * kKRow + i * 16; // token g of the 8-token tile
+                const uint32_t ktok = lt + nt * 8 + g; // token g of the 8-token tile
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int b = 0; b < 8; b++) {
-                    const uint4 w = *reinterpret_cast<const uint4 *>(krow + b * 64);
+                    const uint4 w = *reinterpret_cast<const uint4 *>(sk + swz(kv, ktok, b * 4 + i));
                     mma16<BF16>(acc, qh[2 * b][0], ql[2 * b][0], qh[2 * b][1], ql[2 * b][1], w.x, w.y);
                     mma16<BF16>(acc, qh[2 * b + 1][0], ql[2 * b + 1][0], qh[2 * b + 1][1], ql[2 * b + 1][1], w.z, w.w);
                 }
@@ -305,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
             // ------------------------------------------------ O^T[dim][head] += V^T P^T
             // ldmatrix.trans: lanes 8j..8j+7 give the rows of matrix j -- tokens 0..7 (j < 2) or 8..15 of the
             // sub-tile at dims 0..7 (j even) or 8..15 of the 16-dim slice -- and get back token pairs of one dim.
-            const uint8_t *vrow = sv + (lt + ((lane >> 4) << 3) + (lane & 7)) * kVRow + ((lane >> 3) & 1) * 16;
+            const uint32_t vtok = lt + ((lane >> 4) << 3) + (lane & 7), vhalf = (lane >> 3) & 1;
             uint32_t mask01 = 0xffffffffu, mask23 = 0xffffffffu;
             if (partial) { // what lies past the longest row may be anything: keep it out of 0 * x
                 mask01 = (tok0 + 2 * i < n_any ? 0xffffu : 0u) | (tok0 + 2 * i + 1 < n_any ? 0xffff0000u : 0u);
@@ -314,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_half_kernel(const Args a) 
 #pragma unroll
             for (int mt = 0; mt < 16; mt++) {
                 uint32_t av[4];
-                ldmatrix_x4_trans(av, vrow + mt * 32);
+                ldmatrix_x4_trans(av, sv + swz(kv, vtok, mt * 2 + vhalf));
                 if (partial) av[0] &= mask01, av[1] &= mask01, av[2] &= mask23, av[3] &= mask23;
 #pragma unroll
                 for (int r = 0; r < NR; r++) mma16<BF16>(O[r][mt], av[0], av[1], av[2], av[3], pb[r][0], pb[r][1]);
@@ -407,8 +426,37 @@ int decode_half_configure(int device) {
     return SAETTA_OK;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
 int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t *status, uint32_t m, uint32_t row_step,
                        int splits, uint32_t capacity, const saetta_token_params *params, cudaStream_t stream) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(SAETTA_ERR_CUDA, "decode attention: cuTensorMapEncodeTiled is not available");
+    // rows [capacity][2][256]: a box is one slab, 64 dims of one kv head x 32 tokens, 128-byte swizzle
+    CUtensorMap mk, mv;
+    const CUtensorMapDataType dt = kv.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    for (int side = 0; side < 2; side++) {
+        const cuuint64_t dims[3] = {cuuint64_t(kDim), cuuint64_t(half_decode::kKv), cuuint64_t(capacity)};
+        const cuuint64_t strides[2] = {kDim * 2, cuuint64_t(half_decode::kKv) * kDim * 2};
+        const cuuint32_t box[3] = {64, 1, half_decode::kTile}, el[3] = {1, 1, 1};
+        CUresult r = enc(side ? &mv : &mk, dt, 3, const_cast<void *>(side ? kv.v : kv.k), dims, strides, box, el,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "decode attention: tensor map for the cache rejected");
+    }
     half_decode::Args a{};
     a.k = static_cast<const uint8_t *>(kv.k), a.v = static_cast<const uint8_t *>(kv.v);
     a.q = q, a.parts = parts, a.status = status, a.params = params;
@@ -416,13 +464,13 @@ int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t 
     const int ctas = splits; // one part per CTA, as many as the merge will read; CTAs past the last tile leave an empty part
     if (kv.dtype == SAETTA_BF16)
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, true>, dim3(ctas, m), dim3(half_decode::kThreads),
-                               half_decode::kSmem, stream, a));
+                               half_decode::kSmem, stream, mk, mv, a));
     else if (m == 1)
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, false>, dim3(ctas, 1), dim3(half_decode::kThreads),
-                               half_decode::kSmem, stream, a));
+                               half_decode::kSmem, stream, mk, mv, a));
     else // two rows per pass share every load of the cache
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<2, false>, dim3(ctas, (m + 1) / 2), dim3(half_decode::kThreads),
-                               half_decode::kSmem, stream, a));
+                               half_decode::kSmem, stream, mk, mv, a));
     return SAETTA_OK;
 }
 
