@@ -33,7 +33,7 @@ ROW = KV * DIM
 BYTES_PER_TOKEN = {8: 1088, 4: 576, 16: 2048}  # K + V, both kv heads, codes + scales + biases
 CTX = 262144
 LAYERS = 4
-TRAFFIC_PER_TOKEN = 1122.5  # measured dram bytes per token per layer (ncu), see profiles/
+TRAFFIC_PER_TOKEN = 1125.4  # measured dram bytes per token per layer (ncu), see profiles/
 METRIC = "Decode-attn achieved HBM GB/s @32k/256k KV; prefill-attn TFLOP/s per 4k chunk"
 
 
