@@ -165,7 +165,7 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
     if (warp >= kWarps) {
         // ---------------------------------------------------------------- producer
-        // (same register budget rule as in decode_quant.cu: 128 x (168 - 40) = 256 x (232 - 168))
+        // (same register pool rule as in decode_quant.cu: 128 x (168 - 40) = 256 x (232 - 168))
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp != kWarps) return;
         uint32_t it = 0;

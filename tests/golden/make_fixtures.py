@@ -2,7 +2,7 @@
 
 Run where the reference checkout is mounted:
 
-    python tests/golden/make_fixtures.py /root/reference
+    python tests/golden/make_fixtures.py <path of the reference checkout>
 
 It copies, key by key, the numbers of the reference's own MLX fixtures that pin
 this path (src/cpu/testdata/attention.json read by src/cpu/attention.rs:188-221,
@@ -40,4 +40,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_fixtures.py <path of the reference checkout>")
+    main(sys.argv[1])
