@@ -56,6 +56,33 @@ def test_shape_errors_come_back_as_status_codes(lib):
         sa.QuantRows(0, 16, 512, 64)
 
 
+def test_null_arguments_are_refused_before_any_device_work(lib):
+    """Misuse of the entry points added around the attention kernels -- prep, plan, peer exchange --
+    comes back as BAD_ARG with a message and never reaches the GPU (so this runs without one)."""
+    z = C.c_size_t()
+    f = C.c_float()
+    p = sa.PrepParams(16, 2, 256, 64, 1.0e7, 1.0e-6)
+    assert lib.saetta_attention_prep(p, 1, None, None, None, None, None, None, sa.F32, None, None, 0, None, None) == sa.BAD_ARG
+    assert b"attention prep" in lib.saetta_last_error()
+    for fn in (lib.saetta_plan_begin, lib.saetta_plan_build, lib.saetta_plan_commit, lib.saetta_plan_wait, lib.saetta_plan_run,
+               lib.saetta_plan_parallel_end):
+        assert fn(None) == sa.BAD_ARG
+    assert lib.saetta_plan_create(0, None) == sa.BAD_ARG
+    assert lib.saetta_plan_len(None, C.byref(z)) == sa.BAD_ARG
+    assert lib.saetta_plan_set_params(None, 0, 0) == sa.BAD_ARG
+    assert lib.saetta_plan_run_timed(None, C.byref(f)) == sa.BAD_ARG
+    assert lib.saetta_plan_params(None) is None and lib.saetta_plan_stream(None) is None
+    lib.saetta_plan_destroy(None)  # a no-op, as free(NULL)
+    handle = (C.c_uint8 * 64)()
+    assert lib.saetta_peer_group_create(0, 0, 9, 1, 16, handle, C.byref(C.c_void_p())) == sa.BAD_SHAPE  # 1..8 ranks
+    assert lib.saetta_peer_group_create(0, 2, 2, 1, 16, handle, C.byref(C.c_void_p())) == sa.BAD_SHAPE  # rank < world
+    for fn in (lib.saetta_peer_merge, lib.saetta_peer_collect, lib.saetta_peer_merge_sliced):
+        assert fn(None, 1, None, None, None) == sa.BAD_ARG
+    assert lib.saetta_peer_slice(None, 8, C.byref(z), C.byref(z)) == sa.BAD_ARG
+    assert lib.saetta_decode_publish_cache(None, 1, None, None, None, 0, None, None) == sa.BAD_ARG
+    assert lib.saetta_decode_batch_publish(None, 1, None, None, None, None, None) == sa.BAD_ARG
+
+
 def test_host_quantiser_is_the_oracle_bit_for_bit(lib, oracle):
     x = oracle.noise(37 * 512, 7).reshape(-1, 64)
     x *= np.where(np.arange(x.shape[0]) % 3 == 0, 20.0, 1.0)[:, None].astype(np.float32)
