@@ -134,6 +134,17 @@ int saetta_kv_cache_store(saetta_kv_cache *cache, const float *k_dev, const floa
                           const saetta_token_params *params_dev, size_t rows, void *stream);
 int saetta_kv_cache_store_at(saetta_kv_cache *cache, const float *k_dev, const float *v_dev,
                              size_t pos, size_t tokens, void *stream);
+/* ------------------------------------------------------------------ projections
+ * src/qmv.rs:27-170 `GpuQuant::record` (kernel qmv<5|6|8>, kernels/qmv.metal:12-53) and
+ * src/rows.rs:47-110 `record_proj` / `record_qmv_pk` (m rows): y[r][row] = sum_c W[row][c] x[r][c]
+ * for m <= 8 rows, W [rows][cols] an MLX affine matrix (src/quant.rs:1-30): words_dev holds
+ * rows * cols * bits / 32 u32 words (a little-endian bit stream per row), scales_dev / biases_dev
+ * rows * cols / 64 bfloat16 values; x_dev [m][cols] f32; row r of y starts y_stride floats after
+ * row r-1.  The q/k/v and o projections on either side of the attention path. */
+int saetta_qmv_rows(int device, const uint32_t *words_dev, const uint16_t *scales_dev,
+                    const uint16_t *biases_dev, int bits, size_t rows, size_t cols, size_t m,
+                    const float *x_dev, float *y_dev, size_t y_stride, void *stream);
+
 /* ------------------------------------------------------------------ record / replay
  * src/plan.rs:52-260 `Plan` and `Built`: dispatches recorded once and replayed
  * for every token, the only thing that changes being the TokenParams buffer.

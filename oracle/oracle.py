@@ -148,6 +148,18 @@ def sigmoid(x):
     return float(lib().so_sigmoid(float(x)))
 
 
+def quant_matvec(words, scales, biases, bits, rows, cols, x):
+    """src/cpu/matrix.rs:73-135: y = W x for an MLX affine matrix (u32 words, bfloat16 scale / bias bits per 64)."""
+    words = np.ascontiguousarray(words, np.uint32)
+    s, z = np.ascontiguousarray(scales, np.uint16), np.ascontiguousarray(biases, np.uint16)
+    x = _f32(x)
+    assert words.size == rows * cols * bits // 32 and s.size == rows * cols // 64 == z.size and x.size == cols
+    y = np.empty(rows, np.float32)
+    if lib().so_quant_matvec(_p(words), _p(s), _p(z), bits, C.c_size_t(rows), C.c_size_t(cols), _p(x), _p(y)):
+        raise ValueError("quant_matvec: bits must be 4, 5, 6 or 8 and cols a multiple of 64")
+    return y
+
+
 def rms_norm(x, w, eps):
     """src/cpu/ops.rs:19-36."""
     y, w = _f32(x).copy(), _f32(w)

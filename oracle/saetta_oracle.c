@@ -224,6 +224,57 @@ void so_matvec(const float *w, const float *x, size_t out, size_t n, float *y) {
     for (size_t r = 0; r < out; r++) y[r] = so_dot(w + r * n, x, n);
 }
 
+/*
+ * src/cpu/matrix.rs:104-135 `row_dot` over every row (`quant_matvec`, :73-101): y = W x for an MLX
+ * affine matrix (src/quant.rs:1-30): a row is a little-endian bit stream of `bits`-wide integers in
+ * u32 words, every 64 values share a bfloat16 scale and bias, w = scale * q + bias, and the sum over
+ * a group is scale * sum(q x) + bias * sum(x), groups added in order.
+ */
+static float bf16_bits_to_f32(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+int so_quant_matvec(const uint32_t *words, const uint16_t *scales, const uint16_t *biases, int bits, size_t rows,
+                    size_t cols, const float *x, float *y) {
+    if ((bits != 4 && bits != 5 && bits != 6 && bits != 8) || cols % 64) return 1;
+    const size_t groups = cols / 64, row_words = cols * (size_t)bits / 32;
+    float *x_sums = malloc(groups * sizeof(float));
+    for (size_t g = 0; g < groups; g++) {
+        float t = 0.0f;
+        for (size_t i = 0; i < 64; i++) t = t + x[g * 64 + i];
+        x_sums[g] = t;
+    }
+    const uint64_t mask = (1ull << bits) - 1;
+    for (size_t r = 0; r < rows; r++) {
+        const uint32_t *w = words + r * row_words;
+        uint64_t acc = 0;
+        unsigned have = 0;
+        size_t next = 0;
+        float total = 0.0f;
+        for (size_t g = 0; g < groups; g++) {
+            float dot = 0.0f;
+            for (size_t i = 0; i < 64; i++) {
+                if (have < (unsigned)bits) {
+                    acc |= (uint64_t)w[next++] << have;
+                    have += 32;
+                }
+                float p = (float)(acc & mask) * x[g * 64 + i];
+                dot = dot + p;
+                acc >>= bits;
+                have -= bits;
+            }
+            float a = bf16_bits_to_f32(scales[r * groups + g]) * dot;
+            float b = bf16_bits_to_f32(biases[r * groups + g]) * x_sums[g];
+            total = total + (a + b);
+        }
+        y[r] = total;
+    }
+    free(x_sums);
+    return 0;
+}
+
 /* src/cpu/ops.rs:19-36 `rms_norm`. */
 void so_rms_norm(float *x, const float *w, size_t n, float eps) {
     float ss = 0.0f;

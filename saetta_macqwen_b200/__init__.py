@@ -93,6 +93,7 @@ SYMBOLS = {
     "saetta_kv_cache_store": (_I, [_P, _P, _P, _P, _Z, _P]),
     "saetta_kv_cache_store_at": (_I, [_P, _P, _P, _Z, _Z, _P]),
     "saetta_kv_cache_set_dtype": (_I, [_P, _I]),
+    "saetta_qmv_rows": (_I, [_I, _P, _P, _P, _I, _Z, _Z, _Z, _P, _P, _Z, _P]),
     "saetta_plan_create": (_I, [_I, _PP]),
     "saetta_plan_destroy": (None, [_P]),
     "saetta_plan_params": (_P, [_P]),
@@ -414,6 +415,13 @@ def attention_prep(p, rows, q_and_gate, k, v, q_norm, k_norm, q_out, q_dtype, ca
     _check(lib().saetta_attention_prep(p, rows, ptr(q_and_gate), ptr(k), ptr(v), ptr(q_norm), ptr(k_norm), ptr(q_out),
                                        q_dtype, cache.h, ptr(params) if params is not None else None, pos,
                                        ptr(k_out) if k_out is not None else None, _stream(stream)))
+
+
+def qmv_rows(device, words, scales, biases, bits, rows, cols, m, x, y, y_stride=None, stream=None):
+    """GpuQuant::record / rows::record_proj (src/qmv.rs:27-170, src/rows.rs:47-110): y[m][rows] = x[m][cols] W^T
+    for an MLX affine matrix W (u32 words, bfloat16 scales and biases per 64 values)."""
+    _check(lib().saetta_qmv_rows(device, ptr(words), ptr(scales), ptr(biases), bits, rows, cols, m, ptr(x), ptr(y),
+                                 rows if y_stride is None else y_stride, _stream(stream)))
 
 
 def merge_partials(device, parts, ranks, rows, heads, q_and_gate, out, stream=None):
