@@ -243,6 +243,31 @@ def half_point(sa, torch, ctx, layers, steps, warmup, stream):
     return {"gbs": ctx * 2048 / ms / 1e6, "us_per_layer": ms * 1e3, "layers": layers}
 
 
+def qmv_point(sa, torch, rows, cols, bits, m, steps, warmup, stream):
+    """GB/s of weights for y[m][rows] = x[m][cols] W^T over MLX affine matrices; sixteen matrices rotate so
+    that no launch finds its weights in L2."""
+    dev = torch.cuda.current_device()
+    copies = 16
+    words = [torch.randint(-2**31, 2**31 - 1, (rows * cols * bits // 32,), dtype=torch.int32, device="cuda") for _ in range(copies)]
+    scales = torch.full((rows * cols // 64,), 0x3C00, dtype=torch.int16, device="cuda")  # bfloat16 0.0078
+    biases = torch.full((rows * cols // 64,), -0x4200, dtype=torch.int16, device="cuda")
+    x = torch.randn(m * cols, device="cuda")
+    y = torch.zeros(m * rows, device="cuda")
+    # recorded once and replayed as one graph, the way the per-token plan issues them: launched one by one
+    # from the host a kernel this short is bounded by the launch rate
+    per_plan = 4 * copies
+    plan = sa.Plan(dev)
+    with plan.recording():
+        for i in range(per_plan):
+            sa.qmv_rows(dev, words[i % copies], scales, biases, bits, rows, cols, m, x, y, stream=plan.stream)
+    for _ in range(max(warmup, 3)):
+        plan.run()
+    reps = max(1, steps // per_plan)
+    ms = sum(plan.run_timed() for _ in range(reps)) / (reps * per_plan)
+    nbytes = rows * cols * bits // 8 + 2 * (rows * cols // 64) * 2
+    return {"gbs": nbytes / ms / 1e6, "us": ms * 1e3, "bytes": nbytes}
+
+
 def prep_point(sa, torch, tokens, bits, steps, warmup, stream):
     """GB/s of attention prep fused with the quantised store for one prefill chunk: reads the q halves of
     q_and_gate, k, v (f32), writes q as bf16 and the cache rows.  The inputs of consecutive steps are
@@ -286,6 +311,9 @@ def point_table(sa, torch, stream, s, w):
         "verify_m4_32k_8bit": lambda: decode_point(sa, torch, 32768, 8, 4, 10, s, w, stream),
         "batch64_ragged_8bit": lambda: batch_point(sa, torch, 8, min(s, 3), 2, stream),
         "batch64_ragged_4bit": lambda: batch_point(sa, torch, 4, min(s, 3), 2, stream),
+        "qmv_8192x2048_5bit_m1": lambda: qmv_point(sa, torch, 8192, 2048, 5, 1, max(s, 32), w, stream),
+        "qmv_8192x2048_5bit_m4": lambda: qmv_point(sa, torch, 8192, 2048, 5, 4, max(s, 32), w, stream),
+        "qmv_2048x4096_5bit_m1": lambda: qmv_point(sa, torch, 2048, 4096, 5, 1, max(s, 32), w, stream),
         "prep_store_4k_8bit": lambda: prep_point(sa, torch, 4096, 8, max(s, 12), w, stream),
         "prefill_4k_pos0_bf16": lambda: prefill_point(sa, torch, 0, 4096, s, w, stream),
         "prefill_4k_pos32k_8bit": lambda: prefill_point(sa, torch, 32768, 4096, min(s, 5), 2, stream, quant_bits=8),
@@ -547,7 +575,8 @@ def main():
         s, w = max(5, args.steps // 2), 3
         table = point_table(sa, torch, stream, s, w)
         for name in ["decode_32k_8bit", "decode_128k_8bit", "decode_256k_4bit", "decode_128k_f16", "verify_m4_32k_8bit",
-                     "batch64_ragged_8bit", "batch64_ragged_4bit", "prep_store_4k_8bit", "prefill_4k_pos0_bf16",
+                     "batch64_ragged_8bit", "batch64_ragged_4bit", "qmv_8192x2048_5bit_m1", "qmv_8192x2048_5bit_m4",
+                     "prep_store_4k_8bit", "prefill_4k_pos0_bf16",
                      "prefill_4k_pos32k_8bit", "prefill_4k_pos128k_8bit"]:
             fn = table[name]
             try:

@@ -73,10 +73,11 @@ def test_kernel_matches_oracle(oracle, bits, m):
 
     rng = np.random.default_rng(bits * 10 + m)
     cases = [reference_sample(bits, 300, 1024)]
-    rows, cols = 1100, 2048
-    q = rng.integers(0, 1 << bits, (rows, cols), dtype=np.uint32)
-    cases.append((q, pack(q, bits), bf16_bits(rng.uniform(0.001, 0.02, rows * cols // 64).astype(np.float32)),
-                  bf16_bits(rng.uniform(-0.2, 0.0, rows * cols // 64).astype(np.float32)), None))
+    # teams of 16, 32 and 8 lanes (the last with three units per lane), and a row length only the general kernel takes
+    for rows, cols in ((1100, 2048), (70, 4096), (37, 3072), (33, 320)):
+        q = rng.integers(0, 1 << bits, (rows, cols), dtype=np.uint32)
+        cases.append((q, pack(q, bits), bf16_bits(rng.uniform(0.001, 0.02, rows * cols // 64).astype(np.float32)),
+                      bf16_bits(rng.uniform(-0.2, 0.0, rows * cols // 64).astype(np.float32)), None))
     for q, words, scales, biases, x0 in cases:
         rows, cols = q.shape
         x = rng.standard_normal((m, cols)).astype(np.float32)
