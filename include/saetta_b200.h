@@ -160,7 +160,9 @@ int saetta_qmv_rows(int device, const uint32_t *words_dev, const uint16_t *scale
  *   saetta_plan_run / _commit + _wait / _run_timed   Built::run / commit + Pending::wait / run_timed
  *   saetta_plan_len                          Plan::len (kernel launches recorded)
  * The host copy of TokenParams is uploaded by the graph's first node, so a
- * replay is a single graph launch.  Entry points that allocate (resize, the
+ * replay is a single graph launch; that node reads the host copy when the
+ * replay executes, so call set_params before commit and not again until the
+ * matching wait has returned.  Entry points that allocate (resize, the
  * first encode that grows a staging copy) must not be recorded.
  * Plan::build_where (profiling subsets) has no counterpart. */
 typedef struct saetta_plan saetta_plan;

@@ -519,7 +519,10 @@ class Plan:
                 return plan
 
             def __exit__(self, et, ev, tb):
-                plan.build()
+                if et is None:
+                    plan.build()
+                else:  # the recording failed: close the capture, keep the caller's exception
+                    lib().saetta_plan_build(plan.h)
                 return False
 
         return _Rec()
