@@ -100,7 +100,6 @@ qmv_rows_kernel(const uint32_t *__restrict__ words, const uint16_t *__restrict__
 }
 
 constexpr int kQmvThreads = 128; // threads per block of the units kernel
-constexpr int kQmvPair = 2;      // rows of W per team
 
 // value i of a unit as 1 + q / 2^BITS: its BITS bits moved to the top of the mantissa of 1.0
 template <int BITS, int I>
@@ -118,12 +117,12 @@ __device__ __forceinline__ float unit_value(const uint32_t (&w)[4 * BITS]) {
     return __uint_as_float((v & (((1u << BITS) - 1) << P)) | 0x3f800000u);
 }
 
-template <int BITS, int M, int C>
-__device__ __forceinline__ void unit_word(const uint32_t (&w)[kQmvPair][4 * BITS], const float4 *xu, uint32_t x_words,
-                                          uint32_t sw, float (&qx)[kQmvPair][M]) {
-    float f[kQmvPair][4];
+template <int BITS, int M, int RR, int C>
+__device__ __forceinline__ void unit_word(const uint32_t (&w)[RR][4 * BITS], const float4 *xu, uint32_t x_words,
+                                          uint32_t sw, float (&qx)[RR][M]) {
+    float f[RR][4];
 #pragma unroll
-    for (int r = 0; r < kQmvPair; r++) {
+    for (int r = 0; r < RR; r++) {
         f[r][0] = unit_value<BITS, 4 * C>(w[r]), f[r][1] = unit_value<BITS, 4 * C + 1>(w[r]);
         f[r][2] = unit_value<BITS, 4 * C + 2>(w[r]), f[r][3] = unit_value<BITS, 4 * C + 3>(w[r]);
     }
@@ -131,18 +130,18 @@ __device__ __forceinline__ void unit_word(const uint32_t (&w)[kQmvPair][4 * BITS
     for (int j = 0; j < M; j++) {
         const float4 v = xu[size_t(j) * x_words + (uint32_t(C) ^ sw)];
 #pragma unroll
-        for (int r = 0; r < kQmvPair; r++)
+        for (int r = 0; r < RR; r++)
             qx[r][j] = fmaf(f[r][0], v.x, fmaf(f[r][1], v.y, fmaf(f[r][2], v.z, fmaf(f[r][3], v.w, qx[r][j]))));
     }
 }
 
-template <int BITS, int M, int C0, int... Cs>
-__device__ __forceinline__ void unit_half(const uint32_t (&w)[kQmvPair][4 * BITS], const float4 *xu, uint32_t x_words,
-                                          uint32_t sw, float (&qx)[kQmvPair][M], std::integer_sequence<int, Cs...>) {
-    (unit_word<BITS, M, C0 + Cs>(w, xu, x_words, sw, qx), ...);
+template <int BITS, int M, int RR, int C0, int... Cs>
+__device__ __forceinline__ void unit_half(const uint32_t (&w)[RR][4 * BITS], const float4 *xu, uint32_t x_words,
+                                          uint32_t sw, float (&qx)[RR][M], std::integer_sequence<int, Cs...>) {
+    (unit_word<BITS, M, RR, C0 + Cs>(w, xu, x_words, sw, qx), ...);
 }
 
-template <int BITS, int M>
+template <int BITS, int M, int RR>
 __global__ void __launch_bounds__(kQmvThreads)
 qmv_units_kernel(const uint32_t *__restrict__ words, const uint16_t *__restrict__ scales,
                  const uint16_t *__restrict__ biases, const float *__restrict__ x, float *__restrict__ y,
@@ -152,13 +151,13 @@ qmv_units_kernel(const uint32_t *__restrict__ words, const uint16_t *__restrict_
     float4 *xs = reinterpret_cast<float4 *>(qmv_smem); // [M][cols / 4], swizzled inside every unit of 32
     float *gs = qmv_smem + size_t(M) * cols;          // [M][groups]: sum of x over each group
     const uint32_t tid = threadIdx.x, tl = tid & (team - 1), team_id = tid / team;
-    const uint32_t row0 = (blockIdx.x * (kQmvThreads / team) + team_id) * kQmvPair;
+    const uint32_t row0 = (blockIdx.x * (kQmvThreads / team) + team_id) * RR;
     const size_t row_words = size_t(cols) * BITS / 32;
 
-    uint32_t w[kQmvPair][4 * BITS], sb[kQmvPair][2];
+    uint32_t w[RR][4 * BITS], sb[RR][2];
     auto load = [&](uint32_t u) {
 #pragma unroll
-        for (int r = 0; r < kQmvPair; r++) {
+        for (int r = 0; r < RR; r++) {
             const uint32_t row = min(row0 + r, rows - 1); // a row past the end repeats the last one; its sums are dropped
             const uint4 *wp = reinterpret_cast<const uint4 *>(words + size_t(row) * row_words) + size_t(u) * BITS;
 #pragma unroll
@@ -187,9 +186,9 @@ qmv_units_kernel(const uint32_t *__restrict__ words, const uint16_t *__restrict_
     }
     __syncthreads();
 
-    float acc[kQmvPair][M];
+    float acc[RR][M];
 #pragma unroll
-    for (int r = 0; r < kQmvPair; r++)
+    for (int r = 0; r < RR; r++)
 #pragma unroll
         for (int j = 0; j < M; j++) acc[r][j] = 0.f;
     while (true) {
@@ -197,15 +196,15 @@ qmv_units_kernel(const uint32_t *__restrict__ words, const uint16_t *__restrict_
         const uint32_t sw = u & 7;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            float qx[kQmvPair][M];
+            float qx[RR][M];
 #pragma unroll
-            for (int r = 0; r < kQmvPair; r++)
+            for (int r = 0; r < RR; r++)
 #pragma unroll
                 for (int j = 0; j < M; j++) qx[r][j] = 0.f;
-            if (h == 0) unit_half<BITS, M, 0>(w, xu, x_words, sw, qx, std::make_integer_sequence<int, 16>{});
-            else unit_half<BITS, M, 16>(w, xu, x_words, sw, qx, std::make_integer_sequence<int, 16>{});
+            if (h == 0) unit_half<BITS, M, RR, 0>(w, xu, x_words, sw, qx, std::make_integer_sequence<int, 16>{});
+            else unit_half<BITS, M, RR, 16>(w, xu, x_words, sw, qx, std::make_integer_sequence<int, 16>{});
 #pragma unroll
-            for (int r = 0; r < kQmvPair; r++) {
+            for (int r = 0; r < RR; r++) {
                 const uint32_t s16 = h ? sb[r][0] & 0xffff0000u : sb[r][0] << 16, b16 = h ? sb[r][1] & 0xffff0000u : sb[r][1] << 16;
                 const float s = __uint_as_float(s16) * float(1 << BITS), b = __uint_as_float(b16);
 #pragma unroll
@@ -220,7 +219,7 @@ qmv_units_kernel(const uint32_t *__restrict__ words, const uint16_t *__restrict_
         load(u);
     }
 #pragma unroll
-    for (int r = 0; r < kQmvPair; r++)
+    for (int r = 0; r < RR; r++)
 #pragma unroll
         for (int j = 0; j < M; j++) {
             float v = acc[r][j];
@@ -240,11 +239,12 @@ static int launch_qmv_m(const uint32_t *w, const uint16_t *s, const uint16_t *b,
     const size_t shared = (size_t(M) * cols + size_t(M) * (cols / 64)) * sizeof(float);
     const bool aligned = !(reinterpret_cast<uintptr_t>(w) & 15) && !((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(b)) & 3);
     if (cols % 1024 == 0 && shared <= kQmvMaxShared && aligned) {
+        constexpr int RR = 2; // rows of W per lane (four measured the same at m = 4 and cost 70 more registers)
         const uint32_t units = cols / 128, team = units % 32 == 0 ? 32 : units % 16 == 0 ? 16 : 8;
-        const uint32_t block_rows = kQmvThreads / team * kQmvPair;
+        const uint32_t block_rows = kQmvThreads / team * RR;
         if (shared > 48 * 1024)
-            SAETTA_CUDA(cudaFuncSetAttribute(qmv_units_kernel<BITS, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared)));
-        qmv_units_kernel<BITS, M><<<(rows + block_rows - 1) / block_rows, kQmvThreads, shared, st>>>(w, s, b, x, y, rows, cols, y_stride, team);
+            SAETTA_CUDA(cudaFuncSetAttribute(qmv_units_kernel<BITS, M, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared)));
+        qmv_units_kernel<BITS, M, RR><<<(rows + block_rows - 1) / block_rows, kQmvThreads, shared, st>>>(w, s, b, x, y, rows, cols, y_stride, team);
     } else {
         const unsigned grid = (rows + kQmvWarps * kQmvRows - 1) / (kQmvWarps * kQmvRows);
         qmv_rows_kernel<BITS, M><<<grid, kQmvWarps * 32, 0, st>>>(w, s, b, x, y, rows, cols, y_stride);
