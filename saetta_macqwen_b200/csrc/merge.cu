@@ -17,9 +17,9 @@ size_t decode_quant_part_floats(size_t kv_heads) { return kv_heads * size_t(kPar
 __device__ __forceinline__ float gate_of(float g) { return 1.0f / (1.0f + expf(-g)); }
 
 // grid (32, rows * kv_heads), 1024 threads: 64 fragment elements of one (row, kv
-// head) per block, the parts dealt round-robin to 16 thread groups so that every
-// thread has only a handful of independent loads in flight (the merge is
-// latency-bound, not bandwidth-bound).  Sums are formed in a fixed order.
+// head) per block, the parts dealt round-robin to 16 thread groups, and every thread's loads
+// issued together (the merge is latency-bound, not bandwidth-bound).  Sums are formed in a
+// fixed order.
 constexpr int kMergeGroups = 16;
 constexpr int kMergeElems = 64;
 constexpr int kMergeMaxParts = 512; // m and l of at most this many parts are staged in shared memory
@@ -50,15 +50,34 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
     const uint32_t r = e >> 5, lane = e & 31;
     const uint32_t head = 2 * (lane & 3) + (r & 1);
 
+    // The merge is a chain of latencies (the parts sit in L2), so every thread asks for all it needs at once:
+    // its first kMergeBatch values before the weights are formed, the m / l words in one round.
+    constexpr int kMergeBatch = 12; // x 16 groups = 192 parts per round: one round for a decode over all SMs
     float acc = 0.f;
     if (tid < 8) M_s[tid] = -INFINITY, L_s[tid] = 0.f; // what a row without parts (an empty shard) merges to
     for (uint32_t c0 = p0; c0 < p1; c0 += kMergeMaxParts) { // one pass unless a sequence has > 512 parts
         const uint32_t n = min(p1 - c0, uint32_t(kMergeMaxParts));
+        float v[kMergeBatch];
+#pragma unroll
+        for (int k = 0; k < kMergeBatch; k++) {
+            const uint32_t p = grp + k * kMergeGroups;
+            v[k] = p < n ? base[(c0 + p) * stride + e] : 0.f;
+        }
         __syncthreads();
-        for (uint32_t x = tid; x < n * 16; x += blockDim.x) {
-            const uint32_t p = x >> 4, k = x & 15;
-            const float v = base[(c0 + p) * stride + kFragFloats + k];
-            if (k < 8) w_s[p][k] = v; else l_s[p][k - 8] = v;
+        for (uint32_t xb = tid; xb < n * 16; xb += 4 * blockDim.x) {
+            float ml[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t x = xb + k * blockDim.x;
+                ml[k] = x < n * 16 ? base[(c0 + (x >> 4)) * stride + kFragFloats + (x & 15)] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t x = xb + k * blockDim.x, p = x >> 4, j = x & 15;
+                if (x < n * 16) {
+                    if (j < 8) w_s[p][j] = ml[k]; else l_s[p][j - 8] = ml[k];
+                }
+            }
         }
         __syncthreads();
         if (tid < 256) { // warp h reduces head h
@@ -88,20 +107,25 @@ merge_frag_kernel(const float *__restrict__ parts, uint32_t nparts,
         __syncthreads();
         if (c0 != p0) acc *= red[0][head];
         __syncthreads();
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        uint32_t p = grp;
-        for (; p + 3 * kMergeGroups < n; p += 4 * kMergeGroups) {
-            const float v0 = base[(c0 + p) * stride + e];
-            const float v1 = base[(c0 + p + kMergeGroups) * stride + e];
-            const float v2 = base[(c0 + p + 2 * kMergeGroups) * stride + e];
-            const float v3 = base[(c0 + p + 3 * kMergeGroups) * stride + e];
-            a0 = fmaf(v0, w_s[p][head], a0);
-            a1 = fmaf(v1, w_s[p + kMergeGroups][head], a1);
-            a2 = fmaf(v2, w_s[p + 2 * kMergeGroups][head], a2);
-            a3 = fmaf(v3, w_s[p + 3 * kMergeGroups][head], a3);
+        float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < kMergeBatch; k++) {
+            const uint32_t p = grp + k * kMergeGroups;
+            if (p < n) a4[k & 3] = fmaf(v[k], w_s[p][head], a4[k & 3]);
         }
-        for (; p < n; p += kMergeGroups) a0 = fmaf(base[(c0 + p) * stride + e], w_s[p][head], a0);
-        acc += (a0 + a1) + (a2 + a3);
+        for (uint32_t pb = grp + kMergeBatch * kMergeGroups; pb < n; pb += kMergeBatch * kMergeGroups) { // > 192 parts
+#pragma unroll
+            for (int k = 0; k < kMergeBatch; k++) {
+                const uint32_t p = pb + k * kMergeGroups;
+                v[k] = p < n ? base[(c0 + p) * stride + e] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < kMergeBatch; k++) {
+                const uint32_t p = pb + k * kMergeGroups;
+                if (p < n) a4[k & 3] = fmaf(v[k], w_s[p][head], a4[k & 3]);
+            }
+        }
+        acc += (a4[0] + a4[1]) + (a4[2] + a4[3]);
     }
     __syncthreads();
     red[grp][el] = acc;
