@@ -34,8 +34,9 @@
 //    by more than 2^8.  The tile I/O warps move tiles in and out, two threads per
 //    row (dims 0..127 and 128..255): the Q rows of the next tile are fetched into
 //    registers early and go into TMEM as soon as the last S of the current tile
-//    is done, then comes the current tile's epilogue, which frees O as soon as it
-//    has read it, so a tile change stalls the MMAs as little as possible.  The
+//    is done, then comes the current tile's epilogue, which reads O out of tensor
+//    memory in one go and frees it before it fetches the gate values, so a tile
+//    change stalls the MMAs as little as possible.  The
 //    epilogue divides by l and applies the sigmoid gate (256-bit loads and
 //    stores), or leaves (O, m, l) partials for a merge (across GPUs, or across the
 //    two key halves a long-context tile is cut into).
@@ -535,16 +536,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const bool row_live = r.live;
             const size_t rh = r.rh;
             float *part = r.part;
-            // The gate values do not depend on O: the first 32 are requested before O is final,
-            // and each later chunk one step ahead of its use (two register buffers).
+            // O leaves tensor memory in one go (this thread's 128 values), so that the next tile's P V
+            // products wait for four tensor-memory loads and nothing else; the gate values, which come
+            // from global memory, are fetched afterwards, one 32-byte step ahead of their use.
             // (256-bit loads and stores: a thread's accesses are whole 32-byte sectors of its row)
             const bool gated = row_live && p.out;
             const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim + half * 128 : 0);
-            Float8 gq[2][4];
-            if (gated) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) gq[0][j] = ld_global_v8(gp + j * 8);
-            }
             PF_T0();
             if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             const float l = row_l[(k & 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
@@ -552,38 +549,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (quarter == 0 && !half) { PF_ADD(9); }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
+            uint32_t o[4][32];
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) {
-                if (gated && ch + 1 < 4) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) gq[(ch + 1) & 1][j] = ld_global_v8(gp + (ch + 1) * 32 + j * 8);
-                }
-                const int c = half * 128 + ch * 32;
-                uint32_t o[32];
-                tmem_ld32(tmem_o + lane_addr + c, o);
-                tmem_wait_ld();
-                if (ch == 3) { // O has left tensor memory: the next tile's P V products may start
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(o_empty);
-                }
-                if (!row_live) continue;
+            for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem_o + lane_addr + half * 128 + ch * 32, o[ch]);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_empty); // O has left tensor memory: the next tile's P V products may start
+            if (row_live) {
                 if (p.out) {
-                    float *op = p.out + rh * kDim + c;
+                    float *op = p.out + rh * kDim + half * 128;
+                    Float8 g = ld_global_v8(gp);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
+                    for (int st = 0; st < 16; st++) {
+                        Float8 gn = g;
+                        if (st + 1 < 16) gn = ld_global_v8(gp + (st + 1) * 8);
                         Float8 v;
 #pragma unroll
                         for (int e = 0; e < 8; e++)
-                            v.v[e] = __uint_as_float(o[8 * j + e]) * __fdividef(inv_l, 1.f + __expf(-gq[ch & 1][j].v[e]));
-                        st_global_v8(op + j * 8, v);
+                            v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-g.v[e]));
+                        st_global_v8(op + st * 8, v);
+                        g = gn;
                     }
                 } else {
-                    float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + c);
+                    float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + half * 128);
 #pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        op[j] = make_float4(__uint_as_float(o[4 * j]), __uint_as_float(o[4 * j + 1]),
-                                            __uint_as_float(o[4 * j + 2]), __uint_as_float(o[4 * j + 3]));
+                    for (int j = 0; j < 32; j++)
+                        op[j] = make_float4(__uint_as_float(o[j >> 3][4 * (j & 7)]), __uint_as_float(o[j >> 3][4 * (j & 7) + 1]),
+                                            __uint_as_float(o[j >> 3][4 * (j & 7) + 2]), __uint_as_float(o[j >> 3][4 * (j & 7) + 3]));
                 }
             }
             if (row_live && part && !half) {
