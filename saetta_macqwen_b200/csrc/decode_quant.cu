@@ -257,6 +257,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         uint32_t it = 0;
         bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
         for (uint32_t si = seg_lo; si < seg_hi; si++) {
+            // The query row is asked for before the token parameters are: with one sequence per launch its
+            // address depends on neither, and the two round trips then overlap.
+            const uint32_t seq = a.segs ? a.segs[si].seq : 0u;
+            float4 qraw[4][4];
+            {
+                const float *qp = a.q + ((size_t(seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
+#pragma unroll
+                for (int G = 0; G < 4; G++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) qraw[G][c] = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
+            }
             const Segment s = load_segment(si);
             const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
 
@@ -267,13 +278,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             float qoff[4]; // per group: what the code offsets (1024, and 64 for high nibbles) add to q.c
             {
                 float qs[4];
-                const float *qp = a.q + ((size_t(s.seq) * a.m + (row_live ? row : 0)) * 16 + kv * 8 + g) * kDim;
 #pragma unroll
                 for (int G = 0; G < 4; G++) {
                     float x[16];
 #pragma unroll
                     for (int c = 0; c < 4; c++) {
-                        const float4 v = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
+                        const float4 v = qraw[G][c];
                         x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
                     }
                     float hi[16], lo[16], sum = 0.f, off = 0.f;
