@@ -8,6 +8,8 @@
 #include <cmath>
 #include <new>
 
+#include <mutex>
+
 #include "host.hpp"
 
 namespace saetta {
@@ -48,8 +50,11 @@ static KvView view_of(const saetta_quant_rows *k, const saetta_quant_rows *v) {
 }
 
 // One-time per-device raise of the kernels' dynamic shared-memory limits.
+static std::mutex g_init_mutex; // first calls from several host threads may meet in the lazy set-up below
+
 static int configure_device(int device) {
     static bool done[64] = {};
+    std::lock_guard<std::mutex> lock(g_init_mutex);
     if (device >= 0 && device < 64 && done[device]) return SAETTA_OK;
     int rc = decode_quant_configure(device);
     if (!rc) rc = decode_half_configure(device);
@@ -928,8 +933,11 @@ int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *
     if (int rc = configure_device(device)) return rc;
     static uint32_t *status[64] = {};
     if (device < 0 || device >= 64) return fail(SAETTA_ERR_BAD_ARG, "prefill encode: device");
-    if (!status[device])
-        if (int rc = alloc_zero((void **)&status[device], 16)) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_init_mutex);
+        if (!status[device])
+            if (int rc = alloc_zero((void **)&status[device], 16)) return rc;
+    }
     PrefillArgs a{q_dev, keys_dev, values_dev, dtype, dtype, q_and_gate_dev, out_dev, nullptr, p.heads, p.kv_heads, p.pos,
                   p.tokens, 0, p.pos + p.tokens, p.scale};
     return launch_prefill(a, status[device], (cudaStream_t)stream);

@@ -34,6 +34,8 @@
 //    the status word, raises the CTA's abort flag and the CTA drains and leaves.
 #include <algorithm>
 
+#include <mutex>
+
 #include "host.hpp"
 
 namespace saetta {
@@ -1133,6 +1135,8 @@ static StaticScratch g_static[64];
 // a kernel must be given what cudaGetSymbolAddress returns.
 static int static_scratch(int device, StaticScratch **out) {
     if (device < 0 || device >= 64) return fail(SAETTA_ERR_BAD_ARG, "static decode: device index out of range");
+    static std::mutex init_mutex; // first calls from several host threads may meet here
+    std::lock_guard<std::mutex> lock(init_mutex);
     StaticScratch &s = g_static[device];
     if (!s.parts) {
         void *parts = nullptr, *status = nullptr;
