@@ -162,9 +162,21 @@ int saetta_qmv_rows(int device, const uint32_t *words_dev, const uint16_t *scale
  * The host copy of TokenParams is uploaded by the graph's first node, so a
  * replay is a single graph launch; that node reads the host copy when the
  * replay executes, so call set_params before commit and not again until the
- * matching wait has returned.  Entry points that allocate (resize, the
- * first encode that grows a staging copy) must not be recorded.
- * Plan::build_where (profiling subsets) has no counterpart. */
+ * matching wait has returned.  Entry points that allocate (resize, an
+ * AttGemm encode beyond what saetta_att_gemm_reserve was given) must not be
+ * recorded.
+ *   saetta_plan_kernels                      Plan::kernels: the distinct kernels of the recording and how
+ *                                            many ops each has (names valid until the next begin / destroy)
+ *   saetta_plan_build_where                  Plan::build_where(keep, barriers) (src/plan.rs:190-226): a
+ *                                            second replayable object holding only the ops whose kernel
+ *                                            name contains one of `keep` (n_keep = 0: all of them), with
+ *                                            the recording's order carried over the dropped ops
+ *                                            (barriers != 0) or with no order between kernels at all
+ *                                            (barriers == 0: wrong results, a lower bound).  Copy nodes --
+ *                                            the TokenParams upload among them -- are always kept.  For
+ *                                            profiling, as in src/profile.rs:39-121: its results are not the
+ *                                            plan's results.
+ *   saetta_built_run_timed / _len / _destroy Built::run_timed, the number of ops kept, drop */
 typedef struct saetta_plan saetta_plan;
 int saetta_plan_create(int device, saetta_plan **out);
 void saetta_plan_destroy(saetta_plan *plan);
@@ -180,6 +192,13 @@ int saetta_plan_commit(saetta_plan *plan);
 int saetta_plan_wait(saetta_plan *plan);
 int saetta_plan_run(saetta_plan *plan);
 int saetta_plan_run_timed(saetta_plan *plan, float *gpu_ms);
+typedef struct saetta_built saetta_built;
+int saetta_plan_kernels(saetta_plan *plan, const char **names_out, size_t *ops_out, size_t cap, size_t *count);
+int saetta_plan_build_where(saetta_plan *plan, const char *const *keep, size_t n_keep, int barriers,
+                            saetta_built **out);
+void saetta_built_destroy(saetta_built *built);
+int saetta_built_len(const saetta_built *built, size_t *ops);
+int saetta_built_run_timed(saetta_built *built, float *gpu_ms);
 
 /* ------------------------------------------------------------------ attention prep
  * kernels/layers.metal:637-697 `PrepParams`, `attention_prep` (16-bit cache) and
@@ -277,6 +296,13 @@ int saetta_decode_record_quant_static(int device, size_t m, const float *q_dev,
                                       const saetta_quant_rows *values,
                                       const float *q_and_gate_dev, float *out_dev,
                                       const saetta_token_params *params_dev, void *stream);
+/* The status word of saetta_decode_record_quant_static on `device`: its kernels'
+ * bounded waits set bits there when one of them gives up (the output of that
+ * call is then void), and the word is shared by every call on the device, like
+ * the scratch.  Synchronises `stream`, returns SAETTA_ERR_TIMEOUT when the word
+ * is not 0, and with clear != 0 puts it back to 0 after reading.  Allocates
+ * nothing.  No counterpart in the reference. */
+int saetta_decode_static_status(int device, void *stream, uint32_t *status, int clear);
 /* Number of split-KV parts the op launches (its grid), and the device status
  * word of its bounded waits: 0 when no wait ever gave up.  Synchronises `stream`. */
 int saetta_decode_splits(const saetta_decode *op);
@@ -377,7 +403,12 @@ int saetta_att_gemm_encode(saetta_att_gemm *op, const void *q_dev, int dtype, co
                            const void *values_dev, const saetta_quant_rows *keys_q,
                            const saetta_quant_rows *values_q, const float *q_and_gate_dev,
                            float *out_dev, saetta_flash_params p, void *stream);
-/* attention_prefill::encode: the same computation with no object (16-bit cache only). */
+/* attention_prefill::encode: the same computation with no object, over a binary16
+ * cache (what the reference's function takes).  dtype must be SAETTA_F16: the
+ * tensor-core kernel gives P the values' type, and bfloat16's 8-bit significand
+ * would put P's rounding at the tolerance; AttGemm stages bfloat16 values as
+ * binary16 in its own scratch, which a call without an object has nowhere to
+ * keep, so bfloat16 is refused here with SAETTA_ERR_UNSUPPORTED. */
 int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *keys_dev,
                           const void *values_dev, const float *q_and_gate_dev, float *out_dev,
                           saetta_flash_params p, void *stream);

@@ -108,6 +108,11 @@ SYMBOLS = {
     "saetta_plan_wait": (_I, [_P]),
     "saetta_plan_run": (_I, [_P]),
     "saetta_plan_run_timed": (_I, [_P, C.POINTER(C.c_float)]),
+    "saetta_plan_kernels": (_I, [_P, C.POINTER(C.c_char_p), C.POINTER(_Z), _Z, C.POINTER(_Z)]),
+    "saetta_plan_build_where": (_I, [_P, C.POINTER(C.c_char_p), _Z, _I, _PP]),
+    "saetta_built_destroy": (None, [_P]),
+    "saetta_built_len": (_I, [_P, C.POINTER(_Z)]),
+    "saetta_built_run_timed": (_I, [_P, C.POINTER(C.c_float)]),
     "saetta_attention_prep": (_I, [PrepParams, _Z, _P, _P, _P, _P, _P, _P, _I, _P, _P, _Z, _P, _P]),
     "saetta_row_backup_create": (_I, [_PP]),
     "saetta_row_backup_destroy": (None, [_P]),
@@ -121,6 +126,7 @@ SYMBOLS = {
     "saetta_decode_record_quant": (_I, [_P, _Z, _P, _P, _P, _P, _P, _P, _P]),
     "saetta_decode_record_cache": (_I, [_P, _Z, _P, _P, _P, _P, _P, _P]),
     "saetta_decode_record_quant_static": (_I, [_I, _Z, _P, _P, _P, _P, _P, _P, _P]),
+    "saetta_decode_static_status": (_I, [_I, _P, C.POINTER(_U32), _I]),
     "saetta_decode_splits": (_I, [_P]),
     "saetta_decode_device_status": (_I, [_P, _P, C.POINTER(_U32)]),
     "saetta_decode_batch_create": (_I, [_I, _Z, _Z, _Z, _Z, _Z, _PP]),
@@ -378,6 +384,13 @@ def decode_record_quant_static(device, m, q, keys, values, q_and_gate, out, para
                                                    ptr(params), _stream(stream)))
 
 
+def decode_static_status(device, stream=None, clear=False):
+    """The status word of the allocation-free entry point on `device` (0: no bounded wait ever gave up)."""
+    s = C.c_uint32()
+    _check(lib().saetta_decode_static_status(device, _stream(stream), C.byref(s), 1 if clear else 0))
+    return s.value
+
+
 class DecodeBatch:
     """One decode row for each of many sequences with ragged lengths (no reference counterpart)."""
 
@@ -557,9 +570,49 @@ class Plan:
         _check(lib().saetta_plan_run_timed(self.h, C.byref(ms)))
         return ms.value
 
+    def kernels(self):
+        """Plan::kernels: [(kernel name, ops)] in the order of each kernel's first op."""
+        n = C.c_size_t()
+        _check(lib().saetta_plan_kernels(self.h, None, None, 0, C.byref(n)))
+        names, ops = (C.c_char_p * n.value)(), (C.c_size_t * n.value)()
+        _check(lib().saetta_plan_kernels(self.h, names, ops, n.value, C.byref(n)))
+        return [(names[i].decode(), ops[i]) for i in range(n.value)]
+
+    def build_where(self, keep=None, barriers=True):
+        """Plan::build_where: a Built of only the ops whose kernel name contains one of `keep` (None: all)."""
+        keep = list(keep or [])
+        arr = (C.c_char_p * max(len(keep), 1))(*[k.encode() for k in keep])
+        h = C.c_void_p()
+        _check(lib().saetta_plan_build_where(self.h, arr if keep else None, len(keep), 1 if barriers else 0, C.byref(h)))
+        return Built(h, self)
+
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:
             _lib.saetta_plan_destroy(self.h)
+            self.h = None
+
+
+class Built:
+    """src/plan.rs:229-260 `Built` as Plan::build_where returns it (a profiling replay)."""
+
+    def __init__(self, h, plan):
+        self.h, self._plan = h, plan  # it replays on the plan's stream and reads the plan's buffers
+
+    def __len__(self):
+        n = C.c_size_t()
+        _check(lib().saetta_built_len(self.h, C.byref(n)))
+        return n.value
+
+    def run_timed(self):
+        ms = C.c_float()
+        _check(lib().saetta_built_run_timed(self.h, C.byref(ms)))
+        return ms.value
+
+    run = run_timed
+
+    def __del__(self):
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.saetta_built_destroy(self.h)
             self.h = None
 
 
@@ -590,8 +643,8 @@ class AttGemm:
             self.h = None
 
 
-def prefill_encode(device, q, keys, values, q_and_gate, out, p, dtype=BF16, stream=None):
-    """src/attention_prefill.rs:39-72 `encode`."""
+def prefill_encode(device, q, keys, values, q_and_gate, out, p, dtype=F16, stream=None):
+    """src/attention_prefill.rs:39-72 `encode` (binary16 q and cache, as the reference's)."""
     _check(lib().saetta_prefill_encode(device, ptr(q), dtype, ptr(keys), ptr(values), ptr(q_and_gate), ptr(out), p,
                                        _stream(stream)))
 

@@ -10,7 +10,7 @@
 
 #include <mutex>
 
-#include "host.hpp"
+#include "merge_role.cuh"
 
 namespace saetta {
 
@@ -502,10 +502,10 @@ int saetta_decode_create(int device, size_t heads, size_t kv_heads, size_t head_
     op->device = device, op->heads = heads, op->kv_heads = kv_heads, op->capacity = capacity, op->rows = rows;
     const size_t tiles = (capacity + 31) / 32;
     const size_t sms = size_t(sm_count(device));
-    op->splits = int(tiles < sms ? tiles : sms);
+    op->splits = int(std::min(std::min(tiles, sms), size_t(kMergeRoleMaxParts)));
     const size_t per_row = std::max(decode_quant_part_floats(kv_heads), heads * size_t(kPartStride));
     int rc = alloc_zero((void **)&op->parts, size_t(op->splits) * rows * per_row * sizeof(float));
-    if (!rc) rc = alloc_zero((void **)&op->status, 16);
+    if (!rc) rc = alloc_zero((void **)&op->status, kStatusWords * 4);
     if (rc) {
         saetta_decode_destroy(op);
         return rc;
@@ -548,22 +548,21 @@ static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView 
     if (kv_capacity % 32) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: cache capacity must be a multiple of 32");
     DeviceGuard guard(op->device);
     const uint32_t heads = uint32_t(op->heads);
-    if (kv.bits == 8 || kv.bits == 4) {
+    const bool tensor_quant = kv.bits == 8 || kv.bits == 4;
+    const bool tensor_half = kv.bits == 16 && kv.kv_heads == 2 && aligned16(kv.k) && aligned16(kv.v);
+    if (tensor_quant || tensor_half) {
+        // One launch: the split-KV CTAs, then the merge CTAs that gate the result, leave the merged
+        // partial, or store it into the peers' mailboxes (merge_role.cuh).
         if (kv.kv_heads != 2) return fail(SAETTA_ERR_UNSUPPORTED, "quantised decode attention is built for 2 kv heads");
-        if (int rc = launch_decode_quant(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
-                                         uint32_t(kv_capacity), params, st))
-            return rc;
-        return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
-                                 part_out, st, group ? &group->push : nullptr);
-    }
-    if (kv.bits == 16 && kv.kv_heads == 2 && aligned16(kv.k) && aligned16(kv.v)) {
-        // binary16 (the reference's own cache format) or bfloat16 rows: tensor-core kernel, partials and merge as
-        // for the quantised cache
-        if (int rc = launch_decode_half(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
-                                        uint32_t(kv_capacity), params, st))
-            return rc;
-        return launch_merge_frag(op->parts, uint32_t(op->splits), nullptr, uint32_t(m), kv.kv_heads, q_and_gate, out,
-                                 part_out, st, group ? &group->push : nullptr);
+        MergeOut mo;
+        mo.q_and_gate = q_and_gate, mo.out = out, mo.part_out = part_out;
+        if (group) mo.push = group->push;
+        // binary16 (the reference's own cache format) or bfloat16 rows run the same shape of kernel
+        // without the dequantisation
+        return tensor_quant ? launch_decode_quant(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
+                                                  uint32_t(kv_capacity), params, mo, st)
+                            : launch_decode_half(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
+                                                 uint32_t(kv_capacity), params, mo, st);
     }
     if (int rc = launch_decode_exact(kv, q, op->parts, uint32_t(m), row_step, op->splits, uint32_t(kv_capacity), params, st))
         return rc;
@@ -603,10 +602,22 @@ int saetta_decode_record_quant_static(int device, size_t m, const float *q_dev, 
     if (!aligned16(q_dev)) return fail(SAETTA_ERR_BAD_ARG, "static decode: q must be 16-byte aligned");
     if (keys->bits != values->bits || keys->per_token != values->per_token || keys->capacity != values->capacity)
         return fail(SAETTA_ERR_BAD_SHAPE, "static decode: keys and values differ in format");
+    if (keys->bits != 8 && keys->bits != 4) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: the rows must hold 8- or 4-bit codes");
+    if (keys->device != device || values->device != device)
+        return fail(SAETTA_ERR_BAD_ARG, "static decode: the rows live on another device than the one named");
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SAETTA_ERR_CUDA, "static decode: cannot select the device");
     return decode_quant_static(device, view_of(keys, values), keys->capacity, q_dev, uint32_t(m), q_and_gate_dev,
                                out_dev, params_dev, (cudaStream_t)stream);
+}
+
+int saetta_decode_static_status(int device, void *stream, uint32_t *status, int clear) {
+    if (!status) return fail(SAETTA_ERR_BAD_ARG, "static decode status: null pointer");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SAETTA_ERR_CUDA, "static decode status: cannot select the device");
+    if (int rc = decode_quant_static_status(device, (cudaStream_t)stream, status, clear != 0)) return rc;
+    if (*status) return fail(SAETTA_ERR_TIMEOUT, "a bounded device-side wait gave up");
+    return SAETTA_OK;
 }
 
 static KvView view_of_cache(const saetta_kv_cache *c) {
@@ -927,6 +938,9 @@ int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *
                           const float *q_and_gate_dev, float *out_dev, saetta_flash_params p, void *stream) {
     if (!keys_dev || !values_dev || !q_and_gate_dev || !out_dev) return fail(SAETTA_ERR_BAD_ARG, "prefill encode: null pointer");
     if (int rc = prefill_check(q_dev, dtype, p)) return rc;
+    if (dtype != SAETTA_F16)
+        return fail(SAETTA_ERR_UNSUPPORTED, "prefill encode: binary16 only (bfloat16 values need AttGemm's binary16 staging copy)");
+    if (!aligned16(keys_dev) || !aligned16(values_dev)) return fail(SAETTA_ERR_BAD_ARG, "prefill encode: keys and values must be 16-byte aligned");
     if (!p.tokens) return SAETTA_OK;
     DeviceGuard guard(device);
     if (!guard.ok) return fail(SAETTA_ERR_CUDA, "prefill encode: cannot select the device");

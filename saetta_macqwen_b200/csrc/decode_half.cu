@@ -30,7 +30,7 @@
 
 #include <algorithm>
 
-#include "host.hpp"
+#include "merge_role.cuh"
 
 namespace saetta {
 
@@ -46,21 +46,22 @@ constexpr int kSlab = kTile * 128;          // 32 tokens x 64 dims, 128-byte row
 constexpr int kSideBytes = kKv * 4 * kSlab; // the tile's keys (or values): slab = kv*4 + dims/64
 constexpr int kStageBytes = 2 * kSideBytes;
 constexpr int kStages = 3;
-constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in the merge kernel's fragment order
-constexpr int kPartKv = kFragFloats + 16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;
 constexpr int kPrefetchTiles = 2;
-constexpr int kSmem = 1024 /*align*/ + kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 16;
+constexpr int kSmem = 1024 /*align*/ + kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 32;
+static_assert(kMergeRoleSmem <= kSmem - 1024, "the merge role fits a CTA's shared memory");
 static_assert(kWarps * 2 * kFragFloats * 4 <= kStages * kStageBytes, "the end-of-range merge parks in the ring");
 
 struct Args {
     const uint8_t *k, *v; // [capacity][2][256] binary16
     const float *q;       // [m][16][256]
     float *parts;         // [part][m][kv][kPartKv]
-    uint32_t *status;
+    uint32_t *status;     // the op's status words (merge_role.cuh)
     const saetta_token_params *params;
     uint32_t m, row_step, capacity;
+    uint32_t n_decode;    // split-KV CTAs (= parts); the blocks after them run the merge role
+    MergeOut mo;
 };
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
@@ -116,11 +117,17 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     static_assert(NR == 1 || !BF16, "two rows per pass need binary16");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    if (blockIdx.x >= a.n_decode) { // the blocks after the split-KV CTAs merge what those leave
+        merge_role<kThreads>(a.parts, a.n_decode, a.m, blockIdx.y * NR, NR, a.mo, a.status, blockIdx.y, blockIdx.x - a.n_decode, smem);
+        return;
+    }
     uint8_t *stages = smem;
     float *ml = reinterpret_cast<float *>(smem + kStages * kStageBytes); // [warp][m of 8 heads, l of 8 heads]
     uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
     uint64_t *empty = full + kStages;
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + kStages);
+    uint64_t *ready = empty + kStages;  // the producer has decided what the ring holds (see `skip`)
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(ready + 1);
+    volatile uint32_t *skip = abort_flag + 2; // stages filled before the dependency wait that must be thrown away
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -128,6 +135,8 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kWarps);
         }
+        mbar_init(ready, 1);
+        *skip = 0;
         abort_flag[0] = 0;
         mbar_fence_init();
     }
@@ -137,22 +146,47 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         const uint32_t last = min(row0 + NR, a.m) - 1; // the pass's last live row sees the most keys
         n_any = min(kv_len + last * a.row_step, a.capacity);
         const uint32_t tiles = (n_any + kTile - 1) / kTile;
-        tb = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
-        te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
+        tb = uint32_t(uint64_t(blockIdx.x) * tiles / a.n_decode);
+        te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / a.n_decode);
     };
-    // While the kernel before this one drains, pull the head of this CTA's range into L2 (the range
-    // comes from a possibly stale kv_len: a hint only, everything is read again after the wait).
-    if (warp == kWarps && lane == 0) {
+    auto issue_tile = [&](uint32_t t, uint32_t st) { // the producer warp, all lanes
+        uint8_t *dst = stages + st * kStageBytes;
+        if (lane == 0) mbar_expect_tx(&full[st], kStageBytes);
+        __syncwarp();
+        // lanes 0..7: the key slabs, 8..15: the value slabs (slab = kv*4 + dims/64)
+        if (lane < 16) {
+            const int sl = lane & 7;
+            tma_load_3d(dst + (lane >> 3) * kSideBytes + sl * kSlab, lane < 8 ? &map_k : &map_v, &full[st], (sl & 3) * 64,
+                        sl >> 2, int(t * kTile));
+        }
+        __syncwarp();
+    };
+    // Before the dependency wait -- while the launch before this one still runs -- the producer fills
+    // the copy ring with the head of this CTA's range and asks for the tiles after those to be brought
+    // into L2.  The launch before may write the rows of the new tokens, positions kv_len - 1 and up,
+    // and nothing below (whatever ran before IT has completed), so the ring takes only tiles that end
+    // below kv_len - 1; after the wait kv_len is read again, and if it is not the value the early
+    // range was made from, the early stages are thrown away (`skip`).
+    uint32_t pre = 0, kv_hint = 0;
+    if (warp == kWarps) {
+        kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
         uint32_t tb, te, n_hint;
-        range(*reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len), tb, te, n_hint);
-        const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
-        for (uint32_t t = 0; t < nt; t++) {
-            l2_prefetch(a.k + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
-            l2_prefetch(a.v + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
+        range(kv_hint, tb, te, n_hint);
+        const uint32_t safe = kv_hint ? (kv_hint - 1) / kTile : 0; // tiles [0, safe) hold rows below kv_len - 1 only
+        const uint32_t te_safe = min(te, safe);
+        pre = te_safe > tb ? min(te_safe - tb, uint32_t(kStages)) : 0u;
+        for (uint32_t j = 0; j < pre; j++) issue_tile(tb + j, j);
+        if (lane == 0) {
+            const uint32_t t0 = tb + pre;
+            const uint32_t nt = te > t0 ? min(te - t0, uint32_t(kPrefetchTiles)) : 0u;
+            for (uint32_t t = 0; t < nt; t++) {
+                l2_prefetch(a.k + size_t(t0 + t) * kTile * kRowBytes, kTile * kRowBytes);
+                l2_prefetch(a.v + size_t(t0 + t) * kTile * kRowBytes, kTile * kRowBytes);
+            }
         }
     }
-    pdl_wait();              // q, the token parameters and the cache may come from the kernel before
-    pdl_launch_dependents(); // the merge kernel may be scheduled as SMs free up; it waits for this grid
+    pdl_wait();              // q, the token parameters and the new rows of the cache may come from the launch before
+    pdl_launch_dependents(); // the next launch's CTAs may take the SMs this grid's CTAs leave
     uint32_t tile_begin, tile_end, n_any;
     range(a.params->kv_len, tile_begin, tile_end, n_any);
     uint32_t n_row[NR]; // keys each row of the pass sees (0 for a row past m)
@@ -168,8 +202,13 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         // (same register pool rule as in decode_quant.cu: 128 x (168 - 40) = 256 x (232 - 168))
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp != kWarps) return;
-        uint32_t it = 0;
-        for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
+        const bool keep = a.params->kv_len == kv_hint; // then the early range is this range
+        if (lane == 0) {
+            *skip = keep ? 0u : pre;
+            mbar_arrive(ready);
+        }
+        uint32_t it = pre; // ring slots already issued
+        for (uint32_t t = tile_begin + (keep ? pre : 0u); t < tile_end; t++, it++) {
             const uint32_t st = it % kStages, round = it / kStages;
             if (!mbar_wait(&empty[st], (round & 1) ^ 1, abort_flag)) {
                 if (lane == 0) {
@@ -178,16 +217,7 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                 }
                 break;
             }
-            uint8_t *dst = stages + st * kStageBytes;
-            if (lane == 0) mbar_expect_tx(&full[st], kStageBytes);
-            __syncwarp();
-            // lanes 0..7: the key slabs, 8..15: the value slabs (slab = kv*4 + dims/64)
-            if (lane < 16) {
-                const int sl = lane & 7;
-                tma_load_3d(dst + (lane >> 3) * kSideBytes + sl * kSlab, lane < 8 ? &map_k : &map_v, &full[st], (sl & 3) * 64,
-                            sl >> 2, int(t * kTile));
-            }
-            __syncwarp();
+            issue_tile(t, st);
         }
         // Leave only once every copy this warp issued has landed (bounded): the shared memory must
         // not be handed to another CTA with copies in flight.
@@ -244,7 +274,21 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         Mref[r] = -INFINITY, lsum[r] = 0.f;
     }
 
+    // Start past the early stages, handed back unread, when the producer found them stale.
     uint32_t it = 0;
+    if (!mbar_wait(ready, 0, abort_flag)) {
+        if (lane == 0) {
+            atomicOr(a.status, kStatusFullTimeout);
+            *abort_flag = 1;
+        }
+    } else {
+        it = *skip;
+        for (uint32_t k = 0; k < it; k++) {
+            mbar_wait(&full[k], 0, abort_flag);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[k]);
+        }
+    }
     for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
         const uint32_t st = it % kStages, round = it / kStages;
         if (!mbar_wait(&full[st], round & 1, abort_flag)) {
@@ -411,6 +455,12 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             dst[kFragFloats + 8 + 2 * i] = lc[r][0], dst[kFragFloats + 8 + 2 * i + 1] = lc[r][1];
         }
     }
+    // The partial is written: tell the merge CTAs of this launch (the writers meet, then one of
+    // them fences and takes the ticket).
+    if (a.mo.n_merge) {
+        asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+        if (threadIdx.x == 0) ticket_arrive(a.status, blockIdx.y);
+    }
 }
 
 } // namespace half_decode
@@ -442,7 +492,9 @@ static EncodeTiledFn encode_fn() {
 }
 
 int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t *status, uint32_t m, uint32_t row_step,
-                       int splits, uint32_t capacity, const saetta_token_params *params, cudaStream_t stream) {
+                       int splits, uint32_t capacity, const saetta_token_params *params, const MergeOut &mo,
+                       cudaStream_t stream) {
+    if (splits < 1 || splits > kMergeRoleMaxParts) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: 1..160 split-KV parts");
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(SAETTA_ERR_CUDA, "decode attention: cuTensorMapEncodeTiled is not available");
     // rows [capacity][2][256]: a box is one slab, 64 dims of one kv head x 32 tokens, 128-byte swizzle
@@ -461,14 +513,19 @@ int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t 
     a.k = static_cast<const uint8_t *>(kv.k), a.v = static_cast<const uint8_t *>(kv.v);
     a.q = q, a.parts = parts, a.status = status, a.params = params;
     a.m = m, a.row_step = row_step, a.capacity = capacity;
-    const int ctas = splits; // one part per CTA, as many as the merge will read; CTAs past the last tile leave an empty part
+    // blocks [0, n_decode): one part per CTA (CTAs past the last tile leave an empty part); the n_merge
+    // blocks after them merge the parts of their pass
+    a.n_decode = uint32_t(splits), a.mo = mo;
+    const bool pairs = kv.dtype != SAETTA_BF16 && m > 1; // two rows per pass share every load of the cache
+    a.mo.n_merge = merge_role_ctas(pairs ? 2 : 1);
+    const unsigned ctas = a.n_decode + a.mo.n_merge;
     if (kv.dtype == SAETTA_BF16)
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, true>, dim3(ctas, m), dim3(half_decode::kThreads),
                                half_decode::kSmem, stream, mk, mv, a));
     else if (m == 1)
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, false>, dim3(ctas, 1), dim3(half_decode::kThreads),
                                half_decode::kSmem, stream, mk, mv, a));
-    else // two rows per pass share every load of the cache
+    else
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<2, false>, dim3(ctas, (m + 1) / 2), dim3(half_decode::kThreads),
                                half_decode::kSmem, stream, mk, mv, a));
     return SAETTA_OK;

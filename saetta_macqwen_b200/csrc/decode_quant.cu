@@ -36,7 +36,7 @@
 
 #include <mutex>
 
-#include "host.hpp"
+#include "merge_role.cuh"
 
 namespace saetta {
 
@@ -45,11 +45,8 @@ constexpr int kSub = 16;      // tokens per MMA sub-tile
 constexpr int kWarps = 8;     // consumer warps
 constexpr int kThreads = (kWarps + 4) * 32; // two consumer warpgroups + the producer's warpgroup
 constexpr int kKv = 2;        // kv heads covered by one stage
-constexpr int kFragFloats = 2048; // 8 heads x 256 dims of one (row, kv) in fragment order
-constexpr int kPartKv = kFragFloats + 16; // + m[8], l[8]
 constexpr float kLog2e = 1.4426950408889634f;
-// Tiles of a CTA's range pulled into L2 before the dependency wait.  Measured 0 / 4 / 8 / 16: four is best
-// (deeper prefetches queue ahead of the ring's own copies when the wait turns out to be short).
+// Tiles of a CTA's range, beyond those the copy ring takes before the dependency wait, pulled into L2 there.
 constexpr int kPrefetchTiles = 4;
 constexpr float kRescale = 8.0f; // move the running maximum when it grows by more than 2^8
 
@@ -74,16 +71,9 @@ static_assert(kMergeBytes >= kKv * kFragFloats * 4, "merge buffers fit");
 template <int BITS>
 constexpr int smem_bytes() {
     return Stage<BITS>::kStages * Stage<BITS>::kBytes + kMergeBytes + kQAuxBytes + kWarps * 2 * 16 * 4 +
-           2 * Stage<BITS>::kStages * 8 + 16;
+           2 * Stage<BITS>::kStages * 8 + 32;
 }
-
-#ifdef SAETTA_DQ_TRACE
-__device__ unsigned long long dq_trace[160][8][8]; // [cta][warp][event] global timer ns
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define DQ_MARK(ev) if (lane == 0 && warp < 8) dq_trace[blockIdx.x][warp][ev] = gtime()
-#else
-#define DQ_MARK(ev)
-#endif
+static_assert(kMergeRoleSmem <= smem_bytes<8>() && kMergeRoleSmem <= smem_bytes<4>(), "the merge role fits a CTA's shared memory");
 
 struct DecodeArgs {
     Segment seg;               // the one segment of a single-sequence launch (tiles filled on device)
@@ -91,11 +81,13 @@ struct DecodeArgs {
     const uint32_t *cta_first; // batched: CTA c runs segs[cta_first[c] .. cta_first[c+1])
     const float *q;            // [rows][16][256]
     float *parts;              // [part][rows][kv][kPartKv]
-    uint32_t *status;
+    uint32_t *status;          // the op's status words (merge_role.cuh)
     const saetta_token_params *params;
     uint32_t m;        // query rows
     uint32_t row_step; // row r sees kv_len + r*row_step keys
     uint32_t capacity;
+    uint32_t n_decode; // split-KV CTAs (= parts); blocks past them run the merge role
+    MergeOut mo;
 };
 
 __device__ __forceinline__ uint32_t lop_and_or(uint32_t w, uint32_t mask, uint32_t magic) {
@@ -116,55 +108,91 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
     using St = Stage<BITS>;
     constexpr int NS = St::kStages;
     extern __shared__ __align__(128) uint8_t smem[];
+    if (blockIdx.x >= a.n_decode) { // the blocks after the split-KV CTAs merge what those leave
+        merge_role<kThreads>(a.parts, a.n_decode, a.m, blockIdx.y * ROWS, ROWS, a.mo, a.status, blockIdx.y,
+                             blockIdx.x - a.n_decode, smem);
+        return;
+    }
     uint8_t *stages = smem;
     float *merge = reinterpret_cast<float *>(smem + NS * St::kBytes);
     float *qsums = merge + kMergeBytes / 4;
     float *ml = qsums + kQAuxBytes / 4; // [warp][row of the warp][m of 8 heads, l of 8 heads]
     uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
     uint64_t *empty = full + NS;
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + NS);
+    uint64_t *ready = empty + NS;       // the producer has decided what the ring holds (see `skip`)
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(ready + 1);
+    volatile uint32_t *skip = abort_flag + 2; // stages filled before the dependency wait that must be thrown away
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    DQ_MARK(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kWarps);
         }
+        mbar_init(ready, 1);
+        *skip = 0;
         abort_flag[0] = 0;
         abort_flag[1] = 0; // a word that stays 0, for waits that must ignore the abort flag
         mbar_fence_init();
     }
     __syncthreads();
-#ifndef SAETTA_EXP_NO_PREFETCH
-    // While the kernel before this one drains, pull the head of this CTA's tile range into L2 (and
-    // warm the TLB).  The range comes from a possibly stale kv_len: it is only a hint, every value
-    // is read again after the wait; L2 is the point of coherence, so lines prefetched early still
-    // show what the kernel before writes afterwards.
-    if (warp == kWarps && lane == 0 && !a.segs) {
-        const uint32_t kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
-        const uint32_t longest = min(kv_hint + (a.m - 1) * a.row_step, a.capacity);
+
+    // The tile range of a single-sequence launch's CTA for a given kv_len.
+    auto tile_range = [&](uint32_t kv_len, uint32_t &tb, uint32_t &te) {
+        const uint32_t longest = min(kv_len + (a.m - 1) * a.row_step, a.capacity);
         const uint32_t tiles = (longest + kTile - 1) / kTile;
-        const uint32_t tb = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
-        const uint32_t te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
-        const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
-        const size_t tok = size_t(tb) * kTile;
-        for (uint32_t t = 0; t < nt; t += 2) { // two tiles (32 KB of 8-bit codes) per request
-            const uint32_t n = min(nt - t, 2u);
-            l2_prefetch((const uint8_t *)a.seg.k + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
-            l2_prefetch((const uint8_t *)a.seg.v + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
-        }
-        if (nt) {
-            l2_prefetch((const uint8_t *)a.seg.ks + tok * St::kParamRow, nt * St::kParams);
-            l2_prefetch((const uint8_t *)a.seg.kz + tok * St::kParamRow, nt * St::kParams);
-            l2_prefetch((const uint8_t *)a.seg.vs + tok * St::kParamRow, nt * St::kParams);
-            l2_prefetch((const uint8_t *)a.seg.vz + tok * St::kParamRow, nt * St::kParams);
+        tb = uint32_t(uint64_t(blockIdx.x) * tiles / a.n_decode);
+        te = uint32_t(uint64_t(blockIdx.x + 1) * tiles / a.n_decode);
+    };
+    auto issue_tile = [&](const Segment &s, uint32_t t, uint32_t st) { // one elected lane
+        uint8_t *dst = stages + st * St::kBytes;
+        mbar_expect_tx(&full[st], St::kBytes);
+        const size_t tok = size_t(t) * kTile;
+        bulk_g2s(dst + St::kK, (const uint8_t *)s.k + tok * St::kCodeRow, St::kCodes, &full[st]);
+        bulk_g2s(dst + St::kV, (const uint8_t *)s.v + tok * St::kCodeRow, St::kCodes, &full[st]);
+        bulk_g2s(dst + St::kKs, (const uint8_t *)s.ks + tok * St::kParamRow, St::kParams, &full[st]);
+        bulk_g2s(dst + St::kKz, (const uint8_t *)s.kz + tok * St::kParamRow, St::kParams, &full[st]);
+        bulk_g2s(dst + St::kVs, (const uint8_t *)s.vs + tok * St::kParamRow, St::kParams, &full[st]);
+        bulk_g2s(dst + St::kVz, (const uint8_t *)s.vz + tok * St::kParamRow, St::kParams, &full[st]);
+    };
+
+    // Before the dependency wait -- while the launch before this one (the layer before's merge, or
+    // this token's attention prep) still runs -- the producer already fills the copy ring with the
+    // head of this CTA's range, and asks for the tiles after those to be brought into L2.  What may
+    // be read this early: the launch before may write the rows of the new tokens, positions
+    // kv_len - 1 and up, and nothing below (the launches before IT have completed: it passed its own
+    // wait before it let this one start).  So the ring takes only tiles that end below kv_len - 1,
+    // and after the wait the producer reads kv_len again: if it is not the value the early range was
+    // made from, the early stages are thrown away (`skip`) and the range starts over.  The L2
+    // requests are hints and may cover any row.
+    uint32_t pre = 0, kv_hint = 0;
+    if (warp == kWarps && !a.segs) {
+        kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
+        uint32_t tb, te;
+        tile_range(kv_hint, tb, te);
+        const uint32_t safe = kv_hint ? (kv_hint - 1) / kTile : 0; // tiles [0, safe) hold rows below kv_len - 1 only
+        const uint32_t te_safe = min(te, safe);
+        pre = te_safe > tb ? min(te_safe - tb, uint32_t(NS)) : 0u;
+        if (lane == 0) {
+            for (uint32_t j = 0; j < pre; j++) issue_tile(a.seg, tb + j, j);
+            const uint32_t t0 = tb + pre;
+            const uint32_t nt = te > t0 ? min(te - t0, uint32_t(kPrefetchTiles)) : 0u;
+            const size_t tok = size_t(t0) * kTile;
+            for (uint32_t t = 0; t < nt; t += 2) { // two tiles (32 KB of 8-bit codes) per request
+                const uint32_t n = min(nt - t, 2u);
+                l2_prefetch((const uint8_t *)a.seg.k + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
+                l2_prefetch((const uint8_t *)a.seg.v + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
+            }
+            if (nt) {
+                l2_prefetch((const uint8_t *)a.seg.ks + tok * St::kParamRow, nt * St::kParams);
+                l2_prefetch((const uint8_t *)a.seg.kz + tok * St::kParamRow, nt * St::kParams);
+                l2_prefetch((const uint8_t *)a.seg.vs + tok * St::kParamRow, nt * St::kParams);
+                l2_prefetch((const uint8_t *)a.seg.vz + tok * St::kParamRow, nt * St::kParams);
+            }
         }
     }
-#endif
-    pdl_wait();              // q, the token parameters and the cache may come from the kernel before
-    pdl_launch_dependents(); // the merge kernel may be scheduled as SMs free up; it waits for this grid
-    DQ_MARK(5);
+    pdl_wait();              // q, the token parameters and the new rows of the cache may come from the launch before
+    pdl_launch_dependents(); // the next launch's CTAs may take the SMs this grid's CTAs leave
 
     // The segments this CTA runs.
     uint32_t seg_lo = 0, seg_hi = 1;
@@ -178,11 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         if (a.segs) return a.segs[si];
         Segment s = a.seg;
         const uint32_t kv_len = a.params->kv_len;
-        uint32_t longest = kv_len + (a.m - 1) * a.row_step;
-        longest = min(longest, a.capacity);
-        const uint32_t tiles = (longest + kTile - 1) / kTile;
-        s.tile_begin = uint32_t(uint64_t(blockIdx.x) * tiles / gridDim.x);
-        s.tile_end = uint32_t(uint64_t(blockIdx.x + 1) * tiles / gridDim.x);
+        tile_range(kv_len, s.tile_begin, s.tile_end);
         s.kv_len = kv_len;
         s.part = blockIdx.x;
         s.seq = 0;
@@ -191,11 +215,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 
     auto producer_role = [&]() {
         // ---------------------------------------------------------------- producer
-        uint32_t it = 0;
+        uint32_t it = pre; // ring slots already issued
         bool ok = true;
         for (uint32_t si = seg_lo; si < seg_hi && ok; si++) {
             const Segment s = load_segment(si);
-            for (uint32_t t = s.tile_begin; t < s.tile_end; t++, it++) {
+            uint32_t t = s.tile_begin;
+            if (si == seg_lo) {
+                const bool keep = s.kv_len == kv_hint; // then the early range is this range
+                if (keep) t += pre;
+                if (lane == 0) {
+                    *skip = keep ? 0u : pre;
+                    mbar_arrive(ready);
+                }
+            }
+            for (; t < s.tile_end; t++, it++) {
                 const uint32_t st = it % NS, round = it / NS;
                 if (!mbar_wait(&empty[st], (round & 1) ^ 1, abort_flag)) {
                     if (lane == 0) {
@@ -205,17 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     ok = false;
                     break;
                 }
-                if (lane == 0) {
-                    uint8_t *dst = stages + st * St::kBytes;
-                    mbar_expect_tx(&full[st], St::kBytes);
-                    const size_t tok = size_t(t) * kTile;
-                    bulk_g2s(dst + St::kK, (const uint8_t *)s.k + tok * St::kCodeRow, St::kCodes, &full[st]);
-                    bulk_g2s(dst + St::kV, (const uint8_t *)s.v + tok * St::kCodeRow, St::kCodes, &full[st]);
-                    bulk_g2s(dst + St::kKs, (const uint8_t *)s.ks + tok * St::kParamRow, St::kParams, &full[st]);
-                    bulk_g2s(dst + St::kKz, (const uint8_t *)s.kz + tok * St::kParamRow, St::kParams, &full[st]);
-                    bulk_g2s(dst + St::kVs, (const uint8_t *)s.vs + tok * St::kParamRow, St::kParams, &full[st]);
-                    bulk_g2s(dst + St::kVz, (const uint8_t *)s.vz + tok * St::kParamRow, St::kParams, &full[st]);
-                }
+                if (lane == 0) issue_tile(s, t, st);
                 __syncwarp();
             }
         }
@@ -224,6 +247,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         const uint32_t issued = it;
         for (uint32_t k = issued > NS ? issued - NS : 0; k < issued; k++)
             mbar_wait(&full[k % NS], (k / NS) & 1, abort_flag, 2000000u);
+    };
+    // Consumers: the ring position to start from -- past the early stages, handed back unread, when
+    // the producer found them stale.
+    auto consumer_start = [&]() -> uint32_t {
+        if (!mbar_wait(ready, 0, abort_flag)) {
+            if (lane == 0) {
+                atomicOr(a.status, kStatusFullTimeout);
+                *abort_flag = 1;
+            }
+            return 0;
+        }
+        const uint32_t n = *skip;
+        for (uint32_t k = 0; k < n; k++) {
+            mbar_wait(&full[k], 0, abort_flag);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[k]);
+        }
+        return n;
     };
 
     // Registers move from the producer's warpgroup (only one of its warps works, and it needs
@@ -250,11 +291,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         const bool row_live = row < a.m;
         const int g = lane >> 2, i = lane & 3;
         constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
-        // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128
-        // (8 for 4-bit).  For zero-mean values the two terms then no longer cancel, so the 16-bit
-        // rounding of P costs 3x less relative error.  1152 = 0x6480, 1032 = 0x6408, 72 = 0x5480.
-        constexpr uint32_t k1152 = 0x64806480u, k1032 = 0x64086408u, k72 = 0x54805480u;
-        constexpr float kVCentre = BITS == 8 ? 128.f : 8.f;
+        // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128, or 7.5
+        // for 4-bit.  For zero-mean values the two terms then no longer cancel, so the 16-bit rounding
+        // of P costs 3x less relative error.  The 4-bit centre is the exact middle of the codes: with
+        // C = 8 the centred codes average -0.5, both sums drift apart in proportion to the tokens a
+        // warp has added up, and the tensor cores' truncating f32 adds turn that drift into an error
+        // that does not shrink with the length (measured: 1.3e-3 relative at 28000 tokens per warp).
+        // Every nibble rides on 64 (ulp 1/16, so 71.5 is exact): 1152 = 0x6480, 71.5 = 0x5478.
+        constexpr uint32_t k1152 = 0x64806480u, k71_5 = 0x54785478u;
+        constexpr float kVCentre = BITS == 8 ? 128.f : 7.5f;
 
         uint32_t it = 0;
         bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
@@ -270,6 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
                     for (int c = 0; c < 4; c++) qraw[G][c] = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
             }
+            if (si == seg_lo) it = consumer_start();
             const Segment s = load_segment(si);
             const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
 
@@ -321,7 +367,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 qza1 = i < 2 ? pack_half2(s0 - h0, s1 - h1) : 0u;
             }
 
-            DQ_MARK(1);
             float O[16][4];
             float Ob[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -338,7 +383,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     alive = false;
                     break;
                 }
-                if (t == s.tile_begin) { DQ_MARK(2); }
                 const uint8_t *sg = stages + st * St::kBytes;
 #pragma unroll 1
                 for (int sub = 0; sub < kTile / kSub; sub++) {
@@ -516,14 +560,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                             const uint32_t x23 = prmt(t2, t3, 0x5410), u23 = prmt(t2, t3, 0x7632);
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
-                                const int sh = 8 * (e >> 1);
-                                const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
-                                const uint32_t ctr = (e & 1) ? k72 : k1032; // magic + 8: the centred code n - 8
-                                const uint32_t a0 = hsub2_u32(lop_and_or(x01 >> sh, mask, mg), ctr);
-                                const uint32_t a1 = hsub2_u32(lop_and_or(u01 >> sh, mask, mg), ctr);
-                                const uint32_t a2 = hsub2_u32(lop_and_or(x23 >> sh, mask, mg), ctr);
-                                const uint32_t a3 = hsub2_u32(lop_and_or(u23 >> sh, mask, mg), ctr);
-                                mma_f16(O[4 * G + e], a0, a1, a2, a3, pbf[G][0], pbf[G][1]);
+                                // nibble e of each half-word into bits 4..7 of its byte: 64 + n, minus 71.5
+                                auto code = [&](uint32_t w) {
+                                    const uint32_t x = e == 0 ? w << 4 : e == 1 ? w : e == 2 ? w >> 4 : w >> 8;
+                                    return hsub2_u32(lop_and_or(x, 0x00f000f0u, k64), k71_5);
+                                };
+                                mma_f16(O[4 * G + e], code(x01), code(u01), code(x23), code(u23), pbf[G][0], pbf[G][1]);
                             }
                         }
                     }
@@ -533,7 +575,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             }
 
             // ---------------------------------------------------------------- end of segment
-            DQ_MARK(3);
             // l of head g over the four lanes that share it; then every lane takes m and l of the
             // heads of its accumulator columns (2i, 2i+1) from lanes g = 2i and g = 2i+1.
             lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
@@ -642,7 +683,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // merge buffers free again
             }
-            DQ_MARK(4);
+        }
+        // The partial is written: tell the merge CTAs of this launch (the writers meet, then one
+        // of them fences and takes the ticket).
+        if (a.mo.n_merge) {
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            if (threadIdx.x == 0) ticket_arrive(a.status, blockIdx.y);
         }
     } else {
         // Several query rows (MTP verify): a warp owns one kv head and two query rows.  The 16 rows
@@ -667,11 +713,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         uint4 *qf = reinterpret_cast<uint4 *>(merge) + combo * 512;
         float *qaux = qsums + combo * 128; // off[r][G][head], sum[r][G][head]
         constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u, k64 = 0x54005400u;
-        // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128
-        // (8 for 4-bit).  For zero-mean values the two terms then no longer cancel, so the 16-bit
-        // rounding of P costs 3x less relative error.  1152 = 0x6480, 1032 = 0x6408, 72 = 0x5480.
-        constexpr uint32_t k1152 = 0x64806480u, k1032 = 0x64086408u, k72 = 0x54805480u;
-        constexpr float kVCentre = BITS == 8 ? 128.f : 8.f;
+        // Value codes are centred before the P V product: v = s*(c - C) + (z + C*s) with C = 128, or 7.5
+        // for 4-bit.  For zero-mean values the two terms then no longer cancel, so the 16-bit rounding
+        // of P costs 3x less relative error.  The 4-bit centre is the exact middle of the codes: with
+        // C = 8 the centred codes average -0.5, both sums drift apart in proportion to the tokens a
+        // warp has added up, and the tensor cores' truncating f32 adds turn that drift into an error
+        // that does not shrink with the length (measured: 1.3e-3 relative at 28000 tokens per warp).
+        // Every nibble rides on 64 (ulp 1/16, so 71.5 is exact): 1152 = 0x6480, 71.5 = 0x5478.
+        constexpr uint32_t k1152 = 0x64806480u, k71_5 = 0x54785478u;
+        constexpr float kVCentre = BITS == 8 ? 128.f : 7.5f;
 
         uint32_t it = 0;
         bool alive = true; // false once a wait gave up: skip the tiles, keep the barriers
@@ -746,7 +796,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 qza1 = pack_half2(qaux[64 + (4 + 2 * i) * 8 + g], qaux[64 + (4 + 2 * i + 1) * 8 + g]);
             }
 
-            DQ_MARK(1);
             // O[n-tile (group G, byte e)][c]: c0, c1 = MMA row g (dims G*64 + (2i | 2i+1)*8 + e), c2, c3 = row g+8.
             float O[32][4];
             float Ob[4] = {0.f, 0.f, 0.f, 0.f}; // sum_t P (z + C s): columns 2i, 2i+1 = groups (lanes i < 2)
@@ -756,6 +805,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
             for (int r = 0; r < NR; r++) Mref[r] = -INFINITY, lsum[r] = 0.f;
 
+            if (si == seg_lo) it = consumer_start();
             for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
                 const uint32_t st = it % NS, round = it / NS;
                 if (!mbar_wait(&full[st], round & 1, abort_flag)) {
@@ -766,7 +816,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     alive = false;
                     break;
                 }
-                if (t == s.tile_begin) { DQ_MARK(2); }
                 const uint8_t *sg = stages + st * St::kBytes;
 #pragma unroll 1
                 for (int sub = 0; sub < kTile / kSub; sub++) {
@@ -969,12 +1018,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                             const uint32_t x23[2] = {prmt(t2, t3, 0x5410), prmt(t2, t3, 0x7632)};
 #pragma unroll
                             for (int e = 0; e < 8; e++) { // nibble e of the 8
-                                const int sh = 8 * ((e & 3) >> 1);
-                                const uint32_t mask = (e & 1) ? 0x00f000f0u : 0x000f000fu, mg = (e & 1) ? k64 : k1024;
-                                const uint32_t ctr = (e & 1) ? k72 : k1032; // magic + 8: the centred code n - 8
-                                const uint32_t b0 = hsub2_u32(lop_and_or(x01[e >> 2] >> sh, mask, mg), ctr);
-                                const uint32_t b1 = hsub2_u32(lop_and_or(x23[e >> 2] >> sh, mask, mg), ctr);
-                                mma_f16(O[G * 8 + e], A[0], A[1], A[2], A[3], b0, b1);
+                                // nibble e & 3 of each half-word into bits 4..7 of its byte: 64 + n, minus 71.5
+                                auto code = [&](uint32_t w) {
+                                    const uint32_t x = (e & 3) == 0 ? w << 4 : (e & 3) == 1 ? w : (e & 3) == 2 ? w >> 4 : w >> 8;
+                                    return hsub2_u32(lop_and_or(x, 0x00f000f0u, k64), k71_5);
+                                };
+                                mma_f16(O[G * 8 + e], A[0], A[1], A[2], A[3], code(x01[e >> 2]), code(x23[e >> 2]));
                             }
                         }
                     }
@@ -984,7 +1033,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             }
 
             // ---------------------------------------------------------------- end of segment
-            DQ_MARK(3);
 #pragma unroll
             for (int r = 0; r < NR; r++) { // l of head g over the four lanes that share it
                 lsum[r] += __shfl_xor_sync(0xffffffffu, lsum[r], 1);
@@ -1058,7 +1106,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 if (slot == 0 && i == 0) dst[kFragFloats + g] = Mc[r], dst[kFragFloats + 8 + g] = lc[r];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // ring, merge buffer and query fragments free again
-            DQ_MARK(4);
+        }
+        // The partial is written: tell the merge CTAs of this launch (the writers meet, then one
+        // of them fences and takes the ticket).
+        if (a.mo.n_merge) {
+            asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+            if (threadIdx.x == 0) ticket_arrive(a.status, blockIdx.y);
         }
     }
 }
@@ -1070,10 +1123,14 @@ static int launch_one(const DecodeArgs &a, dim3 grid, cudaStream_t stream) {
 }
 
 template <int BITS>
-static int launch_rows(const DecodeArgs &a, int ctas, cudaStream_t stream) {
-    if (a.m == 1) return launch_one<BITS, 1>(a, dim3(ctas, 1), stream);
-    if (a.m == 2) return launch_one<BITS, 2>(a, dim3(ctas, 1), stream);
-    return launch_one<BITS, 4>(a, dim3(ctas, (a.m + 3) / 4), stream);
+static int launch_rows(DecodeArgs &a, cudaStream_t stream) {
+    // blocks [0, n_decode) are the split-KV CTAs, the n_merge after them merge (per pass)
+    const uint32_t rows_pass = a.m == 1 ? 1 : a.m == 2 ? 2 : 4;
+    a.mo.n_merge = merge_role_ctas(rows_pass);
+    const dim3 grid(a.n_decode + a.mo.n_merge, rows_pass == 4 ? (a.m + 3) / 4 : 1);
+    if (rows_pass == 1) return launch_one<BITS, 1>(a, grid, stream);
+    if (rows_pass == 2) return launch_one<BITS, 2>(a, grid, stream);
+    return launch_one<BITS, 4>(a, grid, stream);
 }
 
 int decode_quant_configure(int device) {
@@ -1093,13 +1150,15 @@ int decode_quant_configure(int device) {
 
 int launch_decode_quant(const KvView &kv, const float *q, float *parts, uint32_t *status,
                         uint32_t m, uint32_t row_step, int splits, uint32_t capacity,
-                        const saetta_token_params *params, cudaStream_t stream) {
+                        const saetta_token_params *params, const MergeOut &mo, cudaStream_t stream) {
+    if (splits < 1 || splits > kMergeRoleMaxParts) return fail(SAETTA_ERR_BAD_SHAPE, "decode attention: 1..160 split-KV parts");
     DecodeArgs a{};
     a.seg.k = kv.k, a.seg.v = kv.v, a.seg.ks = kv.ks, a.seg.kz = kv.kz, a.seg.vs = kv.vs, a.seg.vz = kv.vz;
     a.segs = nullptr, a.cta_first = nullptr;
     a.q = q, a.parts = parts, a.status = status, a.params = params;
     a.m = m, a.row_step = row_step, a.capacity = capacity;
-    return kv.bits == 8 ? launch_rows<8>(a, splits, stream) : launch_rows<4>(a, splits, stream);
+    a.n_decode = uint32_t(splits), a.mo = mo;
+    return kv.bits == 8 ? launch_rows<8>(a, stream) : launch_rows<4>(a, stream);
 }
 
 int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uint32_t *cta_first_dev,
@@ -1109,19 +1168,21 @@ int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uin
     a.segs = segments_dev, a.cta_first = cta_first_dev;
     a.q = q, a.parts = parts, a.status = status, a.params = nullptr;
     a.m = 1, a.row_step = 0, a.capacity = 0xffffffffu;
+    a.n_decode = uint32_t(ctas), a.mo = MergeOut{}; // the ragged batch keeps its merge as a launch of its own (merge.cu)
     return bits == 8 ? launch_one<8, 1>(a, dim3(ctas, 1), stream) : launch_one<4, 1>(a, dim3(ctas, 1), stream);
 }
 
 // ----------------------------------------------------------------- fixed-scratch entry point
 //
 // Scratch for saetta_decode_record_quant_static: the split-KV partials and the
-// status word live in this file-scope device array instead of a cudaMalloc'd
-// buffer.  Every GPU that loads the library holds these bytes until exit.
+// status words live in these file-scope device arrays instead of cudaMalloc'd
+// buffers.  Every GPU that loads the library holds these bytes until exit.
 constexpr int kStaticMaxRows = 2;
-constexpr int kStaticMaxSplits = 160;
+constexpr int kStaticMaxSplits = kMergeRoleMaxParts;
 constexpr size_t kStaticFloats = size_t(kStaticMaxSplits) * kStaticMaxRows * kKv * kPartKv; // 5.3 MB
 static __device__ __align__(256) float g_static_parts[kStaticFloats];
-static __device__ __align__(256) uint32_t g_static_status[64];
+static __device__ __align__(256) uint32_t g_static_status[64]; // laid out as an op's status words
+static_assert(kStatusWords <= 64, "the status words fit");
 
 struct StaticScratch {
     float *parts = nullptr;   // device address of g_static_parts on that device
@@ -1156,21 +1217,29 @@ int decode_quant_static(int device, const KvView &kv, size_t capacity, const flo
                         cudaStream_t stream) {
     if (m < 1 || m > uint32_t(kStaticMaxRows))
         return fail(SAETTA_ERR_BAD_SHAPE, "static decode: at most 2 query rows fit the fixed scratch (use saetta_decode_create for more)");
+    if (kv.bits != 8 && kv.bits != 4) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: the rows must hold 8- or 4-bit codes");
     if (kv.kv_heads != kKv) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: built for 2 kv heads");
     if (capacity % kTile || !capacity) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: capacity must be a positive multiple of 32");
     if (capacity > 0xffffffe0ull) return fail(SAETTA_ERR_BAD_SHAPE, "static decode: capacity too large");
     StaticScratch *s = nullptr;
     if (int rc = static_scratch(device, &s)) return rc;
     const int splits = int(std::min<size_t>(size_t(s->splits), capacity / kTile));
-    // The kernels overwrite every partial they later read, so nothing has to be cleared between calls.
-    if (int rc = launch_decode_quant(kv, q, s->parts, s->status, m, 1, splits, uint32_t(capacity), params, stream)) return rc;
-    return launch_merge_frag(s->parts, uint32_t(splits), nullptr, m, kKv, q_and_gate, out, nullptr, stream);
+    // The launch overwrites every partial it later reads, and its merge CTAs put the two counters
+    // in the status words back to zero, so nothing has to be cleared between calls.
+    MergeOut mo{};
+    mo.q_and_gate = q_and_gate, mo.out = out;
+    return launch_decode_quant(kv, q, s->parts, s->status, m, 1, splits, uint32_t(capacity), params, mo, stream);
+}
+
+// The status word of the fixed-scratch path on `device` (bits of bounded waits that gave up); with
+// `clear` it is put back to zero after being read.
+int decode_quant_static_status(int device, cudaStream_t stream, uint32_t *status, bool clear) {
+    StaticScratch *s = nullptr;
+    if (int rc = static_scratch(device, &s)) return rc;
+    SAETTA_CUDA(cudaMemcpyAsync(status, s->status, 4, cudaMemcpyDeviceToHost, stream));
+    if (clear) SAETTA_CUDA(cudaMemsetAsync(s->status, 0, 4, stream));
+    SAETTA_CUDA(cudaStreamSynchronize(stream));
+    return SAETTA_OK;
 }
 
 } // namespace saetta
-
-#ifdef SAETTA_DQ_TRACE
-extern "C" int saetta_debug_decode_trace(unsigned long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, saetta::dq_trace, sizeof(saetta::dq_trace));
-}
-#endif

@@ -90,6 +90,15 @@ struct PeerPush {
     uint32_t *seq_sent;                   // ... and published
     uint32_t world, rank, slot_floats;
 };
+// Where a decode launch's merged result goes: out (gated), part_out (the logical (O, m, l) partial), or
+// the peers' mailboxes (push.world != 0).  n_merge is filled in by the launcher.
+struct MergeOut {
+    const float *q_and_gate = nullptr;
+    float *out = nullptr;
+    float *part_out = nullptr;
+    PeerPush push = {};
+    uint32_t n_merge = 0; // merge CTAs per pass; 0: the launch carries no merge role
+};
 // One mailbox word: a float with the number of the exchange it belongs to, written by one 64-bit
 // store so that the reader sees both or neither.
 __host__ __device__ inline unsigned long long peer_word(float v, uint32_t seq) {
@@ -152,9 +161,11 @@ struct Segment {
 };
 
 // decode_quant.cu: tensor-core split-KV over 8/4-bit codes.
+// The merge over the parts and what follows it (gate, logical partial, or the push to the peers) run
+// inside the same launch (merge_role.cuh); `status` points at kStatusWords zeroed words.
 int launch_decode_quant(const KvView &kv, const float *q, float *parts, uint32_t *status,
                         uint32_t m, uint32_t row_step, int splits, uint32_t capacity,
-                        const saetta_token_params *params, cudaStream_t stream);
+                        const saetta_token_params *params, const MergeOut &mo, cudaStream_t stream);
 size_t decode_quant_part_floats(size_t kv_heads); // floats per (part, row) of the internal partial format
 int launch_decode_quant_batched(int bits, const Segment *segments_dev, const uint32_t *cta_first_dev,
                                 int ctas, const float *q, float *parts, uint32_t *status,
@@ -163,10 +174,12 @@ int decode_quant_configure(int device);
 int decode_quant_static(int device, const KvView &kv, size_t capacity, const float *q, uint32_t m,
                         const float *q_and_gate, float *out, const saetta_token_params *params,
                         cudaStream_t stream);
+int decode_quant_static_status(int device, cudaStream_t stream, uint32_t *status, bool clear);
 
 // decode_half.cu: tensor-core split-KV over binary16 rows (2 kv heads); partials in decode_quant.cu's format.
 int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t *status, uint32_t m, uint32_t row_step,
-                       int splits, uint32_t capacity, const saetta_token_params *params, cudaStream_t stream);
+                       int splits, uint32_t capacity, const saetta_token_params *params, const MergeOut &mo,
+                       cudaStream_t stream);
 int decode_half_configure(int device);
 
 // decode_exact.cu: f32 arithmetic over f32 / 16-bit rows.

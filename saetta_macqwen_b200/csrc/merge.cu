@@ -5,12 +5,9 @@
 // reference: M = max m_p, l = sum l_p 2^(m_p - M), O = sum O_p 2^(m_p - M),
 // out = O / l * sigmoid(gate).  Maxima are in log2 units.  Parts are added in
 // index order, so the result does not depend on scheduling.
-#include "host.hpp"
+#include "merge_role.cuh"
 
 namespace saetta {
-
-constexpr int kFragFloats = 2048;
-constexpr int kPartKv = kFragFloats + 16;
 
 size_t decode_quant_part_floats(size_t kv_heads) { return kv_heads * size_t(kPartKv); }
 

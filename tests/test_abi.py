@@ -71,6 +71,10 @@ def test_null_arguments_are_refused_before_any_device_work(lib):
     assert lib.saetta_plan_len(None, C.byref(z)) == sa.BAD_ARG
     assert lib.saetta_plan_set_params(None, 0, 0) == sa.BAD_ARG
     assert lib.saetta_plan_run_timed(None, C.byref(f)) == sa.BAD_ARG
+    assert lib.saetta_plan_kernels(None, None, None, 0, C.byref(z)) == sa.BAD_ARG
+    assert lib.saetta_plan_build_where(None, None, 0, 1, C.byref(C.c_void_p())) == sa.BAD_ARG
+    assert lib.saetta_built_len(None, C.byref(z)) == sa.BAD_ARG and lib.saetta_built_run_timed(None, C.byref(f)) == sa.BAD_ARG
+    lib.saetta_built_destroy(None)
     assert lib.saetta_plan_params(None) is None and lib.saetta_plan_stream(None) is None
     lib.saetta_plan_destroy(None)  # a no-op, as free(NULL)
     handle = (C.c_uint8 * 64)()
@@ -81,6 +85,13 @@ def test_null_arguments_are_refused_before_any_device_work(lib):
     assert lib.saetta_peer_slice(None, 8, C.byref(z), C.byref(z)) == sa.BAD_ARG
     assert lib.saetta_decode_publish_cache(None, 1, None, None, None, 0, None, None) == sa.BAD_ARG
     assert lib.saetta_decode_batch_publish(None, 1, None, None, None, None, None) == sa.BAD_ARG
+    # attention_prefill::encode without an object: nulls, then bfloat16 (binary16 only), both before any device work
+    fp = sa.FlashParams(16, 2, 0, 8, 0.0625)
+    assert lib.saetta_prefill_encode(0, None, sa.F16, None, None, None, None, fp, None) == sa.BAD_ARG
+    fake = 4096  # a non-null, 16-byte aligned address that is never dereferenced
+    assert lib.saetta_prefill_encode(0, fake, sa.BF16, fake, fake, fake, fake, fp, None) == sa.UNSUPPORTED
+    assert b"binary16 only" in lib.saetta_last_error()
+    assert lib.saetta_decode_static_status(0, None, None, 0) == sa.BAD_ARG
 
 
 def test_host_quantiser_is_the_oracle_bit_for_bit(lib, oracle):

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 import saetta_macqwen_b200 as sa
-from util import ROW, dev, params_dev
+from util import ROW, dev, params_dev, read_dev
 
 pytestmark = pytest.mark.gpu
 GROUP = 64
@@ -105,7 +105,15 @@ def test_verify_rows_append_bit_exact(oracle, bits):
     torch.cuda.synchronize()
     bufs = cache.buffers()
     assert [rb for _, rb in bufs] == [64 * bits, 64 * bits, 16, 16, 16, 16]
-    # read the four rows back through a dequantise of the whole prefix
+    # the raw words, scales and biases of the four rows, both sides, straight from the cache's buffers
+    pos = 32768
+    (kd, cb), (vd, _), (ks, pb), (kz, _), (vs, _), (vz, _) = bufs
+    for data, scales, biases, x in ((kd, ks, kz, k), (vd, vs, vz, v)):
+        want_d, want_s, want_z = oracle.quantize(x, bits)
+        assert np.array_equal(read_dev(data + pos * cb, 4 * cb).view(np.uint32), want_d)
+        assert np.array_equal(read_dev(scales + pos * pb, 4 * pb).view(np.uint16), want_s)
+        assert np.array_equal(read_dev(biases + pos * pb, 4 * pb).view(np.uint16), want_z)
+    # and through a dequantise of the whole prefix
     kq, vq = cache.quant()
     for side, x in ((kq, k), (vq, v)):
         out = torch.zeros((32768 + 4) * ROW, dtype=torch.int16, device="cuda")
@@ -146,8 +154,19 @@ def test_store_into_half_and_f32_caches(oracle):
         torch.cuda.synchronize()
         (kp, rb), (vp, _) = cache.buffers()
         assert rb == ROW * (4 if bits == 32 else 2)
-        # read back through a decode over rows 7..9 would be indirect; use a resize round trip instead:
-        cache.resize(256)
-        assert cache.capacity == 256
-        cache.resize(128)
-        assert cache.capacity == 128
+        # the stored rows, read back raw: the reference's to_half narrowing (binary16), this build's
+        # bfloat16 twin, or the f32 values themselves; and again after a resize up and down
+        for _ in range(2):
+            (kp, rb), (vp, _) = cache.buffers()
+            for ptr, x in ((kp, k), (vp, v)):
+                raw = read_dev(ptr + 7 * rb, 3 * rb)
+                if bits == 32:
+                    assert np.array_equal(raw.view(np.float32), x)
+                elif dtype == sa.F16:
+                    assert np.array_equal(raw.view(np.uint16), oracle.to_f16_bits(x))
+                else:
+                    assert np.array_equal(raw.view(np.uint16), oracle.to_bf16_bits(x))
+            cache.resize(256)
+            assert cache.capacity == 256
+            cache.resize(128)
+            assert cache.capacity == 128

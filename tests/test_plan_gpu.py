@@ -31,7 +31,7 @@ def test_recorded_decode_step_replays_for_every_position(oracle):
     with plan.recording():
         sa.attention_prep(P, 1, qg, k, v, qn, kn, q, sa.F32, caches[0], params=plan.params, stream=plan.stream)
         op.record_cache(1, q, caches[0], qg, out, plan.params, stream=plan.stream)
-    assert len(plan) == 3  # prep, split-KV attention, merge
+    assert len(plan) == 2  # prep, attention (split-KV CTAs and merge CTAs in one launch)
 
     for s in range(steps):
         pos = ctx + s
@@ -79,3 +79,55 @@ def test_parallel_branch_and_misuse():
     torch.cuda.synchronize()
     # replay r: b = 2r, a_r = a_{r-1} + 1 + 2r  ->  after 3 replays a = 3 + 2*(1+2+3) = 15
     assert float(b[0]) == 6.0 and float(a[0]) == 15.0 and float(a[-1]) == 15.0
+
+
+def test_build_where_replays_the_ops_of_chosen_kernels(oracle):
+    """Plan::build_where (src/plan.rs:190-226) as src/profile.rs:39-121 uses it: the whole recording again,
+    the ops of one kernel alone, and the recording without its barriers."""
+    import torch
+
+    ctx, bits, cap, layers = 900, 8, 1024, 3
+    keys, values = dev(oracle.normal(ctx * ROW, 1)), dev(oracle.normal(ctx * ROW, 2))
+    ones = torch.ones(DIM, device="cuda")
+    caches = [sa.GpuKvCache(0, bits, cap) for _ in range(layers)]
+    for c in caches:
+        c.store_at(keys, values, 0, ctx)
+    op = sa.AttentionRows(0, HEADS, KV, cap, 1)
+    qg = dev(oracle.normal(HEADS * 2 * DIM, 5))
+    k, v = dev(oracle.normal(ROW, 6)), dev(oracle.normal(ROW, 7))
+    q = torch.zeros(layers, HEADS * DIM, device="cuda")
+    out = torch.zeros(layers, HEADS * DIM, device="cuda")
+    plan = sa.Plan(0)
+    with plan.recording():
+        for l, c in enumerate(caches):
+            sa.attention_prep(P, 1, qg, k, v, ones, ones, q[l], sa.F32, c, params=plan.params, stream=plan.stream)
+            op.record_cache(1, q[l], c, qg, out[l], plan.params, stream=plan.stream)
+    kernels = plan.kernels()
+    assert [n for _, n in kernels] == [layers, layers] and sum(n for _, n in kernels) == len(plan)
+    assert "attention_prep" in kernels[0][0] and "decode_quant_kernel" in kernels[1][0]
+
+    plan.set_params(3, ctx)
+    plan.run()
+    want = out.cpu().numpy().copy()
+
+    whole = plan.build_where()  # keep = |_| true, with barriers: the plan itself again
+    assert len(whole) == len(plan)
+    out.zero_()
+    assert whole.run_timed() > 0.0
+    assert np.array_equal(out.cpu().numpy(), want)
+
+    only = plan.build_where(["decode_quant_kernel"])  # the attention ops alone: q and the cache rows are still there
+    assert len(only) == layers
+    out.zero_()
+    assert only.run_timed() > 0.0
+    assert np.array_equal(out.cpu().numpy(), want)
+
+    prep_only = plan.build_where(["attention_prep"])
+    assert len(prep_only) == layers
+    out.zero_()
+    prep_only.run()
+    assert not out.any()  # no attention op ran
+
+    free = plan.build_where(barriers=False)  # a lower bound on the time; its results are not the plan's
+    assert len(free) == len(plan) and free.run_timed() > 0.0
+    assert len(plan.build_where(["no such kernel"])) == 0

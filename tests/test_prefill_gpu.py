@@ -45,6 +45,51 @@ def test_matches_cpu_on_reference_shapes(oracle, pos, tokens):
     assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3, (pos, tokens, max_abs(got, want), rel_rms(got, want))
 
 
+@pytest.mark.parametrize("pos,tokens", [(0, 1), (0, 7), (5, 8), (70, 100), (1000, 64), (0, 300), (4093, 37)])
+def test_prefill_encode_matches_cpu_on_reference_shapes(oracle, pos, tokens):
+    """attention_prefill::encode (src/attention_prefill.rs:39-72), the entry point without an op object,
+    on the shapes of tests/attention_prefill.rs:10-62: binary16 q and cache, `spread` inputs, the
+    (i % 7) - 3 gate pattern.  2e-3 max-abs / 1e-3 relative RMS against the CPU oracle."""
+    import torch
+
+    capacity = (pos + tokens + 63) // 64 * 64 + 64
+    q = oracle.round_f16(oracle.spread(tokens * HEADS * DIM, 1))
+    k = oracle.round_f16(oracle.spread(capacity * ROW, 2))
+    v = oracle.round_f16(oracle.spread(capacity * ROW, 3))
+    qg = ((np.arange(tokens * HEADS * 2 * DIM) % 7) - 3).astype(np.float32)
+    out = torch.full((tokens * HEADS * DIM,), float("nan"), dtype=torch.float32, device="cuda")
+    p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
+    sa.prefill_encode(0, to16(torch, q, sa.F16), to16(torch, k, sa.F16), to16(torch, v, sa.F16), dev(qg), out, p)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
+    want = oracle.attention_rows(q, qg, k, v, [pos + i + 1 for i in range(tokens)], threads=8)
+    assert np.isfinite(got).all()
+    assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3, (pos, tokens, max_abs(got, want), rel_rms(got, want))
+
+
+def test_prefill_encode_matches_att_gemm_and_refuses_bfloat16(oracle):
+    """N(0,1) binary16 inputs with partial RoPE at a position past the first tile: the object-less entry
+    point gives what AttGemm::encode gives, bit for bit (one kernel, no staging on either route), and
+    bfloat16 -- which it could only run with P rounded to 8 bits -- comes back as UNSUPPORTED."""
+    import torch
+
+    pos, tokens = 700, 150
+    q, k, v, qg = bf16_inputs(oracle, pos, tokens, 600)
+    q, k, v = oracle.round_f16(q), oracle.round_f16(k), oracle.round_f16(v)
+    a = run(torch, q, k, v, qg, pos, tokens, sa.F16)
+    out = torch.full((tokens * HEADS * DIM,), float("nan"), dtype=torch.float32, device="cuda")
+    p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
+    qd, kd, vd, gd = to16(torch, q, sa.F16), to16(torch, k, sa.F16), to16(torch, v, sa.F16), dev(qg)
+    sa.prefill_encode(0, qd, kd, vd, gd, out, p)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
+    assert np.array_equal(got, a)
+    check_rows(oracle, got, q, qg, k, v, pos, np.arange(tokens))
+    with pytest.raises(sa.SaettaError) as e:
+        sa.prefill_encode(0, qd, kd, vd, gd, out, p, dtype=sa.BF16)
+    assert e.value.code == sa.UNSUPPORTED
+
+
 def bf16_inputs(oracle, pos, tokens, seed):
     total = pos + tokens
     k = oracle.rope_rows(oracle.normal(total * ROW, seed).reshape(total, ROW), DIM, 64, range(total), 1e7)
@@ -145,8 +190,7 @@ def test_shape_errors(oracle):
 def test_config4_long_context_chunk_over_8bit_prefix(oracle):
     """A 4096-token chunk at position 131072 on top of a 131072-token 8-bit cache
     (the chunk's own rows quantised into the cache first), bf16 queries.  The
-    oracle is evaluated on a sample of rows: first, last, tile edges, a few
-    inside.  Keys are read as the bf16 rounding of s*q+z, values as binary16."""
+    oracle is evaluated on a sample of 64 or more rows.  Keys are read as the bf16 rounding of s*q+z, values as binary16."""
     import torch
 
     pos, tokens, bits = 131072, 4096, 8
@@ -166,5 +210,10 @@ def test_config4_long_context_chunk_over_8bit_prefix(oracle):
     q = oracle.round_bf16(oracle.normal(tokens * HEADS * DIM, 41))
     qg = oracle.normal(tokens * HEADS * 2 * DIM, 42)
     got = run(torch, q, None, None, qg, pos, tokens, sa.BF16, quant=cache.quant())
-    rows = np.array([0, 15, 16, 2047, 2048, 4080, 4095])
-    print("config 4:", check_rows(oracle, got, q, qg, kr.ravel(), vr.ravel(), pos, rows))
+    # 64+ rows: first and last, the 16-token tile edges, the middle of the chunk (where the halves of a
+    # two-GPU row slicing meet), the quarter points, and random rows; all 16 heads of each
+    rng = np.random.default_rng(4)
+    rows = np.unique(np.concatenate([[0, 1, 15, 16, 17, 31, 32, 1023, 1024, 2047, 2048, 2049, 3071, 3072, 4079, 4080, 4094, 4095],
+                                     rng.integers(0, tokens, 50)]))
+    assert len(rows) >= 64
+    print("config 4:", len(rows), "rows", check_rows(oracle, got, q, qg, kr.ravel(), vr.ravel(), pos, rows))

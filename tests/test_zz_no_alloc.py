@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 import saetta_macqwen_b200 as sa
-from util import DIM, HEADS, KV, ROW, dev, params_dev, quant_rows_from_oracle
+from util import DIM, HEADS, KV, ROW, dev, max_abs, params_dev, quant_rows_from_oracle, rel_rms
 
 pytestmark = pytest.mark.gpu
 
@@ -38,8 +38,19 @@ def test_static_scratch_matches_allocating_entry_point(oracle, bits):
         torch.cuda.synchronize()
         # same kernels, same split count, fixed merge order: equal to the last bit
         assert np.array_equal(got.cpu().numpy(), want.cpu().numpy()), (bits, call)
+        # no bounded wait of the fixed-scratch path gave up (the word is shared by all calls on the device)
+        assert sa.decode_static_status(0) == 0
+        if call < 2:  # and pinned on the CPU oracle too, not only on the other GPU path
+            kr, vr = oracle.round_trip(keys, bits), oracle.round_trip(values, bits)
+            ref = oracle.attention_rows(q.cpu().numpy(), qg.cpu().numpy(), kr, vr, [pos + r + 1 for r in range(m)], threads=8)
+            assert max_abs(got.cpu().numpy().reshape(m, HEADS, DIM), ref) < 2e-3
+            assert rel_rms(got.cpu().numpy().reshape(m, HEADS, DIM), ref) < 1e-3
     # a size beyond the fixed scratch is refused, nothing is launched
     q3 = torch.zeros(3 * HEADS * DIM, device="cuda")
     with pytest.raises(sa.SaettaError) as e:
         sa.decode_record_quant_static(0, 3, q3, kq, vq, torch.zeros(3 * HEADS * 2 * DIM, device="cuda"), q3, params_dev(10))
     assert e.value.code == sa.BAD_SHAPE and "at most 2 query rows" in str(e.value)
+    # rows that live on another device than the one named are refused before any launch
+    with pytest.raises(sa.SaettaError) as e:
+        sa.decode_record_quant_static(1, 1, q3, kq, vq, torch.zeros(HEADS * 2 * DIM, device="cuda"), q3, params_dev(10))
+    assert e.value.code == sa.BAD_ARG
