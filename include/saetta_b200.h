@@ -393,9 +393,20 @@ typedef struct saetta_att_gemm saetta_att_gemm;
 /* AttGemm::new(gpu, chunk, kv_heads). */
 int saetta_att_gemm_create(int device, size_t chunk, size_t kv_heads, saetta_att_gemm **out);
 void saetta_att_gemm_destroy(saetta_att_gemm *op);
-/* Grows the 16-bit staging copy a quantised cache is read through to `tokens`
- * tokens now, so that later encodes allocate nothing. */
+/* Allocates now all the scratch encodes over caches of up to `tokens` rows need
+ * -- the 16-bit copies a quantised (or bfloat16-valued) cache is read through,
+ * and the partials of the key splits of a long-context chunk -- as AttGemm::new
+ * does (src/attention_gemm.rs:119-148), so that later encodes allocate nothing
+ * and can be recorded in a Plan.  Without it an encode grows the scratch when it
+ * has to, and refuses to when its stream is being captured. */
 int saetta_att_gemm_reserve(saetta_att_gemm *op, size_t tokens);
+/* The 16-bit copy persists between encodes: per chunk of a long prompt only the
+ * rows from the chunk's first row on are converted, the rows below it are taken
+ * as converted by the encode of the chunk before (same buffers, same types).  A
+ * caller that rewrites rows BELOW the position of its next chunk outside of this
+ * sequence (not a rewind followed by a new prefill from there, which is covered)
+ * says so here, and the next encode converts every row it reads again. */
+int saetta_att_gemm_invalidate(saetta_att_gemm *op);
 /* AttGemm::encode: with keys_q/values_q non-NULL the cache is read from those
  * 8/4-bit rows (through a 16-bit copy, as the reference's kv_stage reads it)
  * and keys_dev/values_dev are ignored. */
@@ -420,6 +431,17 @@ int saetta_att_gemm_partial(saetta_att_gemm *op, const void *q_dev, int dtype,
                             const saetta_quant_rows *keys_q, const saetta_quant_rows *values_q,
                             float *part_dev, saetta_flash_params p, size_t key_lo, size_t key_hi,
                             void *stream);
+
+/* The same for a shard that STORES only its own slice of the sequence (no
+ * counterpart in the reference): row 0 of keys_dev / values_dev / the quantised
+ * rows is the key at global position key_base (a multiple of 64, at most
+ * key_lo), and the buffers hold at least key_hi - key_base rows.  p.pos and
+ * key_lo / key_hi stay global positions. */
+int saetta_att_gemm_partial_shard(saetta_att_gemm *op, const void *q_dev, int dtype,
+                                  const void *keys_dev, const void *values_dev,
+                                  const saetta_quant_rows *keys_q, const saetta_quant_rows *values_q,
+                                  float *part_dev, saetta_flash_params p, size_t key_base,
+                                  size_t key_lo, size_t key_hi, void *stream);
 
 #ifdef __cplusplus
 }

@@ -148,6 +148,8 @@ SYMBOLS = {
     "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
     "saetta_att_gemm_destroy": (None, [_P]),
     "saetta_att_gemm_reserve": (_I, [_P, _Z]),
+    "saetta_att_gemm_invalidate": (_I, [_P]),
+    "saetta_att_gemm_partial_shard": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, FlashParams, _Z, _Z, _Z, _P]),
     "saetta_att_gemm_encode": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, FlashParams, _P]),
     "saetta_att_gemm_partial": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, FlashParams, _Z, _Z, _P]),
     "saetta_prefill_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, FlashParams, _P]),
@@ -632,10 +634,19 @@ class AttGemm:
         _check(lib().saetta_att_gemm_encode(self.h, ptr(q), dtype, ptr(keys), ptr(values), kq, vq, ptr(q_and_gate),
                                             ptr(out), p, _stream(stream)))
 
-    def partial(self, q, keys, values, quant, part, p, key_lo, key_hi, dtype=BF16, stream=None):
+    def partial(self, q, keys, values, quant, part, p, key_lo, key_hi, dtype=BF16, stream=None, key_base=None):
+        """Keys [key_lo, key_hi) only, the result left as (O, m, l) partials.  With key_base the cache handed
+        in holds only this shard's slice of the sequence: its row 0 is the key at global position key_base."""
         kq, vq = (quant[0].h, quant[1].h) if quant else (None, None)
-        _check(lib().saetta_att_gemm_partial(self.h, ptr(q), dtype, ptr(keys), ptr(values), kq, vq, ptr(part), p,
-                                             key_lo, key_hi, _stream(stream)))
+        if key_base is None:
+            _check(lib().saetta_att_gemm_partial(self.h, ptr(q), dtype, ptr(keys), ptr(values), kq, vq, ptr(part), p,
+                                                 key_lo, key_hi, _stream(stream)))
+        else:
+            _check(lib().saetta_att_gemm_partial_shard(self.h, ptr(q), dtype, ptr(keys), ptr(values), kq, vq, ptr(part), p,
+                                                       key_base, key_lo, key_hi, _stream(stream)))
+
+    def invalidate(self):
+        _check(lib().saetta_att_gemm_invalidate(self.h))
 
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:

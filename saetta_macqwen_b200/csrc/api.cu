@@ -6,6 +6,7 @@
 #include <cstring>
 #include <algorithm>
 #include <cmath>
+#include <functional>
 #include <new>
 
 #include <mutex>
@@ -159,7 +160,7 @@ int saetta_quant_rows_encode_dequantize(const saetta_quant_rows *r, void *out_de
     if (tokens > r->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "encode_dequantize: tokens exceeds the capacity");
     if (!aligned16(out_dev)) return fail(SAETTA_ERR_BAD_ARG, "encode_dequantize: out must be 16-byte aligned");
     DeviceGuard guard(r->device);
-    return launch_kv_dequantize(r, out_dev, dtype, tokens, (cudaStream_t)stream);
+    return launch_kv_dequantize(r, out_dev, dtype, 0, tokens, (cudaStream_t)stream);
 }
 
 // Host restatement of the kernels' arithmetic (src/kv_quant.rs:54-105); the
@@ -840,17 +841,47 @@ void saetta_att_gemm_destroy(saetta_att_gemm *op) {
     delete op;
 }
 
+static bool capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+constexpr uint32_t kKeySplits = 2;      // work items a long-context tile's keys are cut into
+constexpr size_t kSplitFromKeys = 16384; // from this many keys on
+
+// AttGemm::new allocates all of its scratch (src/attention_gemm.rs:119-148); here `reserve` does, for
+// caches of up to `tokens` rows: the 16-bit staging copies and the partials of the key splits.
 int saetta_att_gemm_reserve(saetta_att_gemm *op, size_t tokens) {
     if (!op) return fail(SAETTA_ERR_BAD_ARG, "AttGemm: null handle");
-    if (tokens <= op->stage_tokens) return SAETTA_OK;
     DeviceGuard guard(op->device);
+    if (tokens >= kSplitFromKeys) {
+        const size_t need = size_t(kKeySplits) * op->chunk * op->kv_heads * kHeadsPerKv * kPartStride;
+        if (need > op->split_floats) {
+            cudaFree(op->split_parts);
+            op->split_parts = nullptr, op->split_floats = 0;
+            if (int rc = alloc_zero((void **)&op->split_parts, need * sizeof(float))) return rc;
+            op->split_floats = need;
+        }
+    }
+    if (tokens <= op->stage_tokens) return SAETTA_OK;
     tokens = round_up(tokens, 1024);
     cudaFree(op->stage_k), cudaFree(op->stage_v);
     op->stage_k = op->stage_v = nullptr, op->stage_tokens = 0;
+    op->staged[0] = op->staged[1] = saetta_att_gemm::Staged(); // what the old copies held is gone
     const size_t bytes = tokens * op->kv_heads * kDim * 2;
     if (int rc = alloc_zero(&op->stage_k, bytes)) return rc;
     if (int rc = alloc_zero(&op->stage_v, bytes)) return rc;
     op->stage_tokens = tokens;
+    return SAETTA_OK;
+}
+
+int saetta_att_gemm_invalidate(saetta_att_gemm *op) {
+    if (!op) return fail(SAETTA_ERR_BAD_ARG, "AttGemm: null handle");
+    op->staged[0] = op->staged[1] = saetta_att_gemm::Staged();
     return SAETTA_OK;
 }
 
@@ -862,27 +893,62 @@ static int prefill_check(const void *q, int dtype, const saetta_flash_params &p)
     return SAETTA_OK;
 }
 
+// Brings rows [lo, hi) of one side's staging copy (row r of the copy = row r of the cache buffer)
+// up to date.  Rows the copy already holds from the same buffer in the same type are kept when they
+// lie below `fresh_from` (the first row of the chunk being encoded: what lies below it was written
+// before the call that staged it and has not changed since, unless the caller says so with
+// saetta_att_gemm_invalidate); the rest is converted by `convert(first, count)`.
+static int stage_rows(saetta_att_gemm *op, int side, const void *src, int dtype, size_t lo, size_t hi, size_t fresh_from,
+                      cudaStream_t st, const std::function<int(size_t, size_t)> &convert) {
+    if (hi > op->stage_tokens) {
+        if (capturing(st))
+            return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: the staging copy must grow, which a recording cannot do; call saetta_att_gemm_reserve first");
+        if (int rc = saetta_att_gemm_reserve(op, hi)) return rc;
+    }
+    saetta_att_gemm::Staged &s = op->staged[side];
+    size_t from = lo;
+    const bool same = s.src == src && s.dtype == dtype && s.lo <= lo && s.hi >= lo;
+    if (same) from = std::max(lo, std::min(s.hi, fresh_from));
+    if (from < hi)
+        if (int rc = convert(from, hi - from)) return rc;
+    s.src = src, s.dtype = dtype, s.lo = same ? s.lo : lo, s.hi = hi;
+    return SAETTA_OK;
+}
+
+// key_base: global position of row 0 of the cache buffers handed in (0 unless a shard stores only its slice).
 static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const void *keys, const void *values,
                         const saetta_quant_rows *kq, const saetta_quant_rows *vq, const float *q_and_gate, float *out,
-                        float *part, saetta_flash_params p, size_t key_lo, size_t key_hi, cudaStream_t st) {
+                        float *part, saetta_flash_params p, size_t key_base, size_t key_lo, size_t key_hi, cudaStream_t st) {
     if (int rc = prefill_check(q, dtype, p)) return rc;
     if (!p.tokens) return SAETTA_OK;
     if (p.kv_heads != op->kv_heads) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: kv heads differ from the op's");
     DeviceGuard guard(op->device);
     const size_t end = size_t(p.pos) + p.tokens;
     if (key_hi > end) key_hi = end;
+    if (key_base % 64 || key_base > key_lo)
+        return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm: the cache's first row must sit at a multiple of 64 at or below key_lo");
+    if (key_hi <= key_lo) key_hi = key_lo; // an empty shard: every row gets the empty partial
+    // rows of the buffers the kernel reads, and the first row of the chunk itself
+    const size_t lo = key_lo - key_base, hi = key_hi - key_base;
+    const size_t fresh = size_t(p.pos) > key_base ? size_t(p.pos) - key_base : 0;
     int v_dtype = dtype;
     if (kq || vq) {
         if (!kq || !vq || kq->bits != vq->bits) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: quant needs both sides");
-        if (end > kq->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: pos + tokens exceeds the capacity");
+        if (hi > kq->capacity || hi > vq->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: the keys asked for exceed the capacity");
         if (kq->per_token != p.kv_heads * size_t(kGroupsPerHead)) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: quant rows of another shape");
-        if (int rc = saetta_att_gemm_reserve(op, key_hi)) return rc;
-        // The quantised cache is read through a 16-bit copy, as the reference's
-        // kv_stage reads it (src/kv_quant.rs:121-126 semantics).
-        // Keys take q's type; values are staged as binary16 (exactly the reference's
-        // round_trip_as_half), so P is binary16 too and keeps an 11-bit significand.
-        if (int rc = launch_kv_dequantize(kq, op->stage_k, dtype, key_hi, st)) return rc;
-        if (int rc = launch_kv_dequantize(vq, op->stage_v, SAETTA_F16, key_hi, st)) return rc;
+        // The quantised cache is read through a 16-bit copy, as the reference's kv_stage reads it
+        // (src/kv_quant.rs:121-126 semantics).  Keys take q's type; values are staged as binary16
+        // (exactly the reference's round_trip_as_half), so P is binary16 too and keeps an 11-bit
+        // significand.  Only the rows the copy does not hold yet are dequantised: per chunk of a long
+        // prompt, the chunk's own rows.
+        if (int rc = stage_rows(op, 0, kq->data, dtype, lo, hi, fresh, st, [&](size_t first, size_t n) {
+                return launch_kv_dequantize(kq, op->stage_k, dtype, first, n, st);
+            }))
+            return rc;
+        if (int rc = stage_rows(op, 1, vq->data, SAETTA_F16, lo, hi, fresh, st, [&](size_t first, size_t n) {
+                return launch_kv_dequantize(vq, op->stage_v, SAETTA_F16, first, n, st);
+            }))
+            return rc;
         keys = op->stage_k, values = op->stage_v;
         v_dtype = SAETTA_F16;
     }
@@ -890,28 +956,35 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     if (!(kq || vq) && dtype == SAETTA_BF16) {
         // P must share V's type in the second MMA; bfloat16's 8-bit significand would put P's
         // rounding at the tolerance, so bfloat16 values go through a binary16 copy (exact in range).
-        if (int rc = saetta_att_gemm_reserve(op, key_hi)) return rc;
-        if (int rc = launch_bf16_to_f16(values, op->stage_v, key_hi * p.kv_heads * kDim, st)) return rc;
+        const size_t row = p.kv_heads * size_t(kDim);
+        const void *src = values;
+        if (int rc = stage_rows(op, 1, src, SAETTA_F16 + 16 /* converted from bfloat16 */, lo, hi, fresh, st, [&](size_t first, size_t n) {
+                return launch_bf16_to_f16(static_cast<const uint16_t *>(src) + first * row,
+                                          static_cast<uint16_t *>(op->stage_v) + first * row, n * row, st);
+            }))
+            return rc;
         values = op->stage_v;
         v_dtype = SAETTA_F16;
     }
     PrefillArgs a{q, keys, values, dtype, v_dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
                   uint32_t(key_lo), uint32_t(key_hi), p.scale};
+    a.key_base = uint32_t(key_base);
     // Long context: every tile has about the same work, and tiles rarely divide evenly over
     // the SMs.  Cut each tile's keys into two work items (twice as many, half as long) and merge
     // their (m, l, O); the merge is a few tens of microseconds against milliseconds of MMA.
-    constexpr uint32_t kSplits = 2;
-    if (out && key_hi - key_lo >= 16384) {
-        const size_t need = size_t(kSplits) * p.tokens * p.heads * kPartStride;
+    if (out && key_hi - key_lo >= kSplitFromKeys) {
+        const size_t need = size_t(kKeySplits) * p.tokens * p.heads * kPartStride;
         if (need > op->split_floats) {
+            if (capturing(st))
+                return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: the key-split partials must be allocated, which a recording cannot do; call saetta_att_gemm_reserve first");
             cudaFree(op->split_parts);
             op->split_parts = nullptr, op->split_floats = 0;
             if (int rc = alloc_zero((void **)&op->split_parts, need * sizeof(float))) return rc;
             op->split_floats = need;
         }
-        a.out = nullptr, a.part = op->split_parts, a.splits = kSplits;
+        a.out = nullptr, a.part = op->split_parts, a.splits = kKeySplits;
         if (int rc = launch_prefill(a, op->status, st)) return rc;
-        return launch_merge_logical(op->split_parts, kSplits, p.tokens, p.heads, q_and_gate, out, nullptr, st);
+        return launch_merge_logical(op->split_parts, kKeySplits, p.tokens, p.heads, q_and_gate, out, nullptr, st);
     }
     return launch_prefill(a, op->status, st);
 }
@@ -921,7 +994,7 @@ int saetta_att_gemm_encode(saetta_att_gemm *op, const void *q_dev, int dtype, co
                            float *out_dev, saetta_flash_params p, void *stream) {
     if (!op || !q_and_gate_dev || !out_dev) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: null pointer");
     if (p.tokens > op->chunk) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: more tokens than the chunk the op was made for");
-    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, q_and_gate_dev, out_dev, nullptr, p, 0,
+    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, q_and_gate_dev, out_dev, nullptr, p, 0, 0,
                         size_t(p.pos) + p.tokens, (cudaStream_t)stream);
 }
 
@@ -930,8 +1003,18 @@ int saetta_att_gemm_partial(saetta_att_gemm *op, const void *q_dev, int dtype, c
                             saetta_flash_params p, size_t key_lo, size_t key_hi, void *stream) {
     if (!op || !part_dev) return fail(SAETTA_ERR_BAD_ARG, "AttGemm partial: null pointer");
     if (key_lo > key_hi) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm partial: key_lo > key_hi");
-    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, nullptr, nullptr, part_dev, p, key_lo,
+    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, nullptr, nullptr, part_dev, p, 0, key_lo,
                         key_hi, (cudaStream_t)stream);
+}
+
+int saetta_att_gemm_partial_shard(saetta_att_gemm *op, const void *q_dev, int dtype, const void *keys_dev,
+                                  const void *values_dev, const saetta_quant_rows *keys_q,
+                                  const saetta_quant_rows *values_q, float *part_dev, saetta_flash_params p,
+                                  size_t key_base, size_t key_lo, size_t key_hi, void *stream) {
+    if (!op || !part_dev) return fail(SAETTA_ERR_BAD_ARG, "AttGemm partial: null pointer");
+    if (key_lo > key_hi) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm partial: key_lo > key_hi");
+    return att_gemm_run(op, q_dev, dtype, keys_dev, values_dev, keys_q, values_q, nullptr, nullptr, part_dev, p, key_base,
+                        key_lo, key_hi, (cudaStream_t)stream);
 }
 
 int saetta_prefill_encode(int device, const void *q_dev, int dtype, const void *keys_dev, const void *values_dev,

@@ -49,7 +49,7 @@ constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescale = 8.0f;
 constexpr int kPrefetchTiles = 2;
-constexpr int kSmem = 1024 /*align*/ + kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 32;
+constexpr int kSmem = 1024 /*align*/ + kStages * kStageBytes + kWarps * 2 * 16 * 4 + 2 * kStages * 8 + 32; // also what a launch's merge CTAs use
 static_assert(kMergeRoleSmem <= kSmem - 1024, "the merge role fits a CTA's shared memory");
 static_assert(kWarps * 2 * kFragFloats * 4 <= kStages * kStageBytes, "the end-of-range merge parks in the ring");
 
@@ -125,9 +125,7 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     float *ml = reinterpret_cast<float *>(smem + kStages * kStageBytes); // [warp][m of 8 heads, l of 8 heads]
     uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
     uint64_t *empty = full + kStages;
-    uint64_t *ready = empty + kStages;  // the producer has decided what the ring holds (see `skip`)
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(ready + 1);
-    volatile uint32_t *skip = abort_flag + 2; // stages filled before the dependency wait that must be thrown away
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + kStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -135,8 +133,6 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kWarps);
         }
-        mbar_init(ready, 1);
-        *skip = 0;
         abort_flag[0] = 0;
         mbar_fence_init();
     }
@@ -161,28 +157,15 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         }
         __syncwarp();
     };
-    // Before the dependency wait -- while the launch before this one still runs -- the producer fills
-    // the copy ring with the head of this CTA's range and asks for the tiles after those to be brought
-    // into L2.  The launch before may write the rows of the new tokens, positions kv_len - 1 and up,
-    // and nothing below (whatever ran before IT has completed), so the ring takes only tiles that end
-    // below kv_len - 1; after the wait kv_len is read again, and if it is not the value the early
-    // range was made from, the early stages are thrown away (`skip`).
-    uint32_t pre = 0, kv_hint = 0;
-    if (warp == kWarps) {
-        kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
+    // While the launch before this one drains, pull the head of this CTA's range into L2 (the range
+    // comes from a possibly stale kv_len: a hint only, everything is read again after the wait).
+    if (warp == kWarps && lane == 0) {
         uint32_t tb, te, n_hint;
-        range(kv_hint, tb, te, n_hint);
-        const uint32_t safe = kv_hint ? (kv_hint - 1) / kTile : 0; // tiles [0, safe) hold rows below kv_len - 1 only
-        const uint32_t te_safe = min(te, safe);
-        pre = te_safe > tb ? min(te_safe - tb, uint32_t(kStages)) : 0u;
-        for (uint32_t j = 0; j < pre; j++) issue_tile(tb + j, j);
-        if (lane == 0) {
-            const uint32_t t0 = tb + pre;
-            const uint32_t nt = te > t0 ? min(te - t0, uint32_t(kPrefetchTiles)) : 0u;
-            for (uint32_t t = 0; t < nt; t++) {
-                l2_prefetch(a.k + size_t(t0 + t) * kTile * kRowBytes, kTile * kRowBytes);
-                l2_prefetch(a.v + size_t(t0 + t) * kTile * kRowBytes, kTile * kRowBytes);
-            }
+        range(*reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len), tb, te, n_hint);
+        const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
+        for (uint32_t t = 0; t < nt; t++) {
+            l2_prefetch(a.k + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
+            l2_prefetch(a.v + size_t(tb + t) * kTile * kRowBytes, kTile * kRowBytes);
         }
     }
     pdl_wait();              // q, the token parameters and the new rows of the cache may come from the launch before
@@ -202,13 +185,8 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         // (same register pool rule as in decode_quant.cu: 128 x (168 - 40) = 256 x (232 - 168))
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         if (warp != kWarps) return;
-        const bool keep = a.params->kv_len == kv_hint; // then the early range is this range
-        if (lane == 0) {
-            *skip = keep ? 0u : pre;
-            mbar_arrive(ready);
-        }
-        uint32_t it = pre; // ring slots already issued
-        for (uint32_t t = tile_begin + (keep ? pre : 0u); t < tile_end; t++, it++) {
+        uint32_t it = 0;
+        for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
             const uint32_t st = it % kStages, round = it / kStages;
             if (!mbar_wait(&empty[st], (round & 1) ^ 1, abort_flag)) {
                 if (lane == 0) {
@@ -274,21 +252,7 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         Mref[r] = -INFINITY, lsum[r] = 0.f;
     }
 
-    // Start past the early stages, handed back unread, when the producer found them stale.
     uint32_t it = 0;
-    if (!mbar_wait(ready, 0, abort_flag)) {
-        if (lane == 0) {
-            atomicOr(a.status, kStatusFullTimeout);
-            *abort_flag = 1;
-        }
-    } else {
-        it = *skip;
-        for (uint32_t k = 0; k < it; k++) {
-            mbar_wait(&full[k], 0, abort_flag);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[k]);
-        }
-    }
     for (uint32_t t = tile_begin; t < tile_end; t++, it++) {
         const uint32_t st = it % kStages, round = it / kStages;
         if (!mbar_wait(&full[st], round & 1, abort_flag)) {
@@ -441,18 +405,19 @@ decode_half_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 #pragma unroll
     for (int r = 0; r < NR; r++) {
         if (row0 + r >= a.m) continue;
-        float *dst = a.parts + ((size_t(blockIdx.x) * a.m + row0 + r) * kKv + kv) * kPartKv;
+        const PartWriter pw = part_writer(a.parts, a.mo.n_merge != 0, a.n_decode, a.m, row0 + r, kv, blockIdx.x);
         constexpr int per = 64 / NSLOT;
 #pragma unroll
         for (int k = 0; k < per; k++) {
             float v = 0.f;
 #pragma unroll
             for (int sl = 0; sl < NSLOT; sl++) v += ring[((((sl << 1) | kv)) * NR + r) * kFragFloats + (slot * per + k) * 32 + lane];
-            dst[(slot * per + k) * 32 + lane] = v;
+            const int fr = slot * per + k; // fragment register
+            pw.reg(fr)[lane] = v;
         }
         if (slot == 0 && g == 0) {
-            dst[kFragFloats + 2 * i] = Mc[r][0], dst[kFragFloats + 2 * i + 1] = Mc[r][1];
-            dst[kFragFloats + 8 + 2 * i] = lc[r][0], dst[kFragFloats + 8 + 2 * i + 1] = lc[r][1];
+            pw.ml[2 * i] = Mc[r][0], pw.ml[2 * i + 1] = Mc[r][1];
+            pw.ml[8 + 2 * i] = lc[r][0], pw.ml[8 + 2 * i + 1] = lc[r][1];
         }
     }
     // The partial is written: tell the merge CTAs of this launch (the writers meet, then one of

@@ -46,7 +46,8 @@ constexpr int kWarps = 8;     // consumer warps
 constexpr int kThreads = (kWarps + 4) * 32; // two consumer warpgroups + the producer's warpgroup
 constexpr int kKv = 2;        // kv heads covered by one stage
 constexpr float kLog2e = 1.4426950408889634f;
-// Tiles of a CTA's range, beyond those the copy ring takes before the dependency wait, pulled into L2 there.
+// Tiles of a CTA's range pulled into L2 before the dependency wait.  Measured 0 / 4 / 8 / 16: four is best
+// (deeper prefetches queue ahead of the ring's own copies when the wait turns out to be short).
 constexpr int kPrefetchTiles = 4;
 constexpr float kRescale = 8.0f; // move the running maximum when it grows by more than 2^8
 
@@ -70,10 +71,11 @@ constexpr int kMergeBytes = 4 * kQFragBytes;
 static_assert(kMergeBytes >= kKv * kFragFloats * 4, "merge buffers fit");
 template <int BITS>
 constexpr int smem_bytes() {
-    return Stage<BITS>::kStages * Stage<BITS>::kBytes + kMergeBytes + kQAuxBytes + kWarps * 2 * 16 * 4 +
-           2 * Stage<BITS>::kStages * 8 + 32;
+    // (a launch's merge CTAs use the same allocation for their own buffers)
+    return std::max(Stage<BITS>::kStages * Stage<BITS>::kBytes + kMergeBytes + kQAuxBytes + kWarps * 2 * 16 * 4 +
+                        2 * Stage<BITS>::kStages * 8 + 32,
+                    kMergeRoleSmem);
 }
-static_assert(kMergeRoleSmem <= smem_bytes<8>() && kMergeRoleSmem <= smem_bytes<4>(), "the merge role fits a CTA's shared memory");
 
 struct DecodeArgs {
     Segment seg;               // the one segment of a single-sequence launch (tiles filled on device)
@@ -119,9 +121,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
     float *ml = qsums + kQAuxBytes / 4; // [warp][row of the warp][m of 8 heads, l of 8 heads]
     uint64_t *full = reinterpret_cast<uint64_t *>(ml + kWarps * 2 * 16);
     uint64_t *empty = full + NS;
-    uint64_t *ready = empty + NS;       // the producer has decided what the ring holds (see `skip`)
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(ready + 1);
-    volatile uint32_t *skip = abort_flag + 2; // stages filled before the dependency wait that must be thrown away
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(empty + NS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -129,8 +129,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kWarps);
         }
-        mbar_init(ready, 1);
-        *skip = 0;
         abort_flag[0] = 0;
         abort_flag[1] = 0; // a word that stays 0, for waits that must ignore the abort flag
         mbar_fence_init();
@@ -156,39 +154,29 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         bulk_g2s(dst + St::kVz, (const uint8_t *)s.vz + tok * St::kParamRow, St::kParams, &full[st]);
     };
 
-    // Before the dependency wait -- while the launch before this one (the layer before's merge, or
-    // this token's attention prep) still runs -- the producer already fills the copy ring with the
-    // head of this CTA's range, and asks for the tiles after those to be brought into L2.  What may
-    // be read this early: the launch before may write the rows of the new tokens, positions
-    // kv_len - 1 and up, and nothing below (the launches before IT have completed: it passed its own
-    // wait before it let this one start).  So the ring takes only tiles that end below kv_len - 1,
-    // and after the wait the producer reads kv_len again: if it is not the value the early range was
-    // made from, the early stages are thrown away (`skip`) and the range starts over.  The L2
-    // requests are hints and may cover any row.
-    uint32_t pre = 0, kv_hint = 0;
-    if (warp == kWarps && !a.segs) {
-        kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
+    // While the launch before this one drains, pull the head of this CTA's tile range into L2 (and warm
+    // the TLB).  The range comes from a possibly stale kv_len: it is only a hint, every value is read
+    // again after the wait; L2 is the point of coherence, so lines brought in early still show what
+    // the launch before writes afterwards.  (Filling the copy ring itself this early, or right after
+    // the wait from the early kv_len, was measured and lost: in a chain of layers the copies compete
+    // with the merge CTAs of the layer before, and the query conversion after the wait covers the
+    // first tile's latency anyway.)
+    if (warp == kWarps && lane == 0 && !a.segs) {
+        const uint32_t kv_hint = *reinterpret_cast<const volatile uint32_t *>(&a.params->kv_len);
         uint32_t tb, te;
         tile_range(kv_hint, tb, te);
-        const uint32_t safe = kv_hint ? (kv_hint - 1) / kTile : 0; // tiles [0, safe) hold rows below kv_len - 1 only
-        const uint32_t te_safe = min(te, safe);
-        pre = te_safe > tb ? min(te_safe - tb, uint32_t(NS)) : 0u;
-        if (lane == 0) {
-            for (uint32_t j = 0; j < pre; j++) issue_tile(a.seg, tb + j, j);
-            const uint32_t t0 = tb + pre;
-            const uint32_t nt = te > t0 ? min(te - t0, uint32_t(kPrefetchTiles)) : 0u;
-            const size_t tok = size_t(t0) * kTile;
-            for (uint32_t t = 0; t < nt; t += 2) { // two tiles (32 KB of 8-bit codes) per request
-                const uint32_t n = min(nt - t, 2u);
-                l2_prefetch((const uint8_t *)a.seg.k + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
-                l2_prefetch((const uint8_t *)a.seg.v + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
-            }
-            if (nt) {
-                l2_prefetch((const uint8_t *)a.seg.ks + tok * St::kParamRow, nt * St::kParams);
-                l2_prefetch((const uint8_t *)a.seg.kz + tok * St::kParamRow, nt * St::kParams);
-                l2_prefetch((const uint8_t *)a.seg.vs + tok * St::kParamRow, nt * St::kParams);
-                l2_prefetch((const uint8_t *)a.seg.vz + tok * St::kParamRow, nt * St::kParams);
-            }
+        const uint32_t nt = min(te - tb, uint32_t(kPrefetchTiles));
+        const size_t tok = size_t(tb) * kTile;
+        for (uint32_t t = 0; t < nt; t += 2) { // two tiles (32 KB of 8-bit codes) per request
+            const uint32_t n = min(nt - t, 2u);
+            l2_prefetch((const uint8_t *)a.seg.k + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
+            l2_prefetch((const uint8_t *)a.seg.v + (tok + t * kTile) * St::kCodeRow, n * St::kCodes);
+        }
+        if (nt) {
+            l2_prefetch((const uint8_t *)a.seg.ks + tok * St::kParamRow, nt * St::kParams);
+            l2_prefetch((const uint8_t *)a.seg.kz + tok * St::kParamRow, nt * St::kParams);
+            l2_prefetch((const uint8_t *)a.seg.vs + tok * St::kParamRow, nt * St::kParams);
+            l2_prefetch((const uint8_t *)a.seg.vz + tok * St::kParamRow, nt * St::kParams);
         }
     }
     pdl_wait();              // q, the token parameters and the new rows of the cache may come from the launch before
@@ -215,20 +203,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 
     auto producer_role = [&]() {
         // ---------------------------------------------------------------- producer
-        uint32_t it = pre; // ring slots already issued
+        uint32_t it = 0;
         bool ok = true;
         for (uint32_t si = seg_lo; si < seg_hi && ok; si++) {
             const Segment s = load_segment(si);
-            uint32_t t = s.tile_begin;
-            if (si == seg_lo) {
-                const bool keep = s.kv_len == kv_hint; // then the early range is this range
-                if (keep) t += pre;
-                if (lane == 0) {
-                    *skip = keep ? 0u : pre;
-                    mbar_arrive(ready);
-                }
-            }
-            for (; t < s.tile_end; t++, it++) {
+            for (uint32_t t = s.tile_begin; t < s.tile_end; t++, it++) {
                 const uint32_t st = it % NS, round = it / NS;
                 if (!mbar_wait(&empty[st], (round & 1) ^ 1, abort_flag)) {
                     if (lane == 0) {
@@ -248,25 +227,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
         for (uint32_t k = issued > NS ? issued - NS : 0; k < issued; k++)
             mbar_wait(&full[k % NS], (k / NS) & 1, abort_flag, 2000000u);
     };
-    // Consumers: the ring position to start from -- past the early stages, handed back unread, when
-    // the producer found them stale.
-    auto consumer_start = [&]() -> uint32_t {
-        if (!mbar_wait(ready, 0, abort_flag)) {
-            if (lane == 0) {
-                atomicOr(a.status, kStatusFullTimeout);
-                *abort_flag = 1;
-            }
-            return 0;
-        }
-        const uint32_t n = *skip;
-        for (uint32_t k = 0; k < n; k++) {
-            mbar_wait(&full[k], 0, abort_flag);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[k]);
-        }
-        return n;
-    };
-
     // Registers move from the producer's warpgroup (only one of its warps works, and it needs
     // few) to the two consumer warpgroups, whose accumulators and query fragments would
     // otherwise spill inside the inner loop.  What the consumers gain must be what the producers
@@ -315,7 +275,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
                     for (int c = 0; c < 4; c++) qraw[G][c] = *reinterpret_cast<const float4 *>(qp + G * 64 + i * 16 + c * 4);
             }
-            if (si == seg_lo) it = consumer_start();
             const Segment s = load_segment(si);
             const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
 
@@ -592,16 +551,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     O[4 * G + e][2] += b0, O[4 * G + e][3] += b1;
                 }
             }
-            float *dst = a.parts + ((size_t(s.part) * a.m + row) * kKv + kv) * kPartKv;
+            // where this part's fragment register r (32 lanes) and its maxima and sums go
+            const PartWriter pw = part_writer(a.parts, a.mo.n_merge != 0, a.n_decode, a.m, row_live ? row : 0, kv, s.part);
+            auto dst_reg = [&](int r) { return pw.reg(r) + lane; };
             if (NSLOT == 1) {
                 if (row_live) {
 #pragma unroll
                     for (int e = 0; e < 16; e++)
 #pragma unroll
-                        for (int c = 0; c < 4; c++) dst[(4 * e + c) * 32 + lane] = O[e][c];
+                        for (int c = 0; c < 4; c++) *dst_reg(4 * e + c) = O[e][c];
                     if (g == 0) {
-                        dst[kFragFloats + 2 * i] = Mc2[0], dst[kFragFloats + 2 * i + 1] = Mc2[1];
-                        dst[kFragFloats + 8 + 2 * i] = l[0], dst[kFragFloats + 8 + 2 * i + 1] = l[1];
+                        pw.ml[2 * i] = Mc2[0], pw.ml[2 * i + 1] = Mc2[1];
+                        pw.ml[8 + 2 * i] = l[0], pw.ml[8 + 2 * i + 1] = l[1];
                     }
                 }
             } else {
@@ -648,11 +609,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                                 const int w = ((sl * ROWS + row_in_pass) << 1) | kv;
                                 v += reinterpret_cast<const float *>(stages)[w * kFragFloats + (slot * per + r) * 32 + lane];
                             }
-                            dst[(slot * per + r) * 32 + lane] = v;
+                            *dst_reg(slot * per + r) = v;
                         }
                         if (slot == 0 && g == 0) {
-                            dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
-                            dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+                            pw.ml[2 * i] = Mc[0], pw.ml[2 * i + 1] = Mc[1];
+                            pw.ml[8 + 2 * i] = lc[0], pw.ml[8 + 2 * i + 1] = lc[1];
                         }
                     }
                 } else {
@@ -674,10 +635,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                 if (row_live) {
                     constexpr int per = 64 / NSLOT;
 #pragma unroll
-                    for (int r = 0; r < per; r++) dst[(slot * per + r) * 32 + lane] = buf[(slot * per + r) * 32 + lane];
+                    for (int r = 0; r < per; r++) *dst_reg(slot * per + r) = buf[(slot * per + r) * 32 + lane];
                     if (slot == 0 && g == 0) {
-                        dst[kFragFloats + 2 * i] = Mc[0], dst[kFragFloats + 2 * i + 1] = Mc[1];
-                        dst[kFragFloats + 8 + 2 * i] = lc[0], dst[kFragFloats + 8 + 2 * i + 1] = lc[1];
+                        pw.ml[2 * i] = Mc[0], pw.ml[2 * i + 1] = Mc[1];
+                        pw.ml[8 + 2 * i] = lc[0], pw.ml[8 + 2 * i + 1] = lc[1];
                     }
                 }
                 }
@@ -805,7 +766,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
             for (int r = 0; r < NR; r++) Mref[r] = -INFINITY, lsum[r] = 0.f;
 
-            if (si == seg_lo) it = consumer_start();
             for (uint32_t t = s.tile_begin; alive && t < s.tile_end; t++, it++) {
                 const uint32_t st = it % NS, round = it / NS;
                 if (!mbar_wait(&full[st], round & 1, abort_flag)) {
@@ -1091,7 +1051,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
 #pragma unroll
             for (int r = 0; r < NR; r++) {
                 if (rowA + r >= a.m) continue;
-                float *dst = a.parts + ((size_t(s.part) * a.m + rowA + r) * kKv + kv) * kPartKv;
+                const PartWriter pw = part_writer(a.parts, a.mo.n_merge != 0, a.n_decode, a.m, rowA + r, kv, s.part);
                 constexpr int per = 64 / NSLOT;
 #pragma unroll
                 for (int k = 0; k < per; k++) {
@@ -1101,9 +1061,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                         const int w = ((sl * NP + pair) << 1) | kv;
                         v += ring[(w * NR + r) * kFragFloats + (slot * per + k) * 32 + lane];
                     }
-                    dst[(slot * per + k) * 32 + lane] = v;
+                    const int fr = slot * per + k; // fragment register
+                    pw.reg(fr)[lane] = v;
                 }
-                if (slot == 0 && i == 0) dst[kFragFloats + g] = Mc[r], dst[kFragFloats + 8 + g] = lc[r];
+                if (slot == 0 && i == 0) pw.ml[g] = Mc[r], pw.ml[8 + g] = lc[r];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); // ring, merge buffer and query fragments free again
         }

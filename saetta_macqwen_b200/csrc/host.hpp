@@ -74,8 +74,16 @@ struct saetta_decode_batch {
 struct saetta_att_gemm {
     int device = 0;
     size_t chunk = 0, kv_heads = 0;
-    void *stage_k = nullptr, *stage_v = nullptr; // 16-bit copy of a quantised cache
-    size_t stage_tokens = 0;
+    // 16-bit copy of the cache rows the tensor-core kernel reads when the cache itself is quantised (keys
+    // and values) or bfloat16 (values only).  It persists across calls: rows below the chunk being
+    // encoded that an earlier call already converted are not converted again.
+    void *stage_k = nullptr, *stage_v = nullptr;
+    size_t stage_tokens = 0; // rows each copy has room for
+    struct Staged {
+        const void *src = nullptr; // the buffer the rows came from (identity of the cache side)
+        int dtype = 0;
+        size_t lo = 0, hi = 0;     // rows [lo, hi) of the copy are valid
+    } staged[2];
     float *split_parts = nullptr; // partials of the key splits of a long-context chunk
     size_t split_floats = 0;
     uint32_t *status = nullptr;
@@ -131,7 +139,7 @@ using QuantRows = saetta_quant_rows;
 int launch_kv_quantize(int bits, uint32_t per_token, const float *x0, const QuantRows *r0,
                        const float *x1, const QuantRows *r1, size_t rows, size_t pos,
                        const saetta_token_params *params, cudaStream_t stream);
-int launch_kv_dequantize(const QuantRows *rows, void *out, int dtype, size_t tokens,
+int launch_kv_dequantize(const QuantRows *rows, void *out, int dtype, size_t first, size_t tokens,
                          cudaStream_t stream);
 int launch_bf16_to_f16(const void *in, void *out, size_t values, cudaStream_t stream);
 int launch_kv_store_plain(int mode, const float *k, const float *v, void *keys, void *values,
@@ -214,10 +222,12 @@ struct PrefillArgs {
     float *out;          // [tokens][heads][256] or null
     float *part;         // [tokens][heads][kPartStride] or null
     uint32_t heads, kv_heads, pos, tokens;
-    uint32_t key_lo, key_hi; // keys considered (clipped by causality)
+    uint32_t key_lo, key_hi; // keys considered (clipped by causality), global positions
     float scale;
     uint32_t splits = 1;     // > 1: each tile's keys are cut into `splits` work items, each leaving a
                              // partial in part + split * tokens*heads*kPartStride (out must be null)
+    uint32_t key_base = 0;   // global position of row 0 of k and v (a multiple of 64, <= key_lo): a shard
+                             // that stores only its own slice of the sequence
 };
 int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream);
 int prefill_configure(int device);

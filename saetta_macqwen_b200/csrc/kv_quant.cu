@@ -118,13 +118,16 @@ kv_dequantize_kernel(const uint32_t *__restrict__ data, const __half *__restrict
     out[o] = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
-int launch_kv_dequantize(const QuantRows *rows, void *out, int dtype, size_t tokens,
+// Rows [first, first + tokens) of `rows` as 16-bit values into the same rows of out ([row][values]).
+int launch_kv_dequantize(const QuantRows *rows, void *out, int dtype, size_t first, size_t tokens,
                          cudaStream_t stream) {
     const size_t octets = tokens * rows->per_token * 8;
     if (!octets) return SAETTA_OK;
     const unsigned grid = unsigned((octets + 255) / 256);
-    auto d = (const uint32_t *)rows->data;
-    auto s = (const __half *)rows->scales, z = (const __half *)rows->biases;
+    const size_t g0 = first * rows->per_token; // first group
+    auto d = (const uint32_t *)rows->data + g0 * 2 * size_t(rows->bits);
+    auto s = (const __half *)rows->scales + g0, z = (const __half *)rows->biases + g0;
+    out = static_cast<uint4 *>(out) + g0 * 8;
     if (rows->bits == 8 && dtype == SAETTA_F16)
         kv_dequantize_kernel<8, false><<<grid, 256, 0, stream>>>(d, s, z, (uint4 *)out, octets);
     else if (rows->bits == 8)

@@ -74,6 +74,7 @@ struct PfParams {
     uint32_t v_fmt; // of V, and therefore of P (both operands of one MMA must share a format)
     uint32_t splits;      // each tile's key range is cut into this many work items (>1: partials per split)
     uint32_t part_stride; // floats between the partial buffers of consecutive splits
+    uint32_t key_base;    // global position of row 0 of the K / V buffers
 };
 
 // ----------------------------------------------------------------- PTX wrappers
@@ -179,16 +180,6 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes
     return d;
 }
 
-#ifdef SAETTA_PF_TRACE
-// Cycle accounting per CTA and role for tuning builds only (never in the shipped library).
-__device__ unsigned long long pf_trace[160][16];
-#define PF_T0() const long long t0_ = clock64()
-#define PF_ADD(slot) if (lane == 0) pf_trace[blockIdx.x][slot] += (unsigned long long)(clock64() - t0_)
-#else
-#define PF_T0()
-#define PF_ADD(slot)
-#endif
-
 struct PfTile {
     uint32_t tok0, kv, b_begin, nb, split;
 };
@@ -274,7 +265,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 if (!t.nb) continue;
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
                     const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1;
-                    const int key0 = int((t.b_begin + b) * kBN);
+                    const int key0 = int((t.b_begin + b) * kBN) - int(p.key_base); // row of the buffer
                     if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
                     mbar_expect_tx(&k_full[st], kKBytes);
                     for (int c = 0; c < 4; c++) tma_load_3d(sK + st * kKBytes + c * kKChunk, &map_k, &k_full[st], c * 64, int(t.kv), key0);
@@ -306,11 +297,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             PfTile t;
             for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
                 if (!t.nb) continue;
-                { PF_T0(); if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; } PF_ADD(12); }
+                if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; }
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
                     const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1, sb = g & 1;
-                    { PF_T0(); if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } PF_ADD(0); }
-                    { PF_T0(); if (!mbar_wait(&pv_done[sb], ((g >> 1) & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(1); }
+                    if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                    if (!mbar_wait(&pv_done[sb], ((g >> 1) & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
                     const uint64_t bd0 = umma_desc(k_addr + st * kKBytes, 16, 1024);
 #pragma unroll
@@ -340,9 +331,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 if (!t.nb) continue;
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
                     const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1, sb = g & 1, sph = (g >> 1) & 1;
-                    { PF_T0(); if (!mbar_wait(&p_full[sb], sph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(2); }
-                    { PF_T0(); if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } PF_ADD(3); }
-                    { PF_T0(); if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; } PF_ADD(13); }
+                    if (!mbar_wait(&p_full[sb], sph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                    if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
                     // V is MN-major: 64 dims (128 B) x 8 keys per swizzle atom; next 64 dims one slab on
                     // (leading offset), next 8 keys 1024 B on (stride offset); 16 keys per MMA.
@@ -374,14 +365,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             for (uint32_t b = 0; ok && b < t.nb; b++, g++) {
                 const uint32_t st = g & 1, ph = (g >> 1) & 1;
                 const uint32_t key0 = (t.b_begin + b) * kBN;
-                { PF_T0(); if (!mbar_wait(&s_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; } if (quarter == 0) { PF_ADD(4); } }
+                if (!mbar_wait(&s_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
                 tc_fence_after();
                 uint32_t sr[2][32];
-                PF_T0();
                 tmem_ld32(tmem_s + lane_addr + st * kBN, sr[0]);
                 tmem_ld32(tmem_s + lane_addr + st * kBN + 32, sr[1]);
                 tmem_wait_ld();
-                if (quarter == 0) { PF_ADD(5); }
 
                 // raw scores; the positive scale (in log2 units) is folded into the exponent's FFMA
                 float s[64];
@@ -423,8 +412,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     tc_fence_before();
                 }
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                if (quarter == 0) { PF_ADD(6); } // from the first tmem load to here: S read + max + any rescale
-                if (quarter == 0) { PF_ADD(7); }
                 // P over the first 32 columns of the S buffer it came from (two values per column)
                 uint32_t pw[32];
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -447,7 +434,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&p_full[st]);
-                if (quarter == 0) { PF_ADD(8); }
             }
             if (!ok) break;
             // hand the row's sum and maximum to the tile I/O warps and go on to the next tile
@@ -511,7 +497,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             uint4 qv[16];
 #pragma unroll
             for (int j = 0; j < 16; j++) qv[j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
-            PF_T0();
             if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             tc_fence_after();
 #pragma unroll
@@ -528,7 +513,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full);
-            if (quarter == 0 && !half) { PF_ADD(11); }
             return true;
         };
         auto epilogue = [&](const PfTile &t, uint32_t k) -> bool {
@@ -542,11 +526,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             // (256-bit loads and stores: a thread's accesses are whole 32-byte sectors of its row)
             const bool gated = row_live && p.out;
             const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim + half * 128 : 0);
-            PF_T0();
             if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             const float l = row_l[(k & 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
             if (!mbar_wait(o_final, k & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
-            if (quarter == 0 && !half) { PF_ADD(9); }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
             uint32_t o[4][32];
@@ -583,7 +565,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 part[rh * kPartStride + kPartM] = m_ref;
                 part[rh * kPartStride + kPartL] = l;
             }
-            if (quarter == 0 && !half) { PF_ADD(10); }
             return true;
         };
         uint32_t round = 0, k = 0;
@@ -635,7 +616,9 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
         return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q, keys and values must be 16-byte aligned");
     const CUtensorMapDataType dt = a.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap mk, mv;
-    const cuuint64_t keys_total = cuuint64_t(a.pos) + a.tokens;
+    if (a.key_base % kBN || a.key_base > a.key_lo) return fail(SAETTA_ERR_BAD_SHAPE, "prefill attention: the cache's first row must sit at a multiple of 64 at or below the first key");
+    // rows of the buffers the kernel may touch: up to the last key it is asked for (copies past that read zeros)
+    const cuuint64_t keys_total = std::max<cuuint64_t>(1, std::min<cuuint64_t>(cuuint64_t(a.pos) + a.tokens, a.key_hi) - std::min<cuuint64_t>(a.key_base, a.key_hi));
     const CUtensorMapDataType dtv = a.v_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     for (int side = 0; side < 2; side++) {
         const cuuint64_t dims[3] = {cuuint64_t(kDim), a.kv_heads, keys_total};
@@ -648,7 +631,7 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
     }
     PfParams p{a.q, a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
                a.scale * kLog2ePf, a.dtype == SAETTA_BF16 ? 1u : 0u, a.v_dtype == SAETTA_BF16 ? 1u : 0u,
-               a.splits ? a.splits : 1u, uint32_t(size_t(a.tokens) * a.heads * kPartStride)};
+               a.splits ? a.splits : 1u, uint32_t(size_t(a.tokens) * a.heads * kPartStride), a.key_base};
     int dev = 0;
     SAETTA_CUDA(cudaGetDevice(&dev));
     const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads * (a.splits ? a.splits : 1u);
@@ -660,13 +643,3 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
 
 } // namespace saetta
 
-#ifdef SAETTA_PF_TRACE
-extern "C" int saetta_debug_prefill_trace(unsigned long long *out, int reset) {
-    if (out) cudaMemcpyFromSymbol(out, saetta::pf_trace, sizeof(saetta::pf_trace));
-    if (reset) {
-        static unsigned long long zero[160][16];
-        cudaMemcpyToSymbol(saetta::pf_trace, zero, sizeof(zero));
-    }
-    return 0;
-}
-#endif

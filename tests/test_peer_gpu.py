@@ -201,12 +201,16 @@ def _rank_prefill(rank, world, port, out_q):
     group = sa.PeerGroup(rank, rank, world, tokens, HEADS, gather)
     op = sa.AttGemm(rank, 4096, KV)
     p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
-    cuts = [total * r // world for r in range(world + 1)]  # this rank's keys: [cuts[rank], cuts[rank + 1])
+    # this rank's keys: [cuts[rank], cuts[rank + 1]), cut at multiples of 64; it STORES only those rows
+    # (row 0 of its buffers is the key at global position cuts[rank])
+    cuts = [min(total, (total * r // world + 63) // 64 * 64) for r in range(world)] + [total]
+    lo_k, hi_k = cuts[rank], cuts[rank + 1]
+    mine_k, mine_v = to_bf16(k[lo_k * ROW:hi_k * ROW]), to_bf16(v[lo_k * ROW:hi_k * ROW])
     out = torch.zeros(tokens * HEADS * DIM, device="cuda")
     gd = torch.from_numpy(qg).cuda()
     for _ in range(3):
         out.zero_()
-        op.partial(to_bf16(q), to_bf16(k), to_bf16(v), None, group.staging, p, cuts[rank], cuts[rank + 1], dtype=sa.BF16)
+        op.partial(to_bf16(q), mine_k, mine_v, None, group.staging, p, lo_k, hi_k, dtype=sa.BF16, key_base=lo_k)
         group.merge_sliced(tokens, gd, out)
         torch.cuda.synchronize()
         assert group.status() == 0

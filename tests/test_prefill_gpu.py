@@ -217,3 +217,103 @@ def test_config4_long_context_chunk_over_8bit_prefix(oracle):
                                      rng.integers(0, tokens, 50)]))
     assert len(rows) >= 64
     print("config 4:", len(rows), "rows", check_rows(oracle, got, q, qg, kr.ravel(), vr.ravel(), pos, rows))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_chunks_of_a_prompt_convert_only_their_own_rows(oracle, bits):
+    """A prompt prefilled in chunks over a quantised cache: after `reserve` no encode allocates, every chunk
+    matches the oracle (so the rows an earlier chunk staged are still right), the same calls record into a
+    Plan, and rows rewritten below the next chunk are picked up after `invalidate`."""
+    import torch
+
+    chunks = [(0, 200), (200, 120), (320, 64)]
+    total = 384
+    q, k, v, qg = bf16_inputs(oracle, 0, total, 700)
+    cache = sa.GpuKvCache(0, bits, total)
+    op = sa.AttGemm(0, 4096, KV)
+    op.reserve(total)
+    kr = oracle.round_trip_as_half(k, bits, bf16=True)
+    vr = oracle.round_trip_as_half(v, bits)
+    kd, vd = dev(k), dev(v)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for pos, n in chunks:
+        cache.store_at(kd[pos * ROW:(pos + n) * ROW], vd[pos * ROW:(pos + n) * ROW], pos, n)  # src/prefill.rs:1656-1666
+        sl = slice(pos * HEADS * DIM, (pos + n) * HEADS * DIM)
+        gl = slice(pos * HEADS * 2 * DIM, (pos + n) * HEADS * 2 * DIM)
+        got = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=op)
+        check_rows(oracle, got, q[sl], qg[gl], kr, vr, pos, np.arange(n))
+    # nothing was allocated by the library on the way (the test's own tensors come from torch's pool)
+    assert torch.cuda.mem_get_info()[0] >= free0 - (8 << 20)
+
+    # the last chunk again, recorded: an encode that has its scratch is capturable
+    pos, n = chunks[-1]
+    sl = slice(pos * HEADS * DIM, (pos + n) * HEADS * DIM)
+    gl = slice(pos * HEADS * 2 * DIM, (pos + n) * HEADS * 2 * DIM)
+    out = torch.zeros(n * HEADS * DIM, device="cuda")
+    qd, gd = to16(torch, q[sl], sa.BF16), dev(qg[gl])
+    plan = sa.Plan(0)
+    with plan.recording():
+        op.encode(qd, None, None, cache.quant(), gd, out, sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16,
+                  stream=plan.stream)
+    plan.run()
+    check_rows(oracle, out.cpu().numpy().reshape(n, HEADS, DIM), q[sl], qg[gl], kr, vr, pos, np.arange(n))
+    # an op without its scratch refuses to grow it inside a recording
+    bare = sa.AttGemm(0, 4096, KV)
+    plan2 = sa.Plan(0)
+    with pytest.raises(sa.SaettaError) as e:
+        with plan2.recording():
+            bare.encode(qd, None, None, cache.quant(), gd, out, sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16,
+                        stream=plan2.stream)
+    assert "reserve" in str(e.value)
+
+    # rows below the chunk rewritten behind the op's back: told so, it converts them again
+    k2 = k.copy()
+    k2[:100 * ROW] = oracle.round_bf16(oracle.normal(100 * ROW, 701))
+    cache.store_at(dev(k2[:100 * ROW]), vd[:100 * ROW], 0, 100)
+    op.invalidate()
+    got = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=op)
+    check_rows(oracle, got, q[sl], qg[gl], oracle.round_trip_as_half(k2, bits, bf16=True), vr, pos, np.arange(n))
+
+
+@pytest.mark.parametrize("quant_bits", [None, 8])
+def test_shards_that_store_only_their_slice(oracle, quant_bits):
+    """Split-KV prefill where every shard STORES only its own keys: row 0 of shard r's cache is the key at
+    global position cuts[r].  The shards' partials merge to the oracle's result over the whole sequence."""
+    import torch
+
+    pos, tokens = 500, 150
+    total = pos + tokens
+    q, k, v, qg = bf16_inputs(oracle, pos, tokens, 800)
+    cuts = [0, 192, 512, total]  # multiples of 64; the last shard holds part of the chunk itself
+    p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
+    parts = torch.zeros((len(cuts) - 1, tokens * HEADS * sa.PART_STRIDE), dtype=torch.float32, device="cuda")
+    qd = to16(torch, q, sa.BF16)
+    keep = []
+    for r in range(len(cuts) - 1):
+        lo, hi = cuts[r], cuts[r + 1]
+        op = sa.AttGemm(0, 4096, KV)
+        if quant_bits:
+            c = sa.GpuKvCache(0, quant_bits, hi - lo)
+            c.store_at(dev(k[lo * ROW:hi * ROW]), dev(v[lo * ROW:hi * ROW]), 0, hi - lo)
+            op.partial(qd, None, None, c.quant(), parts[r], p, lo, hi, dtype=sa.BF16, key_base=lo)
+            keep.append(c)
+        else:
+            kd, vd = to16(torch, k[lo * ROW:hi * ROW], sa.BF16), to16(torch, v[lo * ROW:hi * ROW], sa.BF16)
+            op.partial(qd, kd, vd, None, parts[r], p, lo, hi, dtype=sa.BF16, key_base=lo)
+            keep.append((kd, vd))
+        keep.append(op)
+    out = torch.zeros(tokens * HEADS * DIM, dtype=torch.float32, device="cuda")
+    sa.merge_partials(0, parts, len(cuts) - 1, tokens, HEADS, dev(qg), out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
+    if quant_bits:
+        kr, vr = oracle.round_trip_as_half(k, quant_bits, bf16=True), oracle.round_trip_as_half(v, quant_bits)
+    else:
+        kr, vr = k, v
+    check_rows(oracle, got, q, qg, kr, vr, pos, np.arange(tokens))
+    # a cache whose first row is not at a multiple of 64 is refused
+    with pytest.raises(sa.SaettaError) as e:
+        op.partial(qd, kd if not quant_bits else None, vd if not quant_bits else None, c.quant() if quant_bits else None,
+                   parts[0], p, 100, 200, dtype=sa.BF16, key_base=100)
+    assert e.value.code == sa.BAD_SHAPE
