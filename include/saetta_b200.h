@@ -380,6 +380,14 @@ int saetta_decode_publish_cache(saetta_decode *op, size_t m, const float *q_dev,
                                 const saetta_kv_cache *cache, saetta_peer_group *group,
                                 uint32_t row_step, const saetta_token_params *params_dev,
                                 void *stream);
+/* saetta_decode_publish_cache and saetta_peer_collect as ONE launch: the merge CTAs of the decode
+ * launch store this rank's partial into the peers' mailboxes and then wait, in the same kernel, for
+ * the peers' partials of the same exchange, merge over the ranks and gate -- no second launch and no
+ * kernel boundary between the two.  Same bounded wait and status word as saetta_peer_collect. */
+int saetta_decode_exchange_cache(saetta_decode *op, size_t m, const float *q_dev,
+                                 const saetta_kv_cache *cache, saetta_peer_group *group,
+                                 uint32_t row_step, const float *q_and_gate_dev, float *out_dev,
+                                 const saetta_token_params *params_dev, void *stream);
 int saetta_peer_group_status(saetta_peer_group *g, void *stream, uint32_t *status);
 
 /* ------------------------------------------------------------------ prefill

@@ -144,6 +144,7 @@ SYMBOLS = {
     "saetta_peer_slice": (_I, [_P, _Z, C.POINTER(_Z), C.POINTER(_Z)]),
     "saetta_decode_batch_publish": (_I, [_P, _Z, _P, _P, _P, _P, _P]),
     "saetta_decode_publish_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P]),
+    "saetta_decode_exchange_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P, _P, _P]),
     "saetta_peer_group_status": (_I, [_P, _P, C.POINTER(_U32)]),
     "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
     "saetta_att_gemm_destroy": (None, [_P]),
@@ -353,6 +354,11 @@ class AttentionRows:
         """partial_cache with the partial stored straight into every peer's mailbox."""
         _check(lib().saetta_decode_publish_cache(self.h, m, ptr(q), cache.h, group.h, row_step, ptr(params),
                                                  _stream(stream)))
+
+    def exchange_cache(self, m, q, cache, group, q_and_gate, out, params, row_step=1, stream=None):
+        """publish_cache and the group's collect in one launch: the gated result over every rank's shard."""
+        _check(lib().saetta_decode_exchange_cache(self.h, m, ptr(q), cache.h, group.h, row_step, ptr(q_and_gate), ptr(out),
+                                                  ptr(params), _stream(stream)))
 
     def device_status(self, stream=None):
         s = C.c_uint32()

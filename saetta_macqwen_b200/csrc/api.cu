@@ -557,7 +557,7 @@ static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView 
         if (kv.kv_heads != 2) return fail(SAETTA_ERR_UNSUPPORTED, "quantised decode attention is built for 2 kv heads");
         MergeOut mo;
         mo.q_and_gate = q_and_gate, mo.out = out, mo.part_out = part_out;
-        if (group) mo.push = group->push;
+        if (group) mo.push = group->push; // with `out` too: the launch publishes AND collects
         // binary16 (the reference's own cache format) or bfloat16 rows run the same shape of kernel
         // without the dequantisation
         return tensor_quant ? launch_decode_quant(kv, q, op->parts, op->status, uint32_t(m), row_step, op->splits,
@@ -567,9 +567,13 @@ static int decode_run(saetta_decode *op, size_t m, const float *q, const KvView 
     }
     if (int rc = launch_decode_exact(kv, q, op->parts, uint32_t(m), row_step, op->splits, uint32_t(kv_capacity), params, st))
         return rc;
-    if (int rc = launch_merge_logical(op->parts, uint32_t(op->splits), uint32_t(m), heads, q_and_gate, out, part_out, st))
+    if (!group) return launch_merge_logical(op->parts, uint32_t(op->splits), uint32_t(m), heads, q_and_gate, out, part_out, st);
+    // across GPUs: the merged partial into the group's staging buffer, published from there; collected
+    // by a launch of its own when the caller asked for the result
+    if (int rc = launch_merge_logical(op->parts, uint32_t(op->splits), uint32_t(m), heads, nullptr, nullptr, group->staging, st))
         return rc;
-    return group ? launch_peer_publish(group, m, st) : SAETTA_OK; // part_out is the group's staging buffer
+    if (int rc = launch_peer_publish(group, m, st)) return rc;
+    return out ? saetta_peer_collect(group, m, q_and_gate, out, st) : SAETTA_OK;
 }
 
 int saetta_decode_record(saetta_decode *op, size_t m, const float *q_dev, const void *keys_dev, const void *values_dev,
@@ -657,6 +661,20 @@ int saetta_decode_publish_cache(saetta_decode *op, size_t m, const float *q_dev,
     if (group->device != op->device) return fail(SAETTA_ERR_BAD_ARG, "decode publish: op and group live on different devices");
     if (m > group->rows_max || op->heads != group->heads) return fail(SAETTA_ERR_BAD_SHAPE, "decode publish: the group was made for another shape");
     return decode_run(op, m, q_dev, view_of_cache(cache), cache->capacity, nullptr, nullptr, group->staging, row_step,
+                      params_dev, (cudaStream_t)stream, group);
+}
+
+int saetta_decode_exchange_cache(saetta_decode *op, size_t m, const float *q_dev, const saetta_kv_cache *cache,
+                                 saetta_peer_group *group, uint32_t row_step, const float *q_and_gate_dev, float *out_dev,
+                                 const saetta_token_params *params_dev, void *stream) {
+    if (!group || !q_and_gate_dev) return fail(SAETTA_ERR_BAD_ARG, "decode exchange: null pointer");
+    if (int rc = decode_check(op, m, q_dev, out_dev, params_dev)) return rc;
+    if (!cache) return fail(SAETTA_ERR_BAD_ARG, "decode attention: null pointer");
+    if (row_step > 1) return fail(SAETTA_ERR_BAD_ARG, "decode partial: row_step is 0 or 1");
+    if (!group->connected) return fail(SAETTA_ERR_BAD_ARG, "decode exchange: the group is not connected");
+    if (group->device != op->device) return fail(SAETTA_ERR_BAD_ARG, "decode exchange: op and group live on different devices");
+    if (m > group->rows_max || op->heads != group->heads) return fail(SAETTA_ERR_BAD_SHAPE, "decode exchange: the group was made for another shape");
+    return decode_run(op, m, q_dev, view_of_cache(cache), cache->capacity, q_and_gate_dev, out_dev, nullptr, row_step,
                       params_dev, (cudaStream_t)stream, group);
 }
 

@@ -483,6 +483,7 @@ int launch_decode_half(const KvView &kv, const float *q, float *parts, uint32_t 
     a.n_decode = uint32_t(splits), a.mo = mo;
     const bool pairs = kv.dtype != SAETTA_BF16 && m > 1; // two rows per pass share every load of the cache
     a.mo.n_merge = merge_role_ctas(pairs ? 2 : 1);
+    a.mo.passes = kv.dtype == SAETTA_BF16 ? m : m == 1 ? 1 : (m + 1) / 2; // gridDim.y below
     const unsigned ctas = a.n_decode + a.mo.n_merge;
     if (kv.dtype == SAETTA_BF16)
         SAETTA_CUDA(launch_pdl(half_decode::decode_half_kernel<1, true>, dim3(ctas, m), dim3(half_decode::kThreads),

@@ -1089,6 +1089,7 @@ static int launch_rows(DecodeArgs &a, cudaStream_t stream) {
     const uint32_t rows_pass = a.m == 1 ? 1 : a.m == 2 ? 2 : 4;
     a.mo.n_merge = merge_role_ctas(rows_pass);
     const dim3 grid(a.n_decode + a.mo.n_merge, rows_pass == 4 ? (a.m + 3) / 4 : 1);
+    a.mo.passes = grid.y;
     if (rows_pass == 1) return launch_one<BITS, 1>(a, grid, stream);
     if (rows_pass == 2) return launch_one<BITS, 2>(a, grid, stream);
     return launch_one<BITS, 4>(a, grid, stream);

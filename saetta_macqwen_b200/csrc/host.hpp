@@ -96,16 +96,20 @@ struct PeerPush {
     unsigned long long *parts[kMaxPeers]; // each rank's mailbox: [2 slots][world][slot_floats] words of (value, exchange number)
     uint32_t *seq_done;                   // this rank's counter of exchanges collected
     uint32_t *seq_sent;                   // ... and published
+    uint32_t *status;                     // the group's status word (a peer that never published)
     uint32_t world, rank, slot_floats;
 };
 // Where a decode launch's merged result goes: out (gated), part_out (the logical (O, m, l) partial), or
-// the peers' mailboxes (push.world != 0).  n_merge is filled in by the launcher.
+// the peers' mailboxes (push.world != 0) -- and with push.world != 0 AND out, the launch also collects:
+// its merge CTAs wait for the peers' partials of the same exchange and write the gated result.
+// n_merge and passes are filled in by the launcher.
 struct MergeOut {
     const float *q_and_gate = nullptr;
     float *out = nullptr;
     float *part_out = nullptr;
     PeerPush push = {};
     uint32_t n_merge = 0; // merge CTAs per pass; 0: the launch carries no merge role
+    uint32_t passes = 1;  // gridDim.y of the launch
 };
 // One mailbox word: a float with the number of the exchange it belongs to, written by one 64-bit
 // store so that the reader sees both or neither.

@@ -36,8 +36,9 @@ constexpr int kSliceFloats = 128;         // fragment elements of one slice
 constexpr int kSlices = kFragFloats / kSliceFloats; // 16 per (row, kv head)
 constexpr int kMergeRoleMaxParts = 160;   // parts a merge CTA has room for
 constexpr uint32_t kStatusMergeTimeout = 8u;
-// Words of an op's status block: [0] status bits, [kTicketWord + pass] parts finished, [kDoneWord + pass] merge CTAs finished.
-constexpr int kTicketWord = 8, kDoneWord = 16, kStatusWords = 32;
+// Words of an op's status block: [0] status bits, [kTicketWord + pass] parts finished, [kDoneWord + pass] merge CTAs finished,
+// [kAllDoneWord] merge CTAs of all passes finished.
+constexpr int kTicketWord = 8, kDoneWord = 16, kAllDoneWord = 24, kStatusWords = 32;
 // shared memory of a merge CTA: two slice buffers, m/l of every part, the weights, the (m, l) of the warps, the warps' sums, 3 barriers
 constexpr int kMergeRoleSmem = 2 * kMergeRoleMaxParts * kSliceFloats * 4 + kMergeRoleMaxParts * 16 * 4 +
                                kMergeRoleMaxParts * 8 * 4 + (12 * 16 + 16) * 4 + 384 * 16 + 32;
@@ -79,6 +80,26 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+// Polls one mailbox word (a float and the number of the exchange it belongs to, written by one 64-bit
+// store) until it carries exchange number `seq`; false after about a second.
+__device__ __forceinline__ bool mailbox_poll(const unsigned long long *p, uint32_t seq, float &v) {
+    unsigned long long t0 = 0;
+    for (uint32_t n = 0;; n++) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+        if (uint32_t(w >> 32) == seq) {
+            v = __uint_as_float(uint32_t(w));
+            return true;
+        }
+        if ((n & 63) == 63) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (!t0) t0 = t;
+            else if (t - t0 > 1000000000ull) return false;
+        }
+    }
 }
 
 // What a split-KV CTA does once all of its partial has been written: the threads that wrote meet at a
@@ -262,22 +283,59 @@ __device__ __forceinline__ void merge_role(const float *__restrict__ parts, uint
                 out_of(sub, head, dim);
                 const size_t rh = (size_t(row) * 2 + kv) * kHeadsPerKv + head;
                 const float l = comb[NW * 16 + head], Mh = comb[NW * 16 + 8 + head];
-                if (mo.out) {
-                    mo.out[rh * kDim + dim] = sum / l * (1.0f / (1.0f + expf(-gate[i & 1])));
-                } else if (!mo.push.world) {
-                    mo.part_out[rh * kPartStride + dim] = sum;
-                    if (dim == 0) mo.part_out[rh * kPartStride + kPartM] = Mh, mo.part_out[rh * kPartStride + kPartL] = l;
+                if (!mo.push.world) {
+                    if (mo.out) {
+                        mo.out[rh * kDim + dim] = sum / l * (1.0f / (1.0f + expf(-gate[i & 1])));
+                    } else {
+                        mo.part_out[rh * kPartStride + dim] = sum;
+                        if (dim == 0) mo.part_out[rh * kPartStride + kPartM] = Mh, mo.part_out[rh * kPartStride + kPartL] = l;
+                    }
                 } else {
-                    // Straight into this rank's place in every rank's mailbox (plain stores over NVLink, this
-                    // rank's own copy included).  Every word carries the exchange number: the reader needs
-                    // no flag and this kernel no fence.
+                    // Straight into this rank's place in every rank's mailbox (plain stores over NVLink).
+                    // Every word carries the exchange number: the reader needs no flag and this kernel no
+                    // fence.  A launch that also collects keeps its own values in registers.
+                    const bool collect = mo.out != nullptr;
                     const size_t at = (size_t(xseq & 1) * mo.push.world + mo.push.rank) * mo.push.slot_floats + rh * kPartStride;
                     for (uint32_t pr = 0; pr < mo.push.world; pr++) {
+                        if (collect && pr == mo.push.rank) continue;
                         unsigned long long *dst = mo.push.parts[pr] + at;
                         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + dim), "l"(peer_word(sum, xseq)) : "memory");
                         if (dim == 0) {
                             asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + kPartM), "l"(peer_word(Mh, xseq)) : "memory");
                             asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + kPartL), "l"(peer_word(l, xseq)) : "memory");
+                        }
+                    }
+                    if (collect) {
+                        // ... and the peers' values of the same element out of this rank's own mailbox, as
+                        // they land; then the merge over the ranks, in rank order, and the gate.
+                        const unsigned long long *mine = mo.push.parts[mo.push.rank] + size_t(xseq & 1) * mo.push.world * mo.push.slot_floats + rh * kPartStride;
+                        float o_r[kMaxPeers], m_r[kMaxPeers], l_r[kMaxPeers];
+                        bool ok = true;
+#pragma unroll
+                        for (uint32_t pr = 0; pr < kMaxPeers; pr++) {
+                            o_r[pr] = sum, m_r[pr] = Mh, l_r[pr] = l;
+                            if (pr < mo.push.world && pr != mo.push.rank && ok) {
+                                const unsigned long long *src = mine + size_t(pr) * mo.push.slot_floats;
+                                ok = mailbox_poll(src + kPartM, xseq, m_r[pr]) && mailbox_poll(src + kPartL, xseq, l_r[pr]) &&
+                                     mailbox_poll(src + dim, xseq, o_r[pr]);
+                            }
+                        }
+                        if (!ok) {
+                            atomicOr(mo.push.status, kStatusFullTimeout); // a peer never published: `out` stays as it is
+                        } else {
+                            float Mx = -INFINITY;
+#pragma unroll
+                            for (uint32_t pr = 0; pr < kMaxPeers; pr++)
+                                if (pr < mo.push.world) Mx = fmaxf(Mx, m_r[pr]);
+                            float acc = 0.f, lt = 0.f;
+#pragma unroll
+                            for (uint32_t pr = 0; pr < kMaxPeers; pr++) {
+                                if (pr >= mo.push.world || m_r[pr] == -INFINITY) continue;
+                                const float w = exp2f(m_r[pr] - Mx);
+                                lt = fmaf(l_r[pr], w, lt);
+                                acc = fmaf(o_r[pr], w, acc);
+                            }
+                            mo.out[rh * kDim + dim] = acc / lt * (1.0f / (1.0f + expf(-gate[i & 1])));
                         }
                     }
                 }
@@ -286,14 +344,20 @@ __device__ __forceinline__ void merge_role(const float *__restrict__ parts, uint
         }
         if (!landed && tid == 0) atomicOr(words, kStatusMergeTimeout);
     }
-    if (mo.push.world && s_ok == 1 && idx == 0 && pass == 0 && tid == 0) *mo.push.seq_sent = xseq; // read by the collecting kernel only
-    // The last merge CTA of the pass to finish clears the two counters for the next launch (which
-    // touches them only after its own dependency wait, i.e. after this grid has completed).
+    // The last merge CTA of the pass to finish clears the pass's two counters for the next launch (which
+    // touches them only after its own dependency wait, i.e. after this grid has completed); the last of
+    // the whole launch moves the exchange numbers on -- only then, so that every merge CTA of the
+    // launch has read them before they change.
     __syncthreads();
     if (tid == 0) {
         if (atomicAdd(words + kDoneWord + pass, 1u) == mo.n_merge - 1) {
             words[kTicketWord + pass] = 0;
             words[kDoneWord + pass] = 0;
+        }
+        if (mo.push.world && atomicAdd(words + kAllDoneWord, 1u) == mo.n_merge * mo.passes - 1) {
+            words[kAllDoneWord] = 0;
+            *mo.push.seq_sent = xseq;
+            if (mo.out) *mo.push.seq_done = xseq; // this launch collected too
         }
     }
 }

@@ -182,6 +182,7 @@ int saetta_peer_group_connect(saetta_peer_group *g, const uint8_t *handles /* [w
         g->push.parts[r] = reinterpret_cast<unsigned long long *>(g->peer_base[r]);
     }
     g->push.seq_done = group_words(g) + kSeqDoneWord, g->push.seq_sent = group_words(g) + kSeqSentWord;
+    g->push.status = group_words(g) + kStatusWord;
     g->push.world = uint32_t(g->world), g->push.rank = uint32_t(g->rank), g->push.slot_floats = uint32_t(g->slot_floats);
     g->connected = true;
     return SAETTA_OK;

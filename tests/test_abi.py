@@ -84,6 +84,7 @@ def test_null_arguments_are_refused_before_any_device_work(lib):
         assert fn(None, 1, None, None, None) == sa.BAD_ARG
     assert lib.saetta_peer_slice(None, 8, C.byref(z), C.byref(z)) == sa.BAD_ARG
     assert lib.saetta_decode_publish_cache(None, 1, None, None, None, 0, None, None) == sa.BAD_ARG
+    assert lib.saetta_decode_exchange_cache(None, 1, None, None, None, 0, None, None, None, None) == sa.BAD_ARG
     assert lib.saetta_decode_batch_publish(None, 1, None, None, None, None, None) == sa.BAD_ARG
     # attention_prefill::encode without an object: nulls, then bfloat16 (binary16 only), both before any device work
     fp = sa.FlashParams(16, 2, 0, 8, 0.0625)

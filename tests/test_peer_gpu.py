@@ -67,12 +67,14 @@ def _rank(rank, world, port, tokens, m, bits, out_q):
     rt = (lambda x: o.round_trip(x, bits)) if bits in (4, 8) else o.round_f16
     kr, vr = rt(keys), rt(values)
     want = o.attention_rows(q, qg, kr, vr, [pos + r + 1 for r in range(m)], threads=4)
-    for it in range(4):  # several exchanges in a row: both mailbox slots get used
+    for it in range(6):  # several exchanges in a row: both mailbox slots get used, the routes interleave
         out.zero_()
-        if it % 2 == 0:  # the decode's merge kernel stores the partial into the mailboxes itself
+        if it % 3 == 0:    # one launch: the decode's merge CTAs publish and collect
+            op.exchange_cache(m, qd, cache, group, gd, out, p, row_step=step)
+        elif it % 3 == 1:  # the decode's merge CTAs store the partial into the mailboxes, a second launch collects
             op.publish_cache(m, qd, cache, group, p, row_step=step)
             group.collect(m, gd, out)
-        else:            # any partial in the staging buffer: publish, then collect
+        else:              # any partial in the staging buffer: publish, then collect
             op.partial_cache(m, qd, cache, group.staging, p, row_step=step)
             group.merge(m, gd, out)
         torch.cuda.synchronize()
