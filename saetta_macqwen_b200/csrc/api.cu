@@ -950,15 +950,18 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     const size_t lo = key_lo - key_base, hi = key_hi - key_base;
     const size_t fresh = size_t(p.pos) > key_base ? size_t(p.pos) - key_base : 0;
     int v_dtype = dtype;
+    const bool in_place = (kq || vq) && p.kv_heads == 2; // the kernel turns the codes into operand tiles itself
     if (kq || vq) {
         if (!kq || !vq || kq->bits != vq->bits) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: quant needs both sides");
         if (hi > kq->capacity || hi > vq->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: the keys asked for exceed the capacity");
         if (kq->per_token != p.kv_heads * size_t(kGroupsPerHead)) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: quant rows of another shape");
-        // The quantised cache is read through a 16-bit copy, as the reference's kv_stage reads it
-        // (src/kv_quant.rs:121-126 semantics).  Keys take q's type; values are staged as binary16
-        // (exactly the reference's round_trip_as_half), so P is binary16 too and keeps an 11-bit
-        // significand.  Only the rows the copy does not hold yet are dequantised: per chunk of a long
-        // prompt, the chunk's own rows.
+    }
+    if ((kq || vq) && !in_place) {
+        // Other head counts: the quantised cache is read through a 16-bit copy, as the reference's
+        // kv_stage reads it (src/kv_quant.rs:121-126 semantics).  Keys take q's type; values are staged
+        // as binary16 (exactly the reference's round_trip_as_half), so P is binary16 too and keeps an
+        // 11-bit significand.  Only the rows the copy does not hold yet are dequantised: per chunk of
+        // a long prompt, the chunk's own rows.
         if (int rc = stage_rows(op, 0, kq->data, dtype, lo, hi, fresh, st, [&](size_t first, size_t n) {
                 return launch_kv_dequantize(kq, op->stage_k, dtype, first, n, st);
             }))
@@ -970,7 +973,7 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
         keys = op->stage_k, values = op->stage_v;
         v_dtype = SAETTA_F16;
     }
-    if (!keys || !values) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: keys or values null");
+    if (!in_place && (!keys || !values)) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: keys or values null");
     if (!(kq || vq) && dtype == SAETTA_BF16) {
         // P must share V's type in the second MMA; bfloat16's 8-bit significand would put P's
         // rounding at the tolerance, so bfloat16 values go through a binary16 copy (exact in range).
@@ -987,6 +990,12 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     PrefillArgs a{q, keys, values, dtype, v_dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
                   uint32_t(key_lo), uint32_t(key_hi), p.scale};
     a.key_base = uint32_t(key_base);
+    if (in_place) {
+        // 8/4-bit rows are read where they are, per key block (kernels/attention_rows_q.metal:16-31): no
+        // 16-bit copy of the cache, nothing to reserve
+        a.qbits = kq->bits;
+        a.qk = kq->data, a.qv = vq->data, a.qks = kq->scales, a.qkz = kq->biases, a.qvs = vq->scales, a.qvz = vq->biases;
+    }
     // Long context: every tile has about the same work, and tiles rarely divide evenly over
     // the SMs.  Cut each tile's keys into two work items (twice as many, half as long) and merge
     // their (m, l, O); the merge is a few tens of microseconds against milliseconds of MMA.

@@ -232,6 +232,9 @@ struct PrefillArgs {
                              // partial in part + split * tokens*heads*kPartStride (out must be null)
     uint32_t key_base = 0;   // global position of row 0 of k and v (a multiple of 64, <= key_lo): a shard
                              // that stores only its own slice of the sequence
+    // a quantised cache read in place (qbits 8 or 4; k and v above are then unused): codes, scales, biases
+    int qbits = 0;
+    const void *qk = nullptr, *qv = nullptr, *qks = nullptr, *qkz = nullptr, *qvs = nullptr, *qvz = nullptr;
 };
 int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream);
 int prefill_configure(int device);

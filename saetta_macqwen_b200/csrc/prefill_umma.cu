@@ -40,6 +40,13 @@
 //    epilogue divides by l and applies the sigmoid gate (256-bit loads and
 //    stores), or leaves (O, m, l) partials for a merge (across GPUs, or across the
 //    two key halves a long-context tile is cut into).
+//  * A quantised cache is read IN PLACE (the reference's attention_rows_q reads the codes per key
+//    block, kernels/attention_rows_q.metal:16-31,206-344): the copy warp brings a block's codes,
+//    scales and biases into a small staging area with tensor copies, one warpgroup turns them into
+//    the binary16 operand tiles in shared memory -- s * c + z with one rounding, the reference's
+//    round_trip_as_half (src/kv_quant.rs:121-126) -- in the swizzled layout the tensor cores read,
+//    and the other tile I/O warpgroup takes whole rows.  No 16-bit copy of the cache exists in
+//    device memory, and a chunk over a long prefix reads 1088 (576) bytes per key instead of 2048.
 //  * All mbarrier waits are bounded; a wait that gives up sets the status word
 //    and the CTA-wide abort flag, every role leaves its loop, and TMEM is freed.
 #include <cuda.h>
@@ -59,6 +66,20 @@ constexpr int kPfStages = 3;
 constexpr int kPfThreads = 512; // four warpgroups: softmax; tile I/O, first halves of the rows; tile I/O, second halves;
                                 // TMA warp, S-MMA warp, P V-MMA warp and a spare
 constexpr int kPfSmem = 2 * kPfStages * kKBytes + 1024 /*align*/ + 256 /*barriers*/ + 2 * 2 * kBM * 4 /*l, m per row, two tiles*/;
+// Shared memory with a quantised cache (QBITS = 8 or 4): two operand stages, and two stages of codes (K and V
+// of one kv head, 64 keys) with the four scale / bias arrays (both kv heads: 16 bytes per key and array).
+template <int QBITS>
+struct PfLayout {
+    static constexpr int kOpStages = QBITS ? 2 : kPfStages;
+    static constexpr int kCodeRow = kDim * QBITS / 8;          // bytes of one key's codes of one kv head
+    static constexpr int kCodeSide = kBN * kCodeRow;           // 16 KB / 8 KB
+    static constexpr int kParamArr = kBN * 16;                 // 1 KB
+    static constexpr int kCodeStage = QBITS ? 2 * kCodeSide + 4 * kParamArr : 0;
+    static constexpr int kCodeStages = QBITS ? 2 : 0;
+    static constexpr int kSmem = 2 * kOpStages * kKBytes + kCodeStages * kCodeStage + 1024 /*align*/ + 256 /*barriers*/ + 2 * 2 * kBM * 4;
+};
+static_assert(PfLayout<0>::kSmem == kPfSmem, "the 16-bit layout is unchanged");
+static_assert(PfLayout<8>::kSmem <= 227 * 1024 && PfLayout<4>::kSmem <= 227 * 1024, "fits a CTA's shared memory");
 constexpr int kTmemO = 0, kTmemQ = 256, kTmemS = 384; // TMEM columns: O, Q (2 values per column), S/P buffers
 constexpr float kLog2ePf = 1.4426950408889634f;
 constexpr float kPfRescale = 8.0f;
@@ -75,6 +96,7 @@ struct PfParams {
     uint32_t splits;      // each tile's key range is cut into this many work items (>1: partials per split)
     uint32_t part_stride; // floats between the partial buffers of consecutive splits
     uint32_t key_base;    // global position of row 0 of the K / V buffers
+    uint32_t q_bf16;      // q arrives as bfloat16 but the operands are binary16 (quantised cache): converted on the way in
 };
 
 // ----------------------------------------------------------------- PTX wrappers
@@ -89,6 +111,12 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -206,17 +234,27 @@ __device__ __forceinline__ bool pf_tile(const PfParams &p, uint32_t round, PfTil
     return true;
 }
 
+// The six maps of a quantised cache: K and V codes (bytes [keys][kv heads][row]) and the four scale / bias arrays
+// (binary16 [keys][kv heads * 4]); unused (copies of map_k) for a 16-bit cache.
+struct PfQuantMaps {
+    CUtensorMap kc, vc, ks, kz, vs, vz;
+};
+
+template <int QBITS>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-               const PfParams p) {
+               const __grid_constant__ PfQuantMaps qm, const PfParams p) {
+    using L = PfLayout<QBITS>;
+    constexpr int NST = L::kOpStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *sK = smem;                        // [kPfStages][kKBytes]
-    uint8_t *sV = sK + kPfStages * kKBytes;    // [kPfStages][kKBytes]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + kPfStages * kKBytes);
+    uint8_t *sK = smem;                  // [NST][kKBytes]
+    uint8_t *sV = sK + NST * kKBytes;    // [NST][kKBytes]
+    uint8_t *sCode = sV + NST * kKBytes; // [2][K codes, V codes, k scales, k biases, v scales, v biases] (quantised cache only)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sCode + L::kCodeStages * L::kCodeStage);
     uint64_t *q_full = bars + 0, *q_empty = bars + 1, *o_final = bars + 2, *o_empty = bars + 3, *k_full = bars + 4,
              *k_empty = bars + 7, *v_full = bars + 10, *v_empty = bars + 13, *s_full = bars + 16, *p_full = bars + 18,
-             *pv_done = bars + 20, *lm_full = bars + 22;
+             *pv_done = bars + 20, *lm_full = bars + 22, *code_full = bars + 26, *code_empty = bars + 28;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 24);
     float *row_l = reinterpret_cast<float *>(bars + 32); // [2][128] row sums handed from the softmax warps
     float *row_m = row_l + 2 * kBM;                      // [2][128] running maxima (log2 units)
@@ -225,9 +263,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 8), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 8);
-        for (int s = 0; s < kPfStages; s++)
-            mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
+        // with a quantised cache one warpgroup (4 warps) does the tile I/O and one fills the operand stages
+        mbar_init(q_full, QBITS ? 4 : 8), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, QBITS ? 4 : 8);
+        for (int s = 0; s < NST; s++)
+            mbar_init(&k_full[s], QBITS ? 4 : 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], QBITS ? 4 : 1), mbar_init(&v_empty[s], 1);
+        for (int s = 0; s < L::kCodeStages; s++) mbar_init(&code_full[s], 1), mbar_init(&code_empty[s], 4);
         for (int s = 0; s < 2; s++)
             mbar_init(&s_full[s], 1), mbar_init(&p_full[s], 4), mbar_init(&pv_done[s], 1), mbar_init(&lm_full[s], 4);
         *abort_flag = 0;
@@ -264,24 +304,45 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
                 if (!t.nb) continue;
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
-                    const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1;
+                    const uint32_t st = g % NST, ph = (g / NST) & 1;
                     const int key0 = int((t.b_begin + b) * kBN) - int(p.key_base); // row of the buffer
-                    if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
-                    mbar_expect_tx(&k_full[st], kKBytes);
-                    for (int c = 0; c < 4; c++) tma_load_3d(sK + st * kKBytes + c * kKChunk, &map_k, &k_full[st], c * 64, int(t.kv), key0);
-                    if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
-                    mbar_expect_tx(&v_full[st], kKBytes);
-                    for (int c = 0; c < 4; c++) tma_load_3d(sV + st * kKBytes + c * kKChunk, &map_v, &v_full[st], c * 64, int(t.kv), key0);
+                    if constexpr (QBITS != 0) {
+                        // the block's codes (this kv head's) and the four scale / bias arrays (both kv heads: 16
+                        // bytes per key, the smallest tensor copy) into a code stage; the converting warpgroup
+                        // makes the operand tiles
+                        const uint32_t cs = g & 1, cph = (g >> 1) & 1;
+                        if (!mbar_wait(&code_empty[cs], cph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                        uint8_t *dst = sCode + cs * L::kCodeStage;
+                        mbar_expect_tx(&code_full[cs], L::kCodeStage);
+                        tma_load_3d(dst, &qm.kc, &code_full[cs], 0, int(t.kv), key0);
+                        tma_load_3d(dst + L::kCodeSide, &qm.vc, &code_full[cs], 0, int(t.kv), key0);
+                        tma_load_2d(dst + 2 * L::kCodeSide, &qm.ks, &code_full[cs], 0, key0);
+                        tma_load_2d(dst + 2 * L::kCodeSide + L::kParamArr, &qm.kz, &code_full[cs], 0, key0);
+                        tma_load_2d(dst + 2 * L::kCodeSide + 2 * L::kParamArr, &qm.vs, &code_full[cs], 0, key0);
+                        tma_load_2d(dst + 2 * L::kCodeSide + 3 * L::kParamArr, &qm.vz, &code_full[cs], 0, key0);
+                    } else {
+                        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                        mbar_expect_tx(&k_full[st], kKBytes);
+                        for (int c = 0; c < 4; c++) tma_load_3d(sK + st * kKBytes + c * kKChunk, &map_k, &k_full[st], c * 64, int(t.kv), key0);
+                        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                        mbar_expect_tx(&v_full[st], kKBytes);
+                        for (int c = 0; c < 4; c++) tma_load_3d(sV + st * kKBytes + c * kKChunk, &map_v, &v_full[st], c * 64, int(t.kv), key0);
+                    }
                 }
                 tc++;
             }
             // On the way out after a failed wait, let the copies already issued land
             // (bounded) so that no copy is in flight when the CTA's shared memory is released.
-            if (*abort_flag)
-                for (uint32_t k = g > kPfStages ? g - kPfStages : 0; k < g; k++) {
-                    mbar_wait(&k_full[k % kPfStages], (k / kPfStages) & 1, never_set, 200000u);
-                    mbar_wait(&v_full[k % kPfStages], (k / kPfStages) & 1, never_set, 200000u);
+            if (*abort_flag) {
+                if constexpr (QBITS != 0) {
+                    for (uint32_t k = g > 2 ? g - 2 : 0; k < g; k++) mbar_wait(&code_full[k & 1], (k >> 1) & 1, never_set, 200000u);
+                } else {
+                    for (uint32_t k = g > NST ? g - NST : 0; k < g; k++) {
+                        mbar_wait(&k_full[k % NST], (k / NST) & 1, never_set, 200000u);
+                        mbar_wait(&v_full[k % NST], (k / NST) & 1, never_set, 200000u);
+                    }
                 }
+            }
         }
     } else if (warp == 13) {
         // ------------------------------------------------------------ MMA issuer for S = Q K^T
@@ -299,7 +360,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 if (!t.nb) continue;
                 if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; }
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
-                    const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1, sb = g & 1;
+                    const uint32_t st = g % NST, ph = (g / NST) & 1, sb = g & 1;
                     if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
                     if (!mbar_wait(&pv_done[sb], ((g >> 1) & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
@@ -330,7 +391,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
                 if (!t.nb) continue;
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
-                    const uint32_t st = g % kPfStages, ph = (g / kPfStages) & 1, sb = g & 1, sph = (g >> 1) & 1;
+                    const uint32_t st = g % NST, ph = (g / NST) & 1, sb = g & 1, sph = (g >> 1) & 1;
                     if (!mbar_wait(&p_full[sb], sph, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
                     if (b == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
@@ -443,13 +504,99 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (lane == 0) mbar_arrive(&lm_full[tc & 1]);
             tc++;
         }
+    } else if (QBITS != 0 && warp < 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        // ------------------------------------------------------------ codes -> binary16 operand tiles
+        // Per 64-key block: wait for its codes, wait for a free operand stage, write K (then V) as
+        // s * c + z rounded once to binary16 -- the code as an exact binary16 integer (byte permute onto
+        // the magic 1024, minus 1024), then one fused multiply-add with the group's scale and bias -- into
+        // the four 64-dim slabs of the stage in the tensor cores' 128-byte-swizzled layout, and hand the
+        // stage to the MMA warps.  A lane reads 16 bytes of codes; eight lanes cover 128 bytes of a key's
+        // row, a warp four keys at a time, the four warps 16 keys each.
+        const uint32_t cw = warp - 4;
+        constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u;
+        uint32_t g = 0;
+        bool ok = true;
+        PfTile t;
+        auto convert_side = [&](const uint8_t *codes, const uint8_t *sc, const uint8_t *bi, uint8_t *dst, uint32_t kv) {
+            constexpr int QB = QBITS ? QBITS : 8;              // (this role is never taken with a 16-bit cache)
+            constexpr int kValsPerLoad = 128 / QB;             // values in a lane's 16 bytes: 16 or 32
+            constexpr int kLoadsPerRow = kDim * QB / 8 / 128;  // 128-byte pieces of a key's row: 2 or 1
+            const uint32_t col = lane & 7;
+#pragma unroll
+            for (int it = 0; it < 4; it++) {
+                const uint32_t key = cw * 16 + it * 4 + (lane >> 3);
+#pragma unroll
+                for (int piece = 0; piece < kLoadsPerRow; piece++) {
+                    const uint4 cw4 = *reinterpret_cast<const uint4 *>(codes + key * L::kCodeRow + piece * 128 + col * 16);
+                    const uint32_t d0 = (piece * 8 + col) * kValsPerLoad; // first dim of these values
+                    const uint32_t G = d0 >> 6;
+                    const uint32_t sraw = *reinterpret_cast<const uint16_t *>(sc + key * 16 + (kv * 4 + G) * 2);
+                    const uint32_t zraw = *reinterpret_cast<const uint16_t *>(bi + key * 16 + (kv * 4 + G) * 2);
+                    const uint32_t s2 = sraw | (sraw << 16), z2 = zraw | (zraw << 16);
+                    const uint32_t w4[4] = {cw4.x, cw4.y, cw4.z, cw4.w};
+                    uint32_t h[kValsPerLoad / 2]; // pairs of consecutive dims
+                    if (QB == 8) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            h[2 * j] = hfma2_u32(hsub2_u32(prmt(w4[j], kMagic, 0x4140), k1024), s2, z2);
+                            h[2 * j + 1] = hfma2_u32(hsub2_u32(prmt(w4[j], kMagic, 0x4342), k1024), s2, z2);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t even = w4[j] & 0x0f0f0f0fu, odd = (w4[j] >> 4) & 0x0f0f0f0fu; // nibbles 0,2,4,6 / 1,3,5,7
+                            const uint32_t n03 = prmt(even, odd, 0x5140), n47 = prmt(even, odd, 0x7362); // bytes n0 n1 n2 n3 / n4..n7
+                            h[4 * j] = hfma2_u32(hsub2_u32(prmt(n03, kMagic, 0x4140), k1024), s2, z2);
+                            h[4 * j + 1] = hfma2_u32(hsub2_u32(prmt(n03, kMagic, 0x4342), k1024), s2, z2);
+                            h[4 * j + 2] = hfma2_u32(hsub2_u32(prmt(n47, kMagic, 0x4140), k1024), s2, z2);
+                            h[4 * j + 3] = hfma2_u32(hsub2_u32(prmt(n47, kMagic, 0x4342), k1024), s2, z2);
+                        }
+                    }
+                    // 16-byte chunks (8 dims) of the key's 128-byte row in slab d / 64, swizzled by the key
+                    uint8_t *rowp = dst + (d0 >> 6) * kKChunk + key * 128;
+#pragma unroll
+                    for (int c = 0; c < kValsPerLoad / 8; c++) {
+                        const uint32_t chunk = ((d0 & 63) >> 3) + c;
+                        *reinterpret_cast<uint4 *>(rowp + ((chunk ^ (key & 7)) << 4)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+                    }
+                }
+            }
+        };
+        for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+            if (!t.nb) continue;
+            for (uint32_t b = 0; b < t.nb; b++, g++) {
+                const uint32_t st = g % NST, ph = (g / NST) & 1, cs = g & 1, cph = (g >> 1) & 1;
+                const uint8_t *code = sCode + cs * L::kCodeStage;
+                if (!mbar_wait(&code_full[cs], cph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                convert_side(code, code + 2 * L::kCodeSide, code + 2 * L::kCodeSide + L::kParamArr, sK + st * kKBytes, t.kv);
+                fence_async_smem(); // the tensor cores read the stage through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&k_full[st]);
+                if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                convert_side(code + L::kCodeSide, code + 2 * L::kCodeSide + 2 * L::kParamArr, code + 2 * L::kCodeSide + 3 * L::kParamArr,
+                             sV + st * kKBytes, t.kv);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&v_full[st]);
+                    mbar_arrive(&code_empty[cs]);
+                }
+            }
+        }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        if constexpr (QBITS != 0) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        else asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
         // ------------------------------------------------------------ tile I/O: Q rows in, results out
         // Per tile these warps write its Q rows into tensor memory and, at its end, scale and gate
         // O out to memory.  The Q rows of tile k+1 go in as soon as the last S of tile k has been
         // computed, before tile k's epilogue, so the MMA warp never waits for a tile change.
-        const uint32_t quarter = warp & 3, row = quarter * 32 + lane, half = warp >= 8 ? 1u : 0u;
+        // 16-bit cache: two threads per row, the warps of the first tile I/O warpgroup take dims 0..127 of
+        // Q, the gate and O, those of the second dims 128..255.  Quantised cache: the second warpgroup
+        // alone, one thread per row, one half after the other.
+        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t half_lo = QBITS ? 0u : (warp >= 8 ? 1u : 0u), half_hi = QBITS ? 2u : half_lo + 1;
         const uint32_t lane_addr = (quarter * 32) << 16;
         struct RowOf {
             uint32_t tok;
@@ -473,41 +620,59 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 const RowOf r = row_of(t);
                 if (r.live && r.part) {
                     float *dst = r.part + r.rh * kPartStride;
-                    for (uint32_t d = half * 128; d < half * 128 + 128; d++) dst[d] = 0.f;
-                    if (!half) dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
+                    for (uint32_t d = half_lo * 128; d < half_hi * 128; d++) dst[d] = 0.f;
+                    if (!half_lo) dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
                 }
             }
             return false;
         };
-        // Two threads per row: the warps of the first tile I/O warpgroup take dims 0..127 of Q, the gate
-        // and O, those of the second dims 128..255.
         auto load_q = [&](const PfTile &t, uint32_t k) -> bool {
             const RowOf r = row_of(t);
             const bool row_live = r.live;
             const size_t rh = r.rh;
-            if (row_live && p.out) { // pull this half row's gate values towards L2 for the epilogue
-                const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim + half * 128);
+            if (row_live && p.out) { // pull this row's gate values towards L2 for the epilogue
+                const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim + half_lo * 128);
 #pragma unroll
-                for (int j = 0; j < 4; j++) prefetch_l2(gpf + j * 128);
+                for (int j = 0; j < (QBITS ? 8 : 4); j++) prefetch_l2(gpf + j * 128);
             }
-            // this thread's half of its Q row into tensor memory (two values per column), once the
+            // this thread's part of its Q row into tensor memory (two values per column), once the
             // MMAs of the tile before no longer read the old one.  The row does not depend on that
-            // wait: it is fetched into registers before it.
-            const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim + half * 128);
-            uint4 qv[16];
+            // wait: its first half is fetched into registers before it.
+            bool waited = false;
+            auto q_half = [&](const uint32_t half) -> bool {
+                const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + rh * kDim + half * 128);
+                uint4 qv[16];
 #pragma unroll
-            for (int j = 0; j < 16; j++) qv[j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
-            if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
-            tc_fence_after();
+                for (int j = 0; j < 16; j++) qv[j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
+                if (QBITS != 0 && p.q_bf16) { // bfloat16 queries over binary16 operand tiles: exact unless outside binary16's range
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t w[32];
+                    for (int j = 0; j < 16; j++) {
+                        uint32_t *w = reinterpret_cast<uint32_t *>(&qv[j]);
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const uint4 v = qv[c * 8 + j];
-                    w[4 * j] = v.x, w[4 * j + 1] = v.y, w[4 * j + 2] = v.z, w[4 * j + 3] = v.w;
+                        for (int e = 0; e < 4; e++) w[e] = pack_half2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                    }
                 }
-                tmem_st32(tmem_q + lane_addr + half * 64 + c * 32, w);
+                if (!waited) {
+                    if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+                    tc_fence_after();
+                    waited = true;
+                }
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    uint32_t w[32];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint4 v = qv[c * 8 + j];
+                        w[4 * j] = v.x, w[4 * j + 1] = v.y, w[4 * j + 2] = v.z, w[4 * j + 3] = v.w;
+                    }
+                    tmem_st32(tmem_q + lane_addr + half * 64 + c * 32, w);
+                }
+                return true;
+            };
+            if constexpr (QBITS != 0) {
+                if (!q_half(0) || !q_half(1)) return false;
+            } else {
+                if (!q_half(half_lo)) return false;
             }
             tmem_wait_st();
             tc_fence_before();
@@ -520,48 +685,58 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const bool row_live = r.live;
             const size_t rh = r.rh;
             float *part = r.part;
-            // O leaves tensor memory in one go (this thread's 128 values), so that the next tile's P V
+            // A half of O leaves tensor memory in one go (128 values), so that the next tile's P V
             // products wait for four tensor-memory loads and nothing else; the gate values, which come
             // from global memory, are fetched afterwards, one 32-byte step ahead of their use.
             // (256-bit loads and stores: a thread's accesses are whole 32-byte sectors of its row)
             const bool gated = row_live && p.out;
-            const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim + half * 128 : 0);
             if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             const float l = row_l[(k & 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
             if (!mbar_wait(o_final, k & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
             tc_fence_after();
             const float inv_l = l > 0.f ? 1.f / l : 0.f;
-            uint32_t o[4][32];
+            auto o_half = [&](const uint32_t half, const bool last) {
+                const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim + half * 128 : 0);
+                uint32_t o[4][32];
 #pragma unroll
-            for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem_o + lane_addr + half * 128 + ch * 32, o[ch]);
-            tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty); // O has left tensor memory: the next tile's P V products may start
-            if (row_live) {
-                if (p.out) {
-                    float *op = p.out + rh * kDim + half * 128;
-                    Float8 g = ld_global_v8(gp);
-#pragma unroll
-                    for (int st = 0; st < 16; st++) {
-                        Float8 gn = g;
-                        if (st + 1 < 16) gn = ld_global_v8(gp + (st + 1) * 8);
-                        Float8 v;
-#pragma unroll
-                        for (int e = 0; e < 8; e++)
-                            v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-g.v[e]));
-                        st_global_v8(op + st * 8, v);
-                        g = gn;
-                    }
-                } else {
-                    float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + half * 128);
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        op[j] = make_float4(__uint_as_float(o[j >> 3][4 * (j & 7)]), __uint_as_float(o[j >> 3][4 * (j & 7) + 1]),
-                                            __uint_as_float(o[j >> 3][4 * (j & 7) + 2]), __uint_as_float(o[j >> 3][4 * (j & 7) + 3]));
+                for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem_o + lane_addr + half * 128 + ch * 32, o[ch]);
+                tmem_wait_ld();
+                if (last) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_empty); // O has left tensor memory: the next tile's P V products may start
                 }
+                if (row_live) {
+                    if (p.out) {
+                        float *op = p.out + rh * kDim + half * 128;
+                        Float8 g = ld_global_v8(gp);
+#pragma unroll
+                        for (int st = 0; st < 16; st++) {
+                            Float8 gn = g;
+                            if (st + 1 < 16) gn = ld_global_v8(gp + (st + 1) * 8);
+                            Float8 v;
+#pragma unroll
+                            for (int e = 0; e < 8; e++)
+                                v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-g.v[e]));
+                            st_global_v8(op + st * 8, v);
+                            g = gn;
+                        }
+                    } else {
+                        float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + half * 128);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            op[j] = make_float4(__uint_as_float(o[j >> 3][4 * (j & 7)]), __uint_as_float(o[j >> 3][4 * (j & 7) + 1]),
+                                                __uint_as_float(o[j >> 3][4 * (j & 7) + 2]), __uint_as_float(o[j >> 3][4 * (j & 7) + 3]));
+                    }
+                }
+            };
+            if constexpr (QBITS != 0) {
+                o_half(0, false);
+                o_half(1, true);
+            } else {
+                o_half(half_lo, true);
             }
-            if (row_live && part && !half) {
+            if (row_live && part && !half_lo) {
                 part[rh * kPartStride + kPartM] = m_ref;
                 part[rh * kPartStride + kPartL] = l;
             }
@@ -605,41 +780,80 @@ static EncodeTiledFn encode_fn() {
 
 int prefill_configure(int device) {
     (void)device;
-    SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfLayout<0>::kSmem));
+    SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfLayout<8>::kSmem));
+    SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfLayout<4>::kSmem));
     return SAETTA_OK;
 }
 
 int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(SAETTA_ERR_CUDA, "prefill attention: cuTensorMapEncodeTiled is not available");
-    if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15)
-        return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q, keys and values must be 16-byte aligned");
-    const CUtensorMapDataType dt = a.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap mk, mv;
+    const bool quant = a.qbits != 0;
+    if (quant && (a.qbits != 8 && a.qbits != 4)) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: 8- or 4-bit codes");
+    if (quant && a.kv_heads != 2) return fail(SAETTA_ERR_UNSUPPORTED, "prefill attention: codes are read in place for 2 kv heads");
+    if (reinterpret_cast<uintptr_t>(a.q) & 15) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q must be 16-byte aligned");
+    if (!quant && ((reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15))
+        return fail(SAETTA_ERR_BAD_ARG, "prefill attention: keys and values must be 16-byte aligned");
     if (a.key_base % kBN || a.key_base > a.key_lo) return fail(SAETTA_ERR_BAD_SHAPE, "prefill attention: the cache's first row must sit at a multiple of 64 at or below the first key");
     // rows of the buffers the kernel may touch: up to the last key it is asked for (copies past that read zeros)
     const cuuint64_t keys_total = std::max<cuuint64_t>(1, std::min<cuuint64_t>(cuuint64_t(a.pos) + a.tokens, a.key_hi) - std::min<cuuint64_t>(a.key_base, a.key_hi));
-    const CUtensorMapDataType dtv = a.v_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    for (int side = 0; side < 2; side++) {
-        const cuuint64_t dims[3] = {cuuint64_t(kDim), a.kv_heads, keys_total};
-        const cuuint64_t strides[2] = {kDim * 2, cuuint64_t(a.kv_heads) * kDim * 2};
-        const cuuint32_t box[3] = {64, 1, kBN}, el[3] = {1, 1, 1};
-        CUresult r = enc(side ? &mv : &mk, side ? dtv : dt, 3, const_cast<void *>(side ? a.v : a.k), dims, strides, box, el,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the cache rejected");
+    CUtensorMap mk, mv;
+    PfQuantMaps qm;
+    const cuuint32_t el[3] = {1, 1, 1};
+    if (!quant) {
+        const CUtensorMapDataType dt = a.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const CUtensorMapDataType dtv = a.v_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        for (int side = 0; side < 2; side++) {
+            const cuuint64_t dims[3] = {cuuint64_t(kDim), a.kv_heads, keys_total};
+            const cuuint64_t strides[2] = {kDim * 2, cuuint64_t(a.kv_heads) * kDim * 2};
+            const cuuint32_t box[3] = {64, 1, kBN};
+            CUresult r = enc(side ? &mv : &mk, side ? dtv : dt, 3, const_cast<void *>(side ? a.v : a.k), dims, strides, box, el,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the cache rejected");
+        }
+        qm.kc = qm.vc = qm.ks = qm.kz = qm.vs = qm.vz = mk; // not read
+    } else {
+        // codes: bytes [keys][kv heads][row]; a box is one kv head's rows of 64 keys, unswizzled
+        const cuuint64_t row = cuuint64_t(kDim) * a.qbits / 8;
+        for (int side = 0; side < 2; side++) {
+            const cuuint64_t dims[3] = {row, a.kv_heads, keys_total};
+            const cuuint64_t strides[2] = {row, cuuint64_t(a.kv_heads) * row};
+            const cuuint32_t box[3] = {cuuint32_t(row), 1, kBN};
+            CUresult r = enc(side ? &qm.vc : &qm.kc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(side ? a.qv : a.qk), dims, strides,
+                             box, el, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the codes rejected");
+        }
+        // scales and biases: binary16 [keys][kv heads * 4]; a box is 64 keys' 16 bytes
+        const void *arr[4] = {a.qks, a.qkz, a.qvs, a.qvz};
+        CUtensorMap *maps[4] = {&qm.ks, &qm.kz, &qm.vs, &qm.vz};
+        for (int i = 0; i < 4; i++) {
+            const cuuint64_t dims[2] = {cuuint64_t(a.kv_heads) * 4, keys_total};
+            const cuuint64_t strides[1] = {cuuint64_t(a.kv_heads) * 4 * 2};
+            const cuuint32_t box[2] = {cuuint32_t(a.kv_heads) * 4, kBN};
+            CUresult r = enc(maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(arr[i]), dims, strides, box, el,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(SAETTA_ERR_CUDA, "prefill attention: tensor map for the scales rejected");
+        }
+        mk = mv = qm.kc; // not read
     }
+    // operands: binary16 throughout over a quantised cache (bfloat16 queries are converted on the way in)
+    const uint32_t fmt = quant ? 0u : (a.dtype == SAETTA_BF16 ? 1u : 0u), v_fmt = quant ? 0u : (a.v_dtype == SAETTA_BF16 ? 1u : 0u);
     PfParams p{a.q, a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
-               a.scale * kLog2ePf, a.dtype == SAETTA_BF16 ? 1u : 0u, a.v_dtype == SAETTA_BF16 ? 1u : 0u,
-               a.splits ? a.splits : 1u, uint32_t(size_t(a.tokens) * a.heads * kPartStride), a.key_base};
+               a.scale * kLog2ePf, fmt, v_fmt, a.splits ? a.splits : 1u, uint32_t(size_t(a.tokens) * a.heads * kPartStride), a.key_base,
+               quant && a.dtype == SAETTA_BF16 ? 1u : 0u};
     int dev = 0;
     SAETTA_CUDA(cudaGetDevice(&dev));
     const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads * (a.splits ? a.splits : 1u);
     const uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count(dev)));
-    prefill_kernel<<<grid, kPfThreads, kPfSmem, stream>>>(mk, mv, p);
+    if (!quant) prefill_kernel<0><<<grid, kPfThreads, PfLayout<0>::kSmem, stream>>>(mk, mv, qm, p);
+    else if (a.qbits == 8) prefill_kernel<8><<<grid, kPfThreads, PfLayout<8>::kSmem, stream>>>(mk, mv, qm, p);
+    else prefill_kernel<4><<<grid, kPfThreads, PfLayout<4>::kSmem, stream>>>(mk, mv, qm, p);
     SAETTA_CUDA(cudaGetLastError());
     return SAETTA_OK;
 }
 
 } // namespace saetta
-

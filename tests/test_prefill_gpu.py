@@ -4,7 +4,7 @@ Mirrors tests/attention_prefill.rs of the reference: its chunk shapes (partial
 tiles and key blocks), its `spread` inputs and (i % 7) - 3 gate pattern, and its
 2e-3 max-abs bound -- here against the CPU oracle instead of another GPU kernel
 -- plus the benchmark configurations on bfloat16 N(0,1) inputs with partial RoPE,
-a quantised prefix read through its 16-bit copy, and the split-key partials.
+a quantised prefix read in place, and the split-key partials.
 Tolerance: 2e-3 max-abs and 1e-3 relative RMS.
 """
 import numpy as np
@@ -125,10 +125,11 @@ def test_config2_chunk_4096_bf16(oracle):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
-def test_quantised_prefix_reads_through_16bit_copy(oracle, bits):
+def test_quantised_prefix_is_read_in_place(oracle, bits):
     """AttGemm::encode with quant: the chunk's rows are quantised into the cache
-    first (src/prefill.rs:1656-1666), then keys and values are read as the
-    16-bit rounding of s*q+z (src/kv_quant.rs:121-126; keys in q's bfloat16, values binary16)."""
+    first (src/prefill.rs:1656-1666), then the kernel reads the codes per key block and
+    uses keys and values as the binary16 rounding of s*q+z (src/kv_quant.rs:121-126,
+    kernels/attention_rows_q.metal:16-31); bfloat16 queries go in as binary16."""
     import torch
 
     pos, tokens = 1000, 72
@@ -137,7 +138,7 @@ def test_quantised_prefix_reads_through_16bit_copy(oracle, bits):
     cache = sa.GpuKvCache(0, bits, total)
     cache.store_at(dev(k), dev(v), 0, total)
     got = run(torch, q, None, None, qg, pos, tokens, sa.BF16, quant=cache.quant())
-    kr = oracle.round_trip_as_half(k, bits, bf16=True)  # keys in q's type
+    kr = oracle.round_trip_as_half(k, bits)  # keys and values as binary16, the reference's own reading (src/kv_quant.rs:121-126)
     vr = oracle.round_trip_as_half(v, bits)             # values as binary16, the reference's own reading
     check_rows(oracle, got, q, qg, kr, vr, pos, np.arange(tokens))
 
@@ -190,7 +191,7 @@ def test_shape_errors(oracle):
 def test_config4_long_context_chunk_over_8bit_prefix(oracle):
     """A 4096-token chunk at position 131072 on top of a 131072-token 8-bit cache
     (the chunk's own rows quantised into the cache first), bf16 queries.  The
-    oracle is evaluated on a sample of 64 or more rows.  Keys are read as the bf16 rounding of s*q+z, values as binary16."""
+    oracle is evaluated on a sample of 64 or more rows.  Keys and values are read as the binary16 rounding of s*q+z."""
     import torch
 
     pos, tokens, bits = 131072, 4096, 8
@@ -205,7 +206,7 @@ def test_config4_long_context_chunk_over_8bit_prefix(oracle):
         k = torch.randn(n * ROW, device="cuda", generator=g)
         v = torch.randn(n * ROW, device="cuda", generator=g)
         cache.store_at(k, v, p0, n)
-        kr[p0:p0 + n] = oracle.round_trip_as_half(k.cpu().numpy(), bits, bf16=True).reshape(n, ROW)
+        kr[p0:p0 + n] = oracle.round_trip_as_half(k.cpu().numpy(), bits).reshape(n, ROW)
         vr[p0:p0 + n] = oracle.round_trip_as_half(v.cpu().numpy(), bits).reshape(n, ROW)
     q = oracle.round_bf16(oracle.normal(tokens * HEADS * DIM, 41))
     qg = oracle.normal(tokens * HEADS * 2 * DIM, 42)
@@ -220,10 +221,10 @@ def test_config4_long_context_chunk_over_8bit_prefix(oracle):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
-def test_chunks_of_a_prompt_convert_only_their_own_rows(oracle, bits):
-    """A prompt prefilled in chunks over a quantised cache: after `reserve` no encode allocates, every chunk
-    matches the oracle (so the rows an earlier chunk staged are still right), the same calls record into a
-    Plan, and rows rewritten below the next chunk are picked up after `invalidate`."""
+def test_chunks_of_a_prompt_over_a_quantised_cache(oracle, bits):
+    """A prompt prefilled in chunks over a quantised cache, read in place: no encode allocates device memory
+    (there is no 16-bit copy of the cache), every chunk matches the oracle, the same call records into a Plan
+    with or without `reserve`, and rows rewritten below the next chunk are simply seen."""
     import torch
 
     chunks = [(0, 200), (200, 120), (320, 64)]
@@ -232,7 +233,7 @@ def test_chunks_of_a_prompt_convert_only_their_own_rows(oracle, bits):
     cache = sa.GpuKvCache(0, bits, total)
     op = sa.AttGemm(0, 4096, KV)
     op.reserve(total)
-    kr = oracle.round_trip_as_half(k, bits, bf16=True)
+    kr = oracle.round_trip_as_half(k, bits)
     vr = oracle.round_trip_as_half(v, bits)
     kd, vd = dev(k), dev(v)
     torch.cuda.synchronize()
@@ -258,22 +259,22 @@ def test_chunks_of_a_prompt_convert_only_their_own_rows(oracle, bits):
                   stream=plan.stream)
     plan.run()
     check_rows(oracle, out.cpu().numpy().reshape(n, HEADS, DIM), q[sl], qg[gl], kr, vr, pos, np.arange(n))
-    # an op without its scratch refuses to grow it inside a recording
+    # an op that never reserved anything records the same call: nothing has to be allocated
     bare = sa.AttGemm(0, 4096, KV)
     plan2 = sa.Plan(0)
-    with pytest.raises(sa.SaettaError) as e:
-        with plan2.recording():
-            bare.encode(qd, None, None, cache.quant(), gd, out, sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16,
-                        stream=plan2.stream)
-    assert "reserve" in str(e.value)
+    out.zero_()
+    with plan2.recording():
+        bare.encode(qd, None, None, cache.quant(), gd, out, sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16,
+                    stream=plan2.stream)
+    plan2.run()
+    check_rows(oracle, out.cpu().numpy().reshape(n, HEADS, DIM), q[sl], qg[gl], kr, vr, pos, np.arange(n))
 
-    # rows below the chunk rewritten behind the op's back: told so, it converts them again
+    # rows below the chunk rewritten: the next encode reads the cache as it is
     k2 = k.copy()
     k2[:100 * ROW] = oracle.round_bf16(oracle.normal(100 * ROW, 701))
     cache.store_at(dev(k2[:100 * ROW]), vd[:100 * ROW], 0, 100)
-    op.invalidate()
     got = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=op)
-    check_rows(oracle, got, q[sl], qg[gl], oracle.round_trip_as_half(k2, bits, bf16=True), vr, pos, np.arange(n))
+    check_rows(oracle, got, q[sl], qg[gl], oracle.round_trip_as_half(k2, bits), vr, pos, np.arange(n))
 
 
 @pytest.mark.parametrize("quant_bits", [None, 8])
@@ -308,7 +309,7 @@ def test_shards_that_store_only_their_slice(oracle, quant_bits):
     torch.cuda.synchronize()
     got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
     if quant_bits:
-        kr, vr = oracle.round_trip_as_half(k, quant_bits, bf16=True), oracle.round_trip_as_half(v, quant_bits)
+        kr, vr = oracle.round_trip_as_half(k, quant_bits), oracle.round_trip_as_half(v, quant_bits)
     else:
         kr, vr = k, v
     check_rows(oracle, got, q, qg, kr, vr, pos, np.arange(tokens))
@@ -317,3 +318,32 @@ def test_shards_that_store_only_their_slice(oracle, quant_bits):
         op.partial(qd, kd if not quant_bits else None, vd if not quant_bits else None, c.quant() if quant_bits else None,
                    parts[0], p, 100, 200, dtype=sa.BF16, key_base=100)
     assert e.value.code == sa.BAD_SHAPE
+
+
+def test_bfloat16_values_keep_their_binary16_copy_between_chunks(oracle):
+    """A bfloat16 cache: the values go through a binary16 copy (P takes the values' type), kept between the
+    chunks of a prompt -- only rows from the chunk's first row on are converted again.  Rows rewritten below
+    the next chunk behind the op's back are picked up after `invalidate`."""
+    import torch
+
+    total = 256
+    q, k, v, qg = bf16_inputs(oracle, 0, total, 900)
+    op = sa.AttGemm(0, 4096, KV)
+    op.reserve(total)
+    kd, vd = to16(torch, k, sa.BF16), to16(torch, v, sa.BF16)
+
+    def chunk(pos, n, vref):
+        sl = slice(pos * HEADS * DIM, (pos + n) * HEADS * DIM)
+        gl = slice(pos * HEADS * 2 * DIM, (pos + n) * HEADS * 2 * DIM)
+        out = torch.full((n * HEADS * DIM,), float("nan"), dtype=torch.float32, device="cuda")
+        op.encode(to16(torch, q[sl], sa.BF16), kd, vd, None, dev(qg[gl]), out, sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16)
+        torch.cuda.synchronize()
+        return check_rows(oracle, out.cpu().numpy().reshape(n, HEADS, DIM), q[sl], qg[gl], k, vref, pos, np.arange(n))
+
+    chunk(0, 160, v)
+    chunk(160, 96, v)
+    v2 = v.copy()
+    v2[:64 * ROW] = oracle.round_bf16(oracle.normal(64 * ROW, 901))
+    vd[:64 * ROW] = to16(torch, v2[:64 * ROW], sa.BF16)
+    op.invalidate()
+    chunk(160, 96, v2)
