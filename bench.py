@@ -200,10 +200,10 @@ def batch_point(sa, torch, bits, warmup, stream, seqs=64, lo=8192, hi=262144, se
     return {"gbs": nbytes / ms / 1e6, "ms": ms, "tokens": int(lens.sum()), "seqs": seqs}
 
 
-def prefill_point(sa, torch, pos, tokens, warmup, stream, quant_bits=None):
-    """TFLOP/s of one causal chunk (flops = 4*H*D*(t*pos + t(t+1)/2), src/attention_prefill.rs:139-142).  Over a
-    quantised prefix the 16-bit staging copy already holds the prefix, as after the chunk before; every call
-    converts the chunk's own rows again."""
+def prefill_point(sa, torch, pos, tokens, warmup, stream, quant_bits=None, staged=False):
+    """TFLOP/s of one causal chunk (flops = 4*H*D*(t*pos + t(t+1)/2), src/attention_prefill.rs:139-142).  A
+    quantised prefix is read in place; with `staged`, through the op's 16-bit staging copy, which already holds
+    the prefix, as after the chunk before (every call converts the chunk's own rows again)."""
     dev = torch.cuda.current_device()
     total = pos + tokens
     q = torch.randn(tokens * HEADS * DIM, device="cuda").to(torch.bfloat16)
@@ -215,6 +215,7 @@ def prefill_point(sa, torch, pos, tokens, warmup, stream, quant_bits=None):
         cache = sa.GpuKvCache(dev, quant_bits, total)
         fill_cache(sa, torch, cache, total, 77)
         quant = cache.quant()
+        op.stage_quantised(staged)
         op.reserve(total)
         fn = lambda: op.encode(q, None, None, quant, qg, out, p, dtype=sa.BF16, stream=stream)
     else:
@@ -356,6 +357,9 @@ def point_table(sa, torch, stream, s, w):
         "prefill_4k_pos0_bf16": lambda: prefill_point(sa, torch, 0, 4096, w, stream),
         "prefill_4k_pos32k_8bit": lambda: prefill_point(sa, torch, 32768, 4096, 2, stream, quant_bits=8),
         "prefill_4k_pos128k_8bit": lambda: prefill_point(sa, torch, 131072, 4096, 2, stream, quant_bits=8),
+        "prefill_4k_pos32k_4bit": lambda: prefill_point(sa, torch, 32768, 4096, 2, stream, quant_bits=4),
+        "prefill_4k_pos32k_8bit_staged": lambda: prefill_point(sa, torch, 32768, 4096, 2, stream, quant_bits=8, staged=True),
+        "prefill_4k_pos128k_8bit_staged": lambda: prefill_point(sa, torch, 131072, 4096, 2, stream, quant_bits=8, staged=True),
         "e2e_prefill_4k_8bit": lambda: e2e_prefill_point(sa, torch, 4096, 8, w, stream),
     }
 
@@ -755,7 +759,8 @@ def main():
         for name in ["decode_32k_8bit", "decode_64k_8bit", "decode_128k_8bit", "decode_256k_4bit", "decode_128k_f16",
                      "verify_m4_32k_8bit", "batch64_ragged_8bit", "batch64_ragged_4bit", "qmv_8192x2048_5bit_m1",
                      "qmv_8192x2048_5bit_m4", "prep_store_4k_8bit", "prefill_4k_pos0_bf16", "prefill_4k_pos32k_8bit",
-                     "prefill_4k_pos128k_8bit", "e2e_prefill_4k_8bit"]:
+                     "prefill_4k_pos128k_8bit", "prefill_4k_pos32k_8bit_staged", "prefill_4k_pos128k_8bit_staged",
+                     "e2e_prefill_4k_8bit"]:
             try:
                 r = table[name]()
                 if "gbs" in r:

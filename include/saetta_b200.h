@@ -415,9 +415,17 @@ int saetta_att_gemm_reserve(saetta_att_gemm *op, size_t tokens);
  * sequence (not a rewind followed by a new prefill from there, which is covered)
  * says so here, and the next encode converts every row it reads again. */
 int saetta_att_gemm_invalidate(saetta_att_gemm *op);
+/* How encode / partial read an 8/4-bit cache.  Off (the default): in place, per key
+ * block, as the reference's attention_rows_q kernels read it
+ * (kernels/attention_rows_q.metal:16-31,206-344); no 16-bit copy exists.  On: through
+ * the op's 16-bit staging copy, the reference's kv_stage route (src/prefill.rs), of
+ * which each call converts only the rows it does not hold yet: faster over long
+ * prefixes (every row is converted once instead of once per query tile), for 2 KB
+ * of device memory per key and side. */
+int saetta_att_gemm_stage_quantised(saetta_att_gemm *op, int on);
 /* AttGemm::encode: with keys_q/values_q non-NULL the cache is read from those
- * 8/4-bit rows (through a 16-bit copy, as the reference's kv_stage reads it)
- * and keys_dev/values_dev are ignored. */
+ * 8/4-bit rows (see saetta_att_gemm_stage_quantised) and keys_dev/values_dev are
+ * ignored. */
 int saetta_att_gemm_encode(saetta_att_gemm *op, const void *q_dev, int dtype, const void *keys_dev,
                            const void *values_dev, const saetta_quant_rows *keys_q,
                            const saetta_quant_rows *values_q, const float *q_and_gate_dev,

@@ -903,6 +903,12 @@ int saetta_att_gemm_invalidate(saetta_att_gemm *op) {
     return SAETTA_OK;
 }
 
+int saetta_att_gemm_stage_quantised(saetta_att_gemm *op, int on) {
+    if (!op) return fail(SAETTA_ERR_BAD_ARG, "AttGemm: null handle");
+    op->stage_quant = on != 0;
+    return SAETTA_OK;
+}
+
 static int prefill_check(const void *q, int dtype, const saetta_flash_params &p) {
     if (!q) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q is null");
     if (dtype != SAETTA_F16 && dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: dtype");
@@ -949,21 +955,25 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     // rows of the buffers the kernel reads, and the first row of the chunk itself
     const size_t lo = key_lo - key_base, hi = key_hi - key_base;
     const size_t fresh = size_t(p.pos) > key_base ? size_t(p.pos) - key_base : 0;
-    int v_dtype = dtype;
-    const bool in_place = (kq || vq) && p.kv_heads == 2; // the kernel turns the codes into operand tiles itself
+    int v_dtype = dtype, k_dtype = dtype;
+    // in place: the kernel turns the codes into operand tiles itself, per key block
+    const bool in_place = (kq || vq) && p.kv_heads == 2 && !op->stage_quant;
     if (kq || vq) {
         if (!kq || !vq || kq->bits != vq->bits) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: quant needs both sides");
         if (hi > kq->capacity || hi > vq->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: the keys asked for exceed the capacity");
         if (kq->per_token != p.kv_heads * size_t(kGroupsPerHead)) return fail(SAETTA_ERR_BAD_SHAPE, "AttGemm::encode: quant rows of another shape");
     }
     if ((kq || vq) && !in_place) {
-        // Other head counts: the quantised cache is read through a 16-bit copy, as the reference's
-        // kv_stage reads it (src/kv_quant.rs:121-126 semantics).  Keys take q's type; values are staged
-        // as binary16 (exactly the reference's round_trip_as_half), so P is binary16 too and keeps an
-        // 11-bit significand.  Only the rows the copy does not hold yet are dequantised: per chunk of
+        // Other head counts, or a caller who asked for it (saetta_att_gemm_stage_quantised: every query tile
+        // converts the blocks it reads when the codes are read in place, which costs the tensor pipe about a
+        // fifth of its rate; with the copy each row is converted once, for 2 KB per key and side of device
+        // memory): the quantised cache is read through a 16-bit copy, as the reference's
+        // kv_stage reads it (src/kv_quant.rs:121-126 semantics).  Both sides are staged as binary16
+        // (exactly the reference's round_trip_as_half; bfloat16 queries are converted on their way into
+        // tensor memory), so P is binary16 too and keeps an 11-bit significand.  Only the rows the copy does not hold yet are dequantised: per chunk of
         // a long prompt, the chunk's own rows.
-        if (int rc = stage_rows(op, 0, kq->data, dtype, lo, hi, fresh, st, [&](size_t first, size_t n) {
-                return launch_kv_dequantize(kq, op->stage_k, dtype, first, n, st);
+        if (int rc = stage_rows(op, 0, kq->data, SAETTA_F16, lo, hi, fresh, st, [&](size_t first, size_t n) {
+                return launch_kv_dequantize(kq, op->stage_k, SAETTA_F16, first, n, st);
             }))
             return rc;
         if (int rc = stage_rows(op, 1, vq->data, SAETTA_F16, lo, hi, fresh, st, [&](size_t first, size_t n) {
@@ -971,7 +981,7 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
             }))
             return rc;
         keys = op->stage_k, values = op->stage_v;
-        v_dtype = SAETTA_F16;
+        k_dtype = v_dtype = SAETTA_F16;
     }
     if (!in_place && (!keys || !values)) return fail(SAETTA_ERR_BAD_ARG, "AttGemm::encode: keys or values null");
     if (!(kq || vq) && dtype == SAETTA_BF16) {
@@ -990,6 +1000,7 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
     PrefillArgs a{q, keys, values, dtype, v_dtype, q_and_gate, out, part, p.heads, p.kv_heads, p.pos, p.tokens,
                   uint32_t(key_lo), uint32_t(key_hi), p.scale};
     a.key_base = uint32_t(key_base);
+    a.k_dtype = k_dtype;
     if (in_place) {
         // 8/4-bit rows are read where they are, per key block (kernels/attention_rows_q.metal:16-31): no
         // 16-bit copy of the cache, nothing to reserve

@@ -79,6 +79,7 @@ struct saetta_att_gemm {
     // encoded that an earlier call already converted are not converted again.
     void *stage_k = nullptr, *stage_v = nullptr;
     size_t stage_tokens = 0; // rows each copy has room for
+    bool stage_quant = false; // read 8/4-bit caches through the 16-bit copy instead of in place
     struct Staged {
         const void *src = nullptr; // the buffer the rows came from (identity of the cache side)
         int dtype = 0;
@@ -234,6 +235,7 @@ struct PrefillArgs {
                              // that stores only its own slice of the sequence
     // a quantised cache read in place (qbits 8 or 4; k and v above are then unused): codes, scales, biases
     int qbits = 0;
+    int k_dtype = -1;        // of k when it differs from q's (binary16 keys under bfloat16 queries: q is converted on the way in)
     const void *qk = nullptr, *qv = nullptr, *qks = nullptr, *qkz = nullptr, *qvs = nullptr, *qvz = nullptr;
 };
 int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream);

@@ -96,7 +96,7 @@ struct PfParams {
     uint32_t splits;      // each tile's key range is cut into this many work items (>1: partials per split)
     uint32_t part_stride; // floats between the partial buffers of consecutive splits
     uint32_t key_base;    // global position of row 0 of the K / V buffers
-    uint32_t q_bf16;      // q arrives as bfloat16 but the operands are binary16 (quantised cache): converted on the way in
+    uint32_t q_bf16;      // q arrives as bfloat16 but the key operands are binary16 (a quantised cache): converted on the way in
 };
 
 // ----------------------------------------------------------------- PTX wrappers
@@ -263,11 +263,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        // with a quantised cache one warpgroup (4 warps) does the tile I/O and one fills the operand stages
-        mbar_init(q_full, QBITS ? 4 : 8), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, QBITS ? 4 : 8);
+                mbar_init(q_full, 8), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 8);
+        // (with a quantised cache the eight tile I/O warps fill the operand stages)
         for (int s = 0; s < NST; s++)
-            mbar_init(&k_full[s], QBITS ? 4 : 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], QBITS ? 4 : 1), mbar_init(&v_empty[s], 1);
-        for (int s = 0; s < L::kCodeStages; s++) mbar_init(&code_full[s], 1), mbar_init(&code_empty[s], 4);
+            mbar_init(&k_full[s], QBITS ? 8 : 1), mbar_init(&k_empty[s], 1), mbar_init(&v_full[s], QBITS ? 8 : 1), mbar_init(&v_empty[s], 1);
+        for (int s = 0; s < L::kCodeStages; s++) mbar_init(&code_full[s], 1), mbar_init(&code_empty[s], 8);
         for (int s = 0; s < 2; s++)
             mbar_init(&s_full[s], 1), mbar_init(&p_full[s], 4), mbar_init(&pv_done[s], 1), mbar_init(&lm_full[s], 4);
         *abort_flag = 0;
@@ -504,36 +504,58 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (lane == 0) mbar_arrive(&lm_full[tc & 1]);
             tc++;
         }
-    } else if (QBITS != 0 && warp < 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
-        // ------------------------------------------------------------ codes -> binary16 operand tiles
-        // Per 64-key block: wait for its codes, wait for a free operand stage, write K (then V) as
-        // s * c + z rounded once to binary16 -- the code as an exact binary16 integer (byte permute onto
-        // the magic 1024, minus 1024), then one fused multiply-add with the group's scale and bias -- into
-        // the four 64-dim slabs of the stage in the tensor cores' 128-byte-swizzled layout, and hand the
-        // stage to the MMA warps.  A lane reads 16 bytes of codes; eight lanes cover 128 bytes of a key's
-        // row, a warp four keys at a time, the four warps 16 keys each.
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        // ------------------------------------------------------------ tile I/O: Q rows in, results out
+        // Per tile these warps write its Q rows into tensor memory and, at its end, scale and gate
+        // O out to memory.  The Q rows of tile k+1 go in as soon as the last S of tile k has been
+        // computed, before tile k's epilogue, so the MMA warp never waits for a tile change.
+        // Two threads per row: the warps of the first tile I/O warpgroup take dims 0..127 of Q, the
+        // gate and O, those of the second dims 128..255.
+        // With a quantised cache the same eight warps also make the operand tiles, between a tile's Q
+        // rows and its epilogue: per 64-key block they wait for its codes and for a free operand stage,
+        // write K (then V) as s * c + z rounded once to binary16 -- the code as an exact binary16
+        // integer (byte permute onto the magic 1024, minus 1024), then one fused multiply-add with the
+        // group's scale and bias -- into the four 64-dim slabs of the stage in the tensor cores'
+        // 128-byte-swizzled layout, and hand the stage to the MMA warps.  A lane reads 16 bytes of
+        // codes; eight lanes cover 128 bytes of a key's row, a warp four keys at a time, the eight
+        // warps 8 keys each.  (Four warps of their own for this, one per scheduler, were measured at
+        // 2.3 us per block against the 1.1 us the MMAs take: chains of dependent instructions with
+        // nothing to switch to.)
+        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t half_lo = warp >= 8 ? 1u : 0u;
         const uint32_t cw = warp - 4;
         constexpr uint32_t kMagic = 0x64646464u, k1024 = 0x64006400u;
-        uint32_t g = 0;
-        bool ok = true;
-        PfTile t;
+        uint32_t cg = 0; // blocks converted so far (the copy warp's and the MMA warps' count)
         auto convert_side = [&](const uint8_t *codes, const uint8_t *sc, const uint8_t *bi, uint8_t *dst, uint32_t kv) {
             constexpr int QB = QBITS ? QBITS : 8;              // (this role is never taken with a 16-bit cache)
             constexpr int kValsPerLoad = 128 / QB;             // values in a lane's 16 bytes: 16 or 32
             constexpr int kLoadsPerRow = kDim * QB / 8 / 128;  // 128-byte pieces of a key's row: 2 or 1
             const uint32_t col = lane & 7;
+            // every load of the side first: the compiler may not move a shared-memory load above the
+            // stores of the piece before (for all it knows they alias), and one piece after the other
+            // is a chain of latencies
+            uint4 cin[2][kLoadsPerRow];
+            uint32_t sin[2][kLoadsPerRow], zin[2][kLoadsPerRow];
 #pragma unroll
-            for (int it = 0; it < 4; it++) {
-                const uint32_t key = cw * 16 + it * 4 + (lane >> 3);
+            for (int it = 0; it < 2; it++) {
+                const uint32_t key = cw * 8 + it * 4 + (lane >> 3);
 #pragma unroll
                 for (int piece = 0; piece < kLoadsPerRow; piece++) {
-                    const uint4 cw4 = *reinterpret_cast<const uint4 *>(codes + key * L::kCodeRow + piece * 128 + col * 16);
+                    const uint32_t G = ((piece * 8 + col) * kValsPerLoad) >> 6;
+                    cin[it][piece] = *reinterpret_cast<const uint4 *>(codes + key * L::kCodeRow + piece * 128 + col * 16);
+                    sin[it][piece] = *reinterpret_cast<const uint16_t *>(sc + key * 16 + (kv * 4 + G) * 2);
+                    zin[it][piece] = *reinterpret_cast<const uint16_t *>(bi + key * 16 + (kv * 4 + G) * 2);
+                }
+            }
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+                const uint32_t key = cw * 8 + it * 4 + (lane >> 3);
+#pragma unroll
+                for (int piece = 0; piece < kLoadsPerRow; piece++) {
+                    const uint4 cw4 = cin[it][piece];
                     const uint32_t d0 = (piece * 8 + col) * kValsPerLoad; // first dim of these values
-                    const uint32_t G = d0 >> 6;
-                    const uint32_t sraw = *reinterpret_cast<const uint16_t *>(sc + key * 16 + (kv * 4 + G) * 2);
-                    const uint32_t zraw = *reinterpret_cast<const uint16_t *>(bi + key * 16 + (kv * 4 + G) * 2);
-                    const uint32_t s2 = sraw | (sraw << 16), z2 = zraw | (zraw << 16);
+                    const uint32_t s2 = prmt(sin[it][piece], 0u, 0x1010), z2 = prmt(zin[it][piece], 0u, 0x1010);
                     const uint32_t w4[4] = {cw4.x, cw4.y, cw4.z, cw4.w};
                     uint32_t h[kValsPerLoad / 2]; // pairs of consecutive dims
                     if (QB == 8) {
@@ -553,50 +575,42 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                             h[4 * j + 3] = hfma2_u32(hsub2_u32(prmt(n47, kMagic, 0x4342), k1024), s2, z2);
                         }
                     }
-                    // 16-byte chunks (8 dims) of the key's 128-byte row in slab d / 64, swizzled by the key
+                    // 16-byte chunks (8 dims) of the key's 128-byte row in slab d / 64, swizzled by the key.
+                    // The eight lanes that share a key store chunks of different slabs at once; which of its
+                    // chunks a lane stores first is rotated by the lane's slab, so that the eight stores of
+                    // a request fall into eight different 16-byte bank groups (unrotated, lanes of different
+                    // slabs write the same chunk number: the stores, the largest user of shared-memory
+                    // bandwidth here, then cost twice or four times as much).
                     uint8_t *rowp = dst + (d0 >> 6) * kKChunk + key * 128;
+                    constexpr int NC = kValsPerLoad / 8; // chunks per lane: 2 or 4
+                    const uint32_t rot = QB == 8 ? (col >> 2) : (col >> 1); // this lane's slab among those of the request
+                    if (NC == 2) {
+                        if (rot & 1) {
 #pragma unroll
-                    for (int c = 0; c < kValsPerLoad / 8; c++) {
-                        const uint32_t chunk = ((d0 & 63) >> 3) + c;
+                            for (int e = 0; e < 4; e++) { const uint32_t x = h[e]; h[e] = h[4 + e]; h[4 + e] = x; }
+                        }
+                    } else {
+                        if (rot & 1) { // rotate the four chunks left by one
+#pragma unroll
+                            for (int e = 0; e < 4; e++) { const uint32_t x = h[e]; h[e] = h[4 + e]; h[4 + e] = h[8 + e]; h[8 + e] = h[12 + e]; h[12 + e] = x; }
+                        }
+                        if (rot & 2) { // ... by two
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const uint32_t x = h[e], y = h[4 + e];
+                                h[e] = h[8 + e], h[4 + e] = h[12 + e], h[8 + e] = x, h[12 + e] = y;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < NC; c++) { // register set c now holds the lane's chunk (c + rot) % NC
+                        const uint32_t chunk = ((d0 & 63) >> 3) + ((c + rot) & (NC - 1));
                         *reinterpret_cast<uint4 *>(rowp + ((chunk ^ (key & 7)) << 4)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
                     }
                 }
             }
         };
-        for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
-            if (!t.nb) continue;
-            for (uint32_t b = 0; b < t.nb; b++, g++) {
-                const uint32_t st = g % NST, ph = (g / NST) & 1, cs = g & 1, cph = (g >> 1) & 1;
-                const uint8_t *code = sCode + cs * L::kCodeStage;
-                if (!mbar_wait(&code_full[cs], cph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
-                if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
-                convert_side(code, code + 2 * L::kCodeSide, code + 2 * L::kCodeSide + L::kParamArr, sK + st * kKBytes, t.kv);
-                fence_async_smem(); // the tensor cores read the stage through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&k_full[st]);
-                if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
-                convert_side(code + L::kCodeSide, code + 2 * L::kCodeSide + 2 * L::kParamArr, code + 2 * L::kCodeSide + 3 * L::kParamArr,
-                             sV + st * kKBytes, t.kv);
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&v_full[st]);
-                    mbar_arrive(&code_empty[cs]);
-                }
-            }
-        }
-    } else {
-        if constexpr (QBITS != 0) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
-        else asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
-        // ------------------------------------------------------------ tile I/O: Q rows in, results out
-        // Per tile these warps write its Q rows into tensor memory and, at its end, scale and gate
-        // O out to memory.  The Q rows of tile k+1 go in as soon as the last S of tile k has been
-        // computed, before tile k's epilogue, so the MMA warp never waits for a tile change.
-        // 16-bit cache: two threads per row, the warps of the first tile I/O warpgroup take dims 0..127 of
-        // Q, the gate and O, those of the second dims 128..255.  Quantised cache: the second warpgroup
-        // alone, one thread per row, one half after the other.
-        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
-        const uint32_t half_lo = QBITS ? 0u : (warp >= 8 ? 1u : 0u), half_hi = QBITS ? 2u : half_lo + 1;
+
         const uint32_t lane_addr = (quarter * 32) << 16;
         struct RowOf {
             uint32_t tok;
@@ -620,11 +634,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 const RowOf r = row_of(t);
                 if (r.live && r.part) {
                     float *dst = r.part + r.rh * kPartStride;
-                    for (uint32_t d = half_lo * 128; d < half_hi * 128; d++) dst[d] = 0.f;
+                    for (uint32_t d = half_lo * 128; d < half_lo * 128 + 128; d++) dst[d] = 0.f;
                     if (!half_lo) dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
                 }
             }
             return false;
+        };
+        auto convert_item = [&](const PfTile &t) -> bool {
+            for (uint32_t b = 0; b < t.nb; b++, cg++) {
+                const uint32_t st = cg % NST, ph = (cg / NST) & 1, cs = cg & 1, cph = (cg >> 1) & 1;
+                const uint8_t *code = sCode + cs * L::kCodeStage;
+                if (!mbar_wait(&code_full[cs], cph, abort_flag)) { give_up(kStatusFullTimeout); return false; }
+                if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); return false; }
+                convert_side(code, code + 2 * L::kCodeSide, code + 2 * L::kCodeSide + L::kParamArr, sK + st * kKBytes, t.kv);
+                fence_async_smem(); // the tensor cores read the stage through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&k_full[st]);
+                if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); return false; }
+                convert_side(code + L::kCodeSide, code + 2 * L::kCodeSide + 2 * L::kParamArr, code + 2 * L::kCodeSide + 3 * L::kParamArr,
+                             sV + st * kKBytes, t.kv);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&v_full[st]);
+                    mbar_arrive(&code_empty[cs]);
+                }
+            }
+            return true;
         };
         auto load_q = [&](const PfTile &t, uint32_t k) -> bool {
             const RowOf r = row_of(t);
@@ -633,7 +669,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (row_live && p.out) { // pull this row's gate values towards L2 for the epilogue
                 const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + rh * 2 * kDim + kDim + half_lo * 128);
 #pragma unroll
-                for (int j = 0; j < (QBITS ? 8 : 4); j++) prefetch_l2(gpf + j * 128);
+                for (int j = 0; j < 4; j++) prefetch_l2(gpf + j * 128);
             }
             // this thread's part of its Q row into tensor memory (two values per column), once the
             // MMAs of the tile before no longer read the old one.  The row does not depend on that
@@ -644,7 +680,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 uint4 qv[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) qv[j] = row_live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
-                if (QBITS != 0 && p.q_bf16) { // bfloat16 queries over binary16 operand tiles: exact unless outside binary16's range
+                if (p.q_bf16) { // bfloat16 queries over binary16 operand tiles: exact unless outside binary16's range
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         uint32_t *w = reinterpret_cast<uint32_t *>(&qv[j]);
@@ -669,11 +705,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
                 return true;
             };
-            if constexpr (QBITS != 0) {
-                if (!q_half(0) || !q_half(1)) return false;
-            } else {
-                if (!q_half(half_lo)) return false;
-            }
+            if (!q_half(half_lo)) return false;
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -730,12 +762,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     }
                 }
             };
-            if constexpr (QBITS != 0) {
-                o_half(0, false);
-                o_half(1, true);
-            } else {
-                o_half(half_lo, true);
-            }
+            o_half(half_lo, true);
             if (row_live && part && !half_lo) {
                 part[rh * kPartStride + kPartM] = m_ref;
                 part[rh * kPartStride + kPartL] = l;
@@ -747,6 +774,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         bool have = next_item(round, cur);
         if (have && !load_q(cur, 0)) have = false;
         while (have) {
+            if constexpr (QBITS != 0)
+                if (!convert_item(cur)) break;
             const bool more = next_item(round, nxt);
             if (more && !load_q(nxt, k + 1)) break;
             if (!epilogue(cur, k)) break;
@@ -798,11 +827,13 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
     if (a.key_base % kBN || a.key_base > a.key_lo) return fail(SAETTA_ERR_BAD_SHAPE, "prefill attention: the cache's first row must sit at a multiple of 64 at or below the first key");
     // rows of the buffers the kernel may touch: up to the last key it is asked for (copies past that read zeros)
     const cuuint64_t keys_total = std::max<cuuint64_t>(1, std::min<cuuint64_t>(cuuint64_t(a.pos) + a.tokens, a.key_hi) - std::min<cuuint64_t>(a.key_base, a.key_hi));
+    const int k_dtype = quant ? SAETTA_F16 : (a.k_dtype < 0 ? a.dtype : a.k_dtype);
+    if (k_dtype == SAETTA_BF16 && a.dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: bfloat16 keys need bfloat16 queries");
     CUtensorMap mk, mv;
     PfQuantMaps qm;
     const cuuint32_t el[3] = {1, 1, 1};
     if (!quant) {
-        const CUtensorMapDataType dt = a.dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const CUtensorMapDataType dt = k_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         const CUtensorMapDataType dtv = a.v_dtype == SAETTA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         for (int side = 0; side < 2; side++) {
             const cuuint64_t dims[3] = {cuuint64_t(kDim), a.kv_heads, keys_total};
@@ -841,10 +872,10 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
         mk = mv = qm.kc; // not read
     }
     // operands: binary16 throughout over a quantised cache (bfloat16 queries are converted on the way in)
-    const uint32_t fmt = quant ? 0u : (a.dtype == SAETTA_BF16 ? 1u : 0u), v_fmt = quant ? 0u : (a.v_dtype == SAETTA_BF16 ? 1u : 0u);
+    const uint32_t fmt = k_dtype == SAETTA_BF16 ? 1u : 0u, v_fmt = quant ? 0u : (a.v_dtype == SAETTA_BF16 ? 1u : 0u);
     PfParams p{a.q, a.q_and_gate, a.out, a.part, status, a.heads, a.kv_heads, a.pos, a.tokens, a.key_lo, a.key_hi,
                a.scale * kLog2ePf, fmt, v_fmt, a.splits ? a.splits : 1u, uint32_t(size_t(a.tokens) * a.heads * kPartStride), a.key_base,
-               quant && a.dtype == SAETTA_BF16 ? 1u : 0u};
+               a.dtype == SAETTA_BF16 && !fmt ? 1u : 0u};
     int dev = 0;
     SAETTA_CUDA(cudaGetDevice(&dev));
     const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads * (a.splits ? a.splits : 1u);

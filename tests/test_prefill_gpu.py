@@ -277,6 +277,48 @@ def test_chunks_of_a_prompt_over_a_quantised_cache(oracle, bits):
     check_rows(oracle, got, q[sl], qg[gl], oracle.round_trip_as_half(k2, bits), vr, pos, np.arange(n))
 
 
+@pytest.mark.parametrize("bits", [8, 4])
+def test_quantised_cache_through_the_staging_copy(oracle, bits):
+    """The other route to a quantised cache (kv_stage): with `stage_quantised` the op reads its 16-bit copy, of
+    which every call converts only the rows it does not hold yet.  Same results as in place; the copy is
+    allocated by `reserve`, and an encode that would have to grow it cannot be recorded."""
+    import torch
+
+    chunks = [(0, 200), (200, 120), (320, 64)]
+    total = 384
+    q, k, v, qg = bf16_inputs(oracle, 0, total, 710)
+    cache = sa.GpuKvCache(0, bits, total)
+    op = sa.AttGemm(0, 4096, KV)
+    op.stage_quantised()
+    op.reserve(total)
+    kr = oracle.round_trip_as_half(k, bits)
+    vr = oracle.round_trip_as_half(v, bits)
+    kd, vd = dev(k), dev(v)
+    in_place = sa.AttGemm(0, 4096, KV)
+    for pos, n in chunks:
+        cache.store_at(kd[pos * ROW:(pos + n) * ROW], vd[pos * ROW:(pos + n) * ROW], pos, n)
+        sl = slice(pos * HEADS * DIM, (pos + n) * HEADS * DIM)
+        gl = slice(pos * HEADS * 2 * DIM, (pos + n) * HEADS * 2 * DIM)
+        got = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=op)
+        check_rows(oracle, got, q[sl], qg[gl], kr, vr, pos, np.arange(n))
+        same = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=in_place)
+        # both routes feed the tensor cores the same binary16 operands
+        assert np.abs(got - same).max() <= 1e-5 * max(1.0, np.abs(same).max())
+    bare = sa.AttGemm(0, 4096, KV)
+    bare.stage_quantised()
+    pos, n = chunks[-1]
+    sl = slice(pos * HEADS * DIM, (pos + n) * HEADS * DIM)
+    out = torch.zeros(n * HEADS * DIM, device="cuda")
+    plan = sa.Plan(0)
+    with pytest.raises(sa.SaettaError):
+        with plan.recording():
+            bare.encode(to16(torch, q[sl], sa.BF16), None, None, cache.quant(), dev(qg[:n * HEADS * 2 * DIM]), out,
+                        sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16, stream=plan.stream)
+    bare.stage_quantised(False)
+    with pytest.raises(sa.SaettaError):
+        sa._check(sa.lib().saetta_att_gemm_stage_quantised(None, 1))
+
+
 @pytest.mark.parametrize("quant_bits", [None, 8])
 def test_shards_that_store_only_their_slice(oracle, quant_bits):
     """Split-KV prefill where every shard STORES only its own keys: row 0 of shard r's cache is the key at
