@@ -310,10 +310,11 @@ def test_quantised_cache_through_the_staging_copy(oracle, bits):
     sl = slice(pos * HEADS * DIM, (pos + n) * HEADS * DIM)
     out = torch.zeros(n * HEADS * DIM, device="cuda")
     plan = sa.Plan(0)
+    qd, gd = to16(torch, q[sl], sa.BF16), dev(qg[:n * HEADS * 2 * DIM])
     with pytest.raises(sa.SaettaError):
         with plan.recording():
-            bare.encode(to16(torch, q[sl], sa.BF16), None, None, cache.quant(), dev(qg[:n * HEADS * 2 * DIM]), out,
-                        sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16, stream=plan.stream)
+            bare.encode(qd, None, None, cache.quant(), gd, out, sa.FlashParams(HEADS, KV, pos, n, 1.0 / 16.0), dtype=sa.BF16,
+                        stream=plan.stream)
     bare.stage_quantised(False)
     with pytest.raises(sa.SaettaError):
         sa._check(sa.lib().saetta_att_gemm_stage_quantised(None, 1))
