@@ -351,7 +351,9 @@ int saetta_merge_partials(int device, const float *parts_dev, size_t ranks, size
  * on every rank.  The sequence counter lives on the device, so the launches can
  * sit in a captured CUDA graph.  The wait for a peer is bounded (about a
  * second); saetta_peer_group_status reports a peer that never published.  All
- * ranks must perform the same number of exchanges. */
+ * ranks must perform the same number of exchanges, and ONE exchange is outstanding
+ * per group at a time: a second publish before the collect of the first reuses its
+ * number and overwrites it. */
 typedef struct saetta_peer_group saetta_peer_group;
 int saetta_peer_group_create(int device, int rank, int world, size_t rows_max, size_t heads,
                              uint8_t handle_out[64], saetta_peer_group **out);
@@ -389,6 +391,14 @@ int saetta_decode_exchange_cache(saetta_decode *op, size_t m, const float *q_dev
                                  uint32_t row_step, const float *q_and_gate_dev, float *out_dev,
                                  const saetta_token_params *params_dev, void *stream);
 int saetta_peer_group_status(saetta_peer_group *g, void *stream, uint32_t *status);
+/* Recovery after a collect that gave up, which leaves the ranks' exchange counters
+ * apart (every later collect would time out too) and the status word set.  Call it
+ * on EVERY rank with the same `seq`, between two host barriers: the first after each
+ * rank's stream has drained (no exchange in flight anywhere), the second before the
+ * next exchange.  It empties this rank's mailbox, sets both of its counters to `seq`
+ * (the next exchange is number seq + 1) and clears its status word.  A CUDA graph
+ * recorded before the reset stays valid: the counters are read on the device. */
+int saetta_peer_group_reset(saetta_peer_group *g, uint32_t seq, void *stream);
 
 /* ------------------------------------------------------------------ prefill
  * src/attention_prefill.rs:39-72 `encode` and src/attention_gemm.rs:93-363

@@ -146,6 +146,7 @@ SYMBOLS = {
     "saetta_decode_publish_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P]),
     "saetta_decode_exchange_cache": (_I, [_P, _Z, _P, _P, _P, _U32, _P, _P, _P, _P]),
     "saetta_peer_group_status": (_I, [_P, _P, C.POINTER(_U32)]),
+    "saetta_peer_group_reset": (_I, [_P, C.c_uint32, _P]),
     "saetta_att_gemm_create": (_I, [_I, _Z, _Z, _PP]),
     "saetta_att_gemm_destroy": (None, [_P]),
     "saetta_att_gemm_reserve": (_I, [_P, _Z]),
@@ -494,6 +495,10 @@ class PeerGroup:
         s = C.c_uint32()
         _check(lib().saetta_peer_group_status(self.h, _stream(stream), C.byref(s)))
         return s.value
+
+    def reset(self, seq=0, stream=None):
+        """After a collect that gave up: on every rank, the same `seq`, between two host barriers."""
+        _check(lib().saetta_peer_group_reset(self.h, seq, _stream(stream)))
 
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:

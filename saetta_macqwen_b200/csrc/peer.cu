@@ -261,4 +261,23 @@ int saetta_peer_group_status(saetta_peer_group *g, void *stream, uint32_t *statu
     return SAETTA_OK;
 }
 
+// After a collect gave up, the ranks' counters differ (the one that waited counts the exchange as done, the
+// one that stayed away never sent it), so every later exchange would use different numbers and slots.
+// This puts one rank's group back: its own mailbox emptied (number 0 matches no exchange), both
+// counters at `seq`, the status word cleared.  Host-side only; nothing of it runs on a peer's memory.
+int saetta_peer_group_reset(saetta_peer_group *g, uint32_t seq, void *stream) {
+    if (!g) return fail(SAETTA_ERR_BAD_ARG, "peer reset: null handle");
+    DeviceGuard guard(g->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    SAETTA_CUDA(cudaStreamSynchronize(st));
+    SAETTA_CUDA(cudaMemsetAsync(g->mailbox, 0, g->words_offset(), st));
+    uint32_t *words = group_words(g);
+    const uint32_t counters[2] = {seq, seq};
+    static_assert(kSeqDoneWord == 0 && kSeqSentWord == 1, "the two counters are set with one copy");
+    SAETTA_CUDA(cudaMemcpyAsync(words, counters, sizeof(counters), cudaMemcpyHostToDevice, st));
+    SAETTA_CUDA(cudaMemsetAsync(words + kStatusWord, 0, 4, st));
+    SAETTA_CUDA(cudaStreamSynchronize(st));
+    return SAETTA_OK;
+}
+
 } // extern "C"

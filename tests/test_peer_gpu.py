@@ -151,6 +151,19 @@ def _rank_with_absent_peer(rank, world, port, out_q):
         x = torch.ones(8, device="cuda")
         result = (result[0], result[1] and float(x.sum()) == 8.0)
     dist.barrier()
+    # recovery, on the host: the ranks' exchange counters now differ (rank 0 counted the exchange, rank 1
+    # never sent it); every rank resets its group to the same number between two barriers, and the next
+    # exchange goes through
+    torch.cuda.synchronize()
+    group.reset(10)
+    dist.barrier()
+    out.fill_(7.0)
+    assert rt.cudaMemcpy(ctypes.c_void_p(group.staging), ctypes.c_void_p(part.data_ptr()), part.numel() * 4, 3) == 0
+    group.merge(1, qg, out)
+    torch.cuda.synchronize()
+    recovered = group.status() == 0 and bool(torch.allclose(out, torch.full_like(out, 0.25)))
+    result = (result[0], result[1] and recovered)
+    dist.barrier()
     out_q.put((rank, result))
     dist.destroy_process_group()
 
@@ -158,7 +171,8 @@ def _rank_with_absent_peer(rank, world, port, out_q):
 def test_collect_gives_up_when_a_peer_stays_away():
     """Failure detection without a fault: rank 1 sits out an exchange (on the host, between steps); rank
     0's collect polls words nobody writes, runs out of its bounded wait (about a second), sets the status
-    word and leaves `out` alone; its context stays usable."""
+    word and leaves `out` alone; its context stays usable.  Then both ranks reset their groups (host side,
+    between barriers) and one more exchange succeeds."""
     import torch
     import torch.multiprocessing as mp
 
