@@ -278,11 +278,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
             const Segment s = load_segment(si);
             const uint32_t n_row = min(s.kv_len + row * a.row_step, a.capacity); // keys this row sees
 
-            // Query fragments of head kv*8+g: 16 dims per group, scaled by log2(e)/16,
-            // split into two halves; and the group sums for the bias term.
-            uint32_t qh[4][8], ql[4][8];
-            uint32_t qza0 = 0, qza1 = 0;
-            float qoff[4]; // per group: what the code offsets (1024, and 64 for high nibbles) add to q.c
+            // Query fragments of head kv*8+g: 16 dims per group, scaled by log2(e)/16 and rounded to binary16
+            // (the B operand of the score product, as in the several-row path); what the code offsets add to
+            // q.c per group, for the two heads of this lane's score columns; the group sums for the bias term.
+            uint32_t qh[4][8];
+            uint32_t qzb = 0;
+            float qoff2[4][2];
             {
                 float qs[4];
 #pragma unroll
@@ -293,15 +294,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                         const float4 v = qraw[G][c];
                         x[4 * c] = v.x, x[4 * c + 1] = v.y, x[4 * c + 2] = v.z, x[4 * c + 3] = v.w;
                     }
-                    float hi[16], lo[16], sum = 0.f, off = 0.f;
+                    float hi[16], sum = 0.f, off = 0.f;
 #pragma unroll
                     for (int d = 0; d < 16; d++) {
-                        x[d] *= kLog2e * 0.0625f;
-                        hi[d] = __half2float(__float2half_rn(x[d]));
-                        lo[d] = __half2float(__float2half_rn(x[d] - hi[d]));
-                        sum += x[d];
+                        hi[d] = __half2float(__float2half_rn(x[d] * (kLog2e * 0.0625f)));
+                        sum += hi[d];
                         // 8-bit: every code rides on 1024; 4-bit: even dims (low nibbles) on 1024, odd on 64
-                        off += (hi[d] + lo[d]) * ((BITS == 4 && (d & 1)) ? 64.f : 1024.f);
+                        off += hi[d] * ((BITS == 4 && (d & 1)) ? 64.f : 1024.f);
                     }
 #pragma unroll
                     for (int j = 0; j < 4; j++)
@@ -309,21 +308,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                         for (int r = 0; r < 2; r++) {
                             const int d0 = q_dim<BITS>(j, r, 0), d1 = q_dim<BITS>(j, r, 1);
                             qh[G][2 * j + r] = pack_half2(hi[d0], hi[d1]);
-                            ql[G][2 * j + r] = pack_half2(lo[d0], lo[d1]);
                         }
                     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                     off += __shfl_xor_sync(0xffffffffu, off, 1);
                     off += __shfl_xor_sync(0xffffffffu, off, 2);
                     qs[G] = sum;
-                    qoff[G] = off;
+                    qoff2[G][0] = __shfl_sync(0xffffffffu, off, 8 * i), qoff2[G][1] = __shfl_sync(0xffffffffu, off, 8 * i + 4);
                 }
-                // A fragment of the bias-term MMA: row g = high halves of the group sums of head g,
-                // row g+8 = low halves; k-slots 0..3 = groups (lanes i < 2 hold two groups each).
-                const float s0 = i == 0 ? qs[0] : qs[2], s1 = i == 0 ? qs[1] : qs[3];
+                // B fragment of the bias-term MMA, column g = head g: k-slots 0..3 = the high halves of the
+                // four group sums (lanes i = 0, 1 hold two each), k-slots 4..7 = their low halves (i = 2, 3).
+                const float s0 = (i & 1) ? qs[2] : qs[0], s1 = (i & 1) ? qs[3] : qs[1];
                 const float h0 = __half2float(__float2half_rn(s0)), h1 = __half2float(__float2half_rn(s1));
-                qza0 = i < 2 ? pack_half2(h0, h1) : 0u;
-                qza1 = i < 2 ? pack_half2(s0 - h0, s1 - h1) : 0u;
+                qzb = i < 2 ? pack_half2(h0, h1) : pack_half2(s0 - h0, s1 - h1);
             }
 
             float O[16][4];
@@ -351,63 +348,72 @@ __global__ void __launch_bounds__(kThreads, 1) decode_quant_kernel(const DecodeA
                     const bool partial = tok0 + kSub > n_row;
                     const int lt = sub * kSub; // token offset inside the stage
 
-                    // ------------------------------------------------ scores S[head][token]
-                    // MMA rows 0..7 = high halves of the 8 query heads, rows 8..15 = their low halves;
-                    // columns = 8 tokens.  Lane (g, i) feeds token g of each 8-token tile and owns
-                    // head g at tokens 2i, 2i+1.
+                    // ------------------------------------------------ scores S[token][head], then transposed
+                    // One MMA row per token (16 of them), one column per query head, 16 dims per instruction:
+                    // the key codes are the A operand (lane (g, i) feeds tokens g and g+8), the query the B
+                    // operand.  Half the instructions of a product with the heads as rows, whose rows 8..15 had
+                    // nothing better to hold than the queries' low halves.
                     float S[2][2];
-                    const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
-#pragma unroll
-                    for (int nt = 0; nt < 2; nt++) {
-                        const int trow = lt + nt * 8 + g;          // token this lane loads
-                        const int tc0 = lt + nt * 8 + 2 * i;       // tokens of this lane's columns
-                        const uint2 sK0 = *reinterpret_cast<const uint2 *>(sg + St::kKs + tc0 * St::kParamRow + kv * 8);
-                        const uint2 sK1 = *reinterpret_cast<const uint2 *>(sg + St::kKs + (tc0 + 1) * St::kParamRow + kv * 8);
-                        const float2 sKf0[2] = {h2f2(sK0.x), h2f2(sK0.y)}, sKf1[2] = {h2f2(sK1.x), h2f2(sK1.y)};
-                        float s_a = 0.f, s_b = 0.f;
+                    {
+                        const uint8_t *kc = sg + St::kK + kv * (kDim * BITS / 8);
+                        const int tA = lt + g, tB = tA + 8;
+                        const uint2 sKA = *reinterpret_cast<const uint2 *>(sg + St::kKs + tA * St::kParamRow + kv * 8);
+                        const uint2 sKB = *reinterpret_cast<const uint2 *>(sg + St::kKs + tB * St::kParamRow + kv * 8);
+                        const float2 sA[2] = {h2f2(sKA.x), h2f2(sKA.y)}, sB[2] = {h2f2(sKB.x), h2f2(sKB.y)};
+                        float sc[4] = {0.f, 0.f, 0.f, 0.f}; // (token g | g+8) x (head 2i | 2i+1)
 #pragma unroll
                         for (int G = 0; G < 4; G++) {
                             float acc[4] = {0.f, 0.f, 0.f, 0.f};
                             if (BITS == 8) {
-                                const uint4 r = *reinterpret_cast<const uint4 *>(kc + trow * St::kCodeRow + G * 64 + i * 16);
-                                const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+                                const uint4 rA = *reinterpret_cast<const uint4 *>(kc + tA * St::kCodeRow + G * 64 + i * 16);
+                                const uint4 rB = *reinterpret_cast<const uint4 *>(kc + tB * St::kCodeRow + G * 64 + i * 16);
+                                const uint32_t wA[4] = {rA.x, rA.y, rA.z, rA.w}, wB[4] = {rB.x, rB.y, rB.z, rB.w};
 #pragma unroll
                                 for (int j = 0; j < 4; j++) {
                                     // operands stay 1024 + c; 1024 * sum(q) is taken off the group sum below
-                                    const uint32_t b0 = prmt(w[j], kMagic, 0x4140);
-                                    const uint32_t b1 = prmt(w[j], kMagic, 0x4342);
-                                    mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
+                                    mma_f16(acc, prmt(wA[j], kMagic, 0x4140), prmt(wB[j], kMagic, 0x4140), prmt(wA[j], kMagic, 0x4342),
+                                            prmt(wB[j], kMagic, 0x4342), qh[G][2 * j], qh[G][2 * j + 1]);
                                 }
                             } else {
-                                const uint2 r = *reinterpret_cast<const uint2 *>(kc + trow * St::kCodeRow + G * 32 + i * 8);
-                                const uint32_t w[2] = {r.x, r.y};
+                                const uint2 rA = *reinterpret_cast<const uint2 *>(kc + tA * St::kCodeRow + G * 32 + i * 8);
+                                const uint2 rB = *reinterpret_cast<const uint2 *>(kc + tB * St::kCodeRow + G * 32 + i * 8);
+                                const uint32_t wA[2] = {rA.x, rA.y}, wB[2] = {rB.x, rB.y};
 #pragma unroll
                                 for (int j = 0; j < 4; j++) {
-                                    const uint32_t x = w[j >> 1] >> (8 * (j & 1));
+                                    const uint32_t xA = wA[j >> 1] >> (8 * (j & 1)), xB = wB[j >> 1] >> (8 * (j & 1));
                                     // low nibbles ride on 1024, high nibbles on 64: (1024, 64) * the matching
                                     // partial sums of q come off below
-                                    const uint32_t b0 = lop_and_or(x, 0x000f000fu, k1024);
-                                    const uint32_t b1 = lop_and_or(x, 0x00f000f0u, k64);
-                                    mma_f16(acc, qh[G][2 * j], ql[G][2 * j], qh[G][2 * j + 1], ql[G][2 * j + 1], b0, b1);
+                                    mma_f16(acc, lop_and_or(xA, 0x000f000fu, k1024), lop_and_or(xB, 0x000f000fu, k1024),
+                                            lop_and_or(xA, 0x00f000f0u, k64), lop_and_or(xB, 0x00f000f0u, k64), qh[G][2 * j], qh[G][2 * j + 1]);
                                 }
                             }
-                            const float sc0 = G == 0 ? sKf0[0].x : G == 1 ? sKf0[0].y : G == 2 ? sKf0[1].x : sKf0[1].y;
-                            const float sc1 = G == 0 ? sKf1[0].x : G == 1 ? sKf1[0].y : G == 2 ? sKf1[1].x : sKf1[1].y;
-                            s_a = fmaf(sc0, (acc[0] + acc[2]) - qoff[G], s_a);
-                            s_b = fmaf(sc1, (acc[1] + acc[3]) - qoff[G], s_b);
+                            const float scA = G == 0 ? sA[0].x : G == 1 ? sA[0].y : G == 2 ? sA[1].x : sA[1].y;
+                            const float scB = G == 0 ? sB[0].x : G == 1 ? sB[0].y : G == 2 ? sB[1].x : sB[1].y;
+                            sc[0] = fmaf(scA, acc[0] - qoff2[G][0], sc[0]);
+                            sc[1] = fmaf(scA, acc[1] - qoff2[G][1], sc[1]);
+                            sc[2] = fmaf(scB, acc[2] - qoff2[G][0], sc[2]);
+                            sc[3] = fmaf(scB, acc[3] - qoff2[G][1], sc[3]);
                         }
-                        {   // bias term: sum_G z[token][G] * qsum[head][G] (k-slots 0..3 = groups)
+                        {   // bias term: sum_G z[token][G] * qsum[head][G]; k-slots 0..3 meet the sums' high halves,
+                            // 4..7 (the same biases again) their low halves
                             float accz[4] = {0.f, 0.f, 0.f, 0.f};
-                            uint32_t zb = *reinterpret_cast<const uint32_t *>(sg + St::kKz + trow * St::kParamRow + kv * 8 + (i & 1) * 4);
-                            if (i >= 2) zb = 0u;
-                            mma_f16(accz, qza0, qza1, 0u, 0u, zb, 0u);
-                            s_a += accz[0] + accz[2];
-                            s_b += accz[1] + accz[3];
+                            const uint32_t zA = *reinterpret_cast<const uint32_t *>(sg + St::kKz + tA * St::kParamRow + kv * 8 + (i & 1) * 4);
+                            const uint32_t zB = *reinterpret_cast<const uint32_t *>(sg + St::kKz + tB * St::kParamRow + kv * 8 + (i & 1) * 4);
+                            mma_f16(accz, zA, zB, 0u, 0u, qzb, 0u);
+                            sc[0] += accz[0], sc[1] += accz[1], sc[2] += accz[2], sc[3] += accz[3];
                         }
-                        S[nt][0] = s_a, S[nt][1] = s_b;
-                        if (partial) {
-                            if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
-                            if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
+                        // To the layout the rest works in -- lane (g, i) owns head g at tokens 2i, 2i+1 of each
+                        // 8-token half -- by transposing the 8x8 blocks of 16-bit halves across the warp.
+#pragma unroll
+                        for (int nt = 0; nt < 2; nt++) {
+                            const uint32_t c0 = __float_as_uint(sc[2 * nt]), c1 = __float_as_uint(sc[2 * nt + 1]);
+                            const uint32_t ylo = movmatrix_trans(prmt(c0, c1, 0x5410)), yhi = movmatrix_trans(prmt(c0, c1, 0x7632));
+                            S[nt][0] = __uint_as_float(prmt(ylo, yhi, 0x5410));
+                            S[nt][1] = __uint_as_float(prmt(ylo, yhi, 0x7632));
+                            if (partial) {
+                                if (tok0 + nt * 8 + 2 * i >= n_row) S[nt][0] = -INFINITY;
+                                if (tok0 + nt * 8 + 2 * i + 1 >= n_row) S[nt][1] = -INFINITY;
+                            }
                         }
                     }
 
