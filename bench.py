@@ -37,7 +37,7 @@ BYTES_PER_TOKEN = {8: 1088, 4: 576, 16: 2048}  # K + V, both kv heads, codes + s
 CTX = 262144
 LAYERS = 4
 TOKENS_PER_STEP = 256  # so that the timed region of the default 20 steps is over a second long
-TRAFFIC_PER_TOKEN = 1125.4  # measured dram bytes read + written per cached token per layer (one ncu capture)
+TRAFFIC_PER_TOKEN = 1118.7  # measured dram bytes read + written per cached token per layer (one ncu capture)
 METRIC = "Decode-attn achieved HBM GB/s @32k/256k KV; prefill-attn TFLOP/s per 4k chunk"
 
 
@@ -365,7 +365,7 @@ def point_table(sa, torch, stream, s, w):
 
 
 def run_only(args):
-    """One point alone, few launches: the command the ncu captures under profiles/ run."""
+    """One point alone, few launches: the command an ncu capture of that point runs."""
     import torch
     import saetta_macqwen_b200 as sa
 
