@@ -440,6 +440,17 @@ int saetta_att_gemm_encode(saetta_att_gemm *op, const void *q_dev, int dtype, co
                            const void *values_dev, const saetta_quant_rows *keys_q,
                            const saetta_quant_rows *values_q, const float *q_and_gate_dev,
                            float *out_dev, saetta_flash_params p, void *stream);
+/* The prefill's row route: src/prefill.rs:1674-1686 selects attention_rows /
+ * attention_rows_q8|q4 (the AttentionRows kernels over the chunk's rows) instead of
+ * the GEMM path for its exact mode.  Here the chunk goes through a decode op in
+ * groups of up to its `rows` rows; row r sees keys 0 ..= pos + r of `cache`, which
+ * already holds the chunk's rows.  q_dev is f32 [tokens][heads][256].  An f32 cache
+ * gets f32 arithmetic throughout; 16-bit and quantised caches the tensor-core row
+ * kernels.  params_scratch_dev: ceil(tokens / rows) saetta_token_params on the
+ * device, written by the call.  Not capturable. */
+int saetta_prefill_rows_cache(saetta_decode *op, const float *q_dev, const saetta_kv_cache *cache,
+                              const float *q_and_gate_dev, float *out_dev, saetta_flash_params p,
+                              saetta_token_params *params_scratch_dev, void *stream);
 /* attention_prefill::encode: the same computation with no object, over a binary16
  * cache (what the reference's function takes).  dtype must be SAETTA_F16: the
  * tensor-core kernel gives P the values' type, and bfloat16's 8-bit significand

@@ -156,6 +156,7 @@ SYMBOLS = {
     "saetta_att_gemm_encode": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, FlashParams, _P]),
     "saetta_att_gemm_partial": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, FlashParams, _Z, _Z, _P]),
     "saetta_prefill_encode": (_I, [_I, _P, _I, _P, _P, _P, _P, FlashParams, _P]),
+    "saetta_prefill_rows_cache": (_I, [_P, _P, _P, _P, _P, FlashParams, _P, _P]),
 }
 
 
@@ -347,6 +348,11 @@ class AttentionRows:
     def record_cache(self, m, q, cache, q_and_gate, out, params, stream=None):
         _check(lib().saetta_decode_record_cache(self.h, m, ptr(q), cache.h, ptr(q_and_gate), ptr(out), ptr(params),
                                                 _stream(stream)))
+
+    def prefill_rows(self, q, cache, q_and_gate, out, p, params_scratch, stream=None):
+        """The prefill's row route (exact mode): the chunk in groups of up to `rows` rows through this op."""
+        _check(lib().saetta_prefill_rows_cache(self.h, ptr(q), cache.h, ptr(q_and_gate), ptr(out), p, ptr(params_scratch),
+                                               _stream(stream)))
 
     def partial_cache(self, m, q, cache, part, params, row_step=1, stream=None):
         _check(lib().saetta_decode_partial_cache(self.h, m, ptr(q), cache.h, ptr(part), row_step, ptr(params),

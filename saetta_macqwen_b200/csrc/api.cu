@@ -10,6 +10,7 @@
 #include <new>
 
 #include <mutex>
+#include <vector>
 
 #include "merge_role.cuh"
 
@@ -39,6 +40,15 @@ static int alloc_zero(void **p, size_t bytes) {
     SAETTA_CUDA(cudaMalloc(p, bytes ? bytes : 16));
     SAETTA_CUDA(cudaMemset(*p, 0, bytes ? bytes : 16));
     return SAETTA_OK;
+}
+
+static bool capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return cs != cudaStreamCaptureStatusNone;
 }
 
 static KvView view_of(const saetta_quant_rows *k, const saetta_quant_rows *v) {
@@ -641,6 +651,37 @@ int saetta_decode_record_cache(saetta_decode *op, size_t m, const float *q_dev, 
                       (cudaStream_t)stream);
 }
 
+// The prefill's row route (src/prefill.rs:1674-1686 selects attention_rows / attention_rows_q8|q4 for its exact
+// mode: the m-row kernels of AttentionRows over the chunk's rows instead of the GEMM path).  The chunk goes through
+// the same op in groups of up to `op->rows` rows: row r of the chunk sees keys 0 ..= pos + r.  An f32 cache gets f32
+// arithmetic throughout (decode_exact_kernel); 16-bit and quantised caches their tensor-core row kernels.
+// `params_scratch_dev` holds one saetta_token_params per group and is written here (from pageable host memory: the
+// call is not capturable).
+int saetta_prefill_rows_cache(saetta_decode *op, const float *q_dev, const saetta_kv_cache *cache,
+                              const float *q_and_gate_dev, float *out_dev, saetta_flash_params p,
+                              saetta_token_params *params_scratch_dev, void *stream) {
+    if (!op || !q_dev || !cache || !q_and_gate_dev || !out_dev || !params_scratch_dev)
+        return fail(SAETTA_ERR_BAD_ARG, "prefill rows: null pointer");
+    if (p.heads != op->heads || p.kv_heads != op->kv_heads) return fail(SAETTA_ERR_BAD_SHAPE, "prefill rows: heads differ from the op's");
+    if (size_t(p.pos) + p.tokens > cache->capacity) return fail(SAETTA_ERR_BAD_SHAPE, "prefill rows: the chunk ends beyond the cache");
+    if (!p.tokens) return SAETTA_OK;
+    if (capturing((cudaStream_t)stream)) return fail(SAETTA_ERR_BAD_ARG, "prefill rows: not capturable (it uploads its row groups' parameters)");
+    const size_t per = op->rows, groups = (p.tokens + per - 1) / per;
+    std::vector<saetta_token_params> host(groups);
+    for (size_t g = 0; g < groups; g++) host[g] = saetta_token_params{0u, uint32_t(p.pos + g * per), uint32_t(p.pos + g * per + 1), 0u};
+    DeviceGuard guard(op->device);
+    SAETTA_CUDA(cudaMemcpyAsync(params_scratch_dev, host.data(), groups * sizeof(saetta_token_params), cudaMemcpyHostToDevice,
+                                (cudaStream_t)stream));
+    const size_t q_row = size_t(p.heads) * kDim;
+    for (size_t g = 0; g < groups; g++) {
+        const size_t r0 = g * per, m = std::min(per, size_t(p.tokens) - r0);
+        if (int rc = saetta_decode_record_cache(op, m, q_dev + r0 * q_row, cache, q_and_gate_dev + r0 * 2 * q_row, out_dev + r0 * q_row,
+                                                params_scratch_dev + g, stream))
+            return rc;
+    }
+    return SAETTA_OK;
+}
+
 int saetta_decode_partial_cache(saetta_decode *op, size_t m, const float *q_dev, const saetta_kv_cache *cache,
                                 float *part_dev, uint32_t row_step, const saetta_token_params *params_dev, void *stream) {
     if (int rc = decode_check(op, m, q_dev, part_dev, params_dev)) return rc;
@@ -859,14 +900,6 @@ void saetta_att_gemm_destroy(saetta_att_gemm *op) {
     delete op;
 }
 
-static bool capturing(cudaStream_t st) {
-    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    return cs != cudaStreamCaptureStatusNone;
-}
 
 constexpr uint32_t kKeySplits = 2;      // work items a long-context tile's keys are cut into
 constexpr size_t kSplitFromKeys = 16384; // from this many keys on

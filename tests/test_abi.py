@@ -95,6 +95,7 @@ def test_null_arguments_are_refused_before_any_device_work(lib):
     assert lib.saetta_prefill_encode(0, fake, sa.BF16, fake, fake, fake, fake, fp, None) == sa.UNSUPPORTED
     assert b"binary16 only" in lib.saetta_last_error()
     assert lib.saetta_decode_static_status(0, None, None, 0) == sa.BAD_ARG
+    assert lib.saetta_prefill_rows_cache(None, None, None, None, None, fp, None, None) == sa.BAD_ARG
 
 
 def test_host_quantiser_is_the_oracle_bit_for_bit(lib, oracle):

@@ -177,6 +177,38 @@ def test_long_context_chunk_uses_key_splits(oracle):
     check_rows(oracle, got, q, qg, k, v, pos, np.array([0, 1, 7, 15, 16, 17, 31, 32, 39]))
 
 
+@pytest.mark.parametrize("bits", [32, 8])
+def test_row_route_of_the_exact_mode(oracle, bits):
+    """src/prefill.rs:1674-1686: in exact mode the chunk goes through the AttentionRows kernels.  Over an f32 cache
+    that is f32 arithmetic throughout (5e-6 rel-RMS, the tolerance of the f32 configuration); over an 8-bit cache the
+    quantised row kernel (2e-3 / 1e-3)."""
+    import torch
+
+    pos, tokens = 37, 21  # three groups of 8, the last one ragged
+    total = pos + tokens
+    q = oracle.normal(tokens * HEADS * DIM, 31)
+    k, v = oracle.normal(total * ROW, 32), oracle.normal(total * ROW, 33)
+    qg = oracle.normal(tokens * HEADS * 2 * DIM, 34)
+    cache = sa.GpuKvCache(0, bits, 128)
+    cache.store_at(dev(k), dev(v), 0, total)
+    op = sa.AttentionRows(0, HEADS, KV, 128, 8)
+    out = torch.full((tokens * HEADS * DIM,), float("nan"), device="cuda")
+    scratch = torch.zeros(4 * 4, dtype=torch.int32, device="cuda")
+    op.prefill_rows(dev(q), cache, dev(qg), out, sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0), scratch)
+    torch.cuda.synchronize()
+    assert op.device_status() == 0
+    got = out.cpu().numpy().reshape(tokens, HEADS, DIM)
+    kr, vr = (k, v) if bits == 32 else (oracle.round_trip(k, bits), oracle.round_trip(v, bits))
+    want = oracle.attention_rows(q, qg, kr, vr, [pos + i + 1 for i in range(tokens)], threads=8)
+    assert np.isfinite(got).all()
+    if bits == 32:
+        assert rel_rms(got, want) < 5e-6, rel_rms(got, want)
+    else:
+        assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3, (max_abs(got, want), rel_rms(got, want))
+    with pytest.raises(sa.SaettaError):  # the chunk must fit the cache
+        op.prefill_rows(dev(q), cache, dev(qg), out, sa.FlashParams(HEADS, KV, 120, tokens, 1.0 / 16.0), scratch)
+
+
 def test_shape_errors(oracle):
     import torch
 
