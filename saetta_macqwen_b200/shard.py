@@ -49,3 +49,35 @@ def local_decode_params(position, m, ranges, rank):
     if lo > first_new:
         raise ValueError("the new rows must lie inside one shard")
     return first_new + 1 - lo, 1
+
+
+def local_rows(first, rows, ranges, rank):
+    """The part of the global rows [first, first + rows) that rank `rank` holds, as rows of its own
+    buffers (row 0 of a shard's buffers is the token at its range's start): (local_first, count);
+    count 0 when the shard holds none of them."""
+    lo, hi = ranges[rank]
+    a, b = max(first, lo), min(first + rows, hi)
+    return (a - lo, b - a) if b > a else (0, 0)
+
+
+def local_capacity(tokens, ranges, rank, align=128):
+    """Rows rank `rank`'s cache needs so that the sequence's first `tokens` tokens have a place: the
+    length of its range below `tokens`, rounded up to the cache chunk (KV_ALIGN).  The cuts of `ranges`
+    never move, so growing a sharded cache (GpuKvCache::resize, src/gpu_layers.rs:249-292) is every rank
+    growing its own cache to this many rows; rows already stored keep their places."""
+    lo, hi = ranges[rank]
+    n = min(max(tokens - lo, 0), hi - lo)
+    return (n + align - 1) // align * align
+
+
+def backup_save(backup, caches, first, rows, ranges, rank, stream=None):
+    """RowBackup::save (src/gpu_cache.rs:234-256) over a sharded cache: the rank saves the rows of the
+    global range [first, first + rows) that its shard holds (nothing, when it holds none: the backup is
+    then empty and its restore a no-op).  `caches` are the rank's own caches (one per layer).  Every rank
+    makes the same call; RowBackup::restore is the rank's own backup.restore(caches)."""
+    a, n = local_rows(first, rows, ranges, rank)
+    if n:
+        backup.save(caches, a, n, stream)
+    else:
+        backup.clear()
+    return n

@@ -84,6 +84,36 @@ def _rank(rank, world, port, tokens, m, out_q):
     dist.destroy_process_group()
 
 
+def test_local_rows_and_capacity_of_a_sharded_cache():
+    """RowBackup and resize over a sharded page layout (src/gpu_cache.rs:196-280, src/gpu_layers.rs:249-292): a
+    global row range falls apart into one local range per shard, disjoint and complete; capacities grow shard by
+    shard without moving a stored row."""
+    for tokens, world in ((3000, 2), (3000, 3), (262144, 8), (100, 4)):
+        ranges = shard.shard_ranges(tokens, world)
+        cuts = [hi for lo, hi in ranges if 0 < hi < tokens]
+        spans = [(0, tokens), (0, 1), (tokens - 1, 1), (1000 % tokens, min(700, tokens - 1000 % tokens))]
+        spans += [(cuts[0] - 1, 2)] if cuts else []  # one row either side of a cut
+        for first, rows in spans:
+            covered = []
+            for r, (lo, hi) in enumerate(ranges):
+                a, n = shard.local_rows(first, rows, ranges, r)
+                assert 0 <= a and a + n <= hi - lo
+                covered += [lo + a + i for i in range(n)]
+            assert covered == list(range(first, first + rows)), (tokens, world, first, rows)
+        # nothing beyond a shard's range, nothing for a range elsewhere
+        assert shard.local_rows(tokens, 5, ranges, 0) == (0, 0)
+        # growing: the capacity a rank needs is monotone in the tokens, reaches its range, and is chunk-aligned
+        for r, (lo, hi) in enumerate(ranges):
+            last = 0
+            for t in (0, 1, lo, lo + 1, (lo + hi) // 2, hi, tokens):
+                c = shard.local_capacity(t, ranges, r)
+                assert c % 128 == 0 and c >= min(max(t - lo, 0), hi - lo) and c < hi - lo + 128
+            caps = [shard.local_capacity(t, ranges, r) for t in range(0, tokens + 1, max(1, tokens // 50))]
+            assert caps == sorted(caps)
+            assert shard.local_capacity(tokens, ranges, r) >= hi - lo
+            last = caps[-1]
+
+
 @pytest.mark.parametrize("tokens,m", [(1000, 1), (777, 4)])
 def test_two_gloo_ranks_merge_to_the_whole(tokens, m):
     import torch.multiprocessing as mp
