@@ -58,6 +58,16 @@ def peaks():
         return 6650.0, 1590.0, "fallback"
 
 
+def sustained_tc_peak():
+    """cuBLAS bf16 in a seconds-long loop under the power cap: the denominator for a point replayed for a
+    quarter of a second and more (the burst figure is for a kernel timed alone)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        return 1400.0
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons (a read-only query) while the timed region runs: the query
     loop starts early, each sample is stamped when it is read, and only the samples inside the window
@@ -767,6 +777,8 @@ def main():
                     r["frac_of_hbm_peak"] = r["gbs"] / hbm_peak
                 if "tflops" in r and not name.startswith("e2e"):
                     r["frac_of_bf16_peak"] = r["tflops"] / tc_peak
+                    r["frac_of_bf16_sustained"] = r["tflops"] / sustained_tc_peak()
+                    r["frac_of_nominal_2250"] = r["tflops"] / 2250.0
                 points[name] = r
             except Exception as e:  # a point that cannot run is reported, not hidden
                 points[name] = {"error": str(e)[:200]}
