@@ -769,7 +769,7 @@ def main():
         for name in ["decode_32k_8bit", "decode_64k_8bit", "decode_128k_8bit", "decode_256k_4bit", "decode_128k_f16",
                      "verify_m4_32k_8bit", "batch64_ragged_8bit", "batch64_ragged_4bit", "qmv_8192x2048_5bit_m1",
                      "qmv_8192x2048_5bit_m4", "prep_store_4k_8bit", "prefill_4k_pos0_bf16", "prefill_4k_pos32k_8bit",
-                     "prefill_4k_pos128k_8bit", "prefill_4k_pos32k_8bit_staged", "prefill_4k_pos128k_8bit_staged",
+                     "prefill_4k_pos128k_8bit", "prefill_4k_pos32k_4bit", "prefill_4k_pos32k_8bit_staged", "prefill_4k_pos128k_8bit_staged",
                      "e2e_prefill_4k_8bit"]:
             try:
                 r = table[name]()
