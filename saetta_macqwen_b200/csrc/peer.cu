@@ -4,10 +4,13 @@
 // kernels produce the (m, l, O) partial of its KV shard.  Instead of an
 // all-gather followed by a merge, the kernel that finishes the partial stores
 // it straight into every peer's mailbox over NVLink (plain peer stores through
-// NVSwitch; no multicast, no library kernel on peer memory), and ONE kernel per
-// rank polls its own memory and merges and gates what has arrived.  A partial
-// crosses NVLink once, as fire-and-forget stores; nothing waits on a remote
-// read or on an acknowledgement.
+// NVSwitch; no multicast, no library kernel on peer memory), and polls its own
+// memory for the peers' words, merges and gates what has arrived: for decode
+// and verify that is all one launch per rank (the merge CTAs of the decode
+// kernel, merge_role.cuh); the kernels in this file are the two-launch form and
+// the route for partials that other kernels leave in the staging buffer.  A
+// partial crosses NVLink once, as fire-and-forget stores; nothing waits on a
+// remote read or on an acknowledgement.
 //
 // Mailbox protocol (memory shared between processes with CUDA IPC handles):
 // every rank owns two slots, each with room for one partial per rank.  A slot

@@ -21,13 +21,16 @@
 //    tile (written once per tile with tcgen05.st) and P (written over the S
 //    columns it was computed from).  Shared-memory traffic per block is then
 //    only the TMA writes and the K / V operand reads, which is what lets the
-//    MMA pipe run near its rate.  TMEM: O 256 columns, Q 128, two S/P buffers of 64.
+//    MMA pipe run near its rate.  TMEM: O 256 columns, Q 128, and 128 for S and P: one S buffer of 64 and two
+//    P buffers of 32 (16-bit cache), or two S buffers of 64 with P written over the scores (quantised cache).
 //  * Two threads issue tcgen05.mma, because one thread needs longer to issue a
 //    block's 20 instructions than the tensor pipe needs to run them: warp 13
-//    issues S = Q K^T (128x64x256, A from TMEM), up to two blocks ahead, and
+//    issues S = Q K^T (128x64x256, A from TMEM) ahead of the softmax, and
 //    warp 14 issues O += P V (128x256x64, A from TMEM, V read MN-major straight
-//    from its [key][dim] rows).  An S buffer is reused for block j+2 once the
-//    P V product of block j has completed.
+//    from its [key][dim] rows).  Measured: a 128x64x16 score instruction occupies
+//    the pipe for about 55 ns whatever its N up to 128 (a 128x256x16 P V
+//    instruction for its nominal 70 ns), so the sixteen score instructions of a
+//    block, not its flops, are most of its time.
 //  * The softmax warps (one TMEM lane = one row per thread) read S with
 //    tcgen05.ld, do the online softmax in log2 units, write P in V's 16-bit type
 //    back to TMEM, and only rescale O in TMEM when the running maximum has grown
@@ -80,7 +83,7 @@ struct PfLayout {
 };
 static_assert(PfLayout<0>::kSmem == kPfSmem, "the 16-bit layout is unchanged");
 static_assert(PfLayout<8>::kSmem <= 227 * 1024 && PfLayout<4>::kSmem <= 227 * 1024, "fits a CTA's shared memory");
-constexpr int kTmemO = 0, kTmemQ = 256, kTmemS = 384; // TMEM columns: O, Q (2 values per column), S/P buffers
+constexpr int kTmemO = 0, kTmemQ = 256, kTmemS = 384, kTmemP = 448; // TMEM columns: O, Q (2 values per column), S (64), two P buffers (32 each)
 constexpr float kLog2ePf = 1.4426950408889634f;
 constexpr float kPfRescale = 8.0f;
 
@@ -246,6 +249,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                const __grid_constant__ PfQuantMaps qm, const PfParams p) {
     using L = PfLayout<QBITS>;
     constexpr int NST = L::kOpStages;
+    // 16-bit cache: ONE S buffer, released by the softmax warps as soon as the scores are in their registers, and two P
+    // buffers of their own (the next block's scores are computed while this block's softmax runs: measured 5-7 % faster).
+    // Quantised cache: two S buffers with P written over the scores (there the converting warps bound the kernel, and
+    // scores that run further ahead only take issue slots from them: measured 10 % slower with the single buffer).
+    constexpr bool kOwnP = QBITS == 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *sK = smem;                  // [NST][kKBytes]
@@ -254,7 +262,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     uint64_t *bars = reinterpret_cast<uint64_t *>(sCode + L::kCodeStages * L::kCodeStage);
     uint64_t *q_full = bars + 0, *q_empty = bars + 1, *o_final = bars + 2, *o_empty = bars + 3, *k_full = bars + 4,
              *k_empty = bars + 7, *v_full = bars + 10, *v_empty = bars + 13, *s_full = bars + 16, *p_full = bars + 18,
-             *pv_done = bars + 20, *lm_full = bars + 22, *code_full = bars + 26, *code_empty = bars + 28;
+             *pv_done = bars + 20, *lm_full = bars + 22, *code_full = bars + 26, *code_empty = bars + 28, *s_free = bars + 30;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 24);
     float *row_l = reinterpret_cast<float *>(bars + 32); // [2][128] row sums handed from the softmax warps
     float *row_m = row_l + 2 * kBM;                      // [2][128] running maxima (log2 units)
@@ -270,6 +278,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         for (int s = 0; s < L::kCodeStages; s++) mbar_init(&code_full[s], 1), mbar_init(&code_empty[s], 8);
         for (int s = 0; s < 2; s++)
             mbar_init(&s_full[s], 1), mbar_init(&p_full[s], 4), mbar_init(&pv_done[s], 1), mbar_init(&lm_full[s], 4);
+        mbar_init(s_free, 4);
         *abort_flag = 0;
         *never_set = 0;
         mbar_fence_init();
@@ -282,7 +291,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_o = tmem + kTmemO, tmem_q = tmem + kTmemQ, tmem_s = tmem + kTmemS;
+    const uint32_t tmem_o = tmem + kTmemO, tmem_q = tmem + kTmemQ, tmem_s = tmem + kTmemS, tmem_p = tmem + kTmemP;
 
     auto give_up = [&](uint32_t bit) {
         atomicOr(p.status, bit);
@@ -348,8 +357,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         // ------------------------------------------------------------ MMA issuer for S = Q K^T
         // Two threads issue MMAs, this one the score products and warp 14 the P V products: one
         // thread alone spends longer issuing the 20 instructions of a block than the tensor
-        // pipe needs to run them.  An S buffer is reused two blocks later, once the P V product
-        // that read P out of it has completed (pv_done).
+        // pipe needs to run them.  There is ONE S buffer: the softmax warps release it as soon as the
+        // scores are in their registers (s_free), so the next block's scores are computed while the
+        // softmax of this one runs; P has buffers of its own.
         if (lane == 0) {
             const uint32_t idesc_s = (1u << 4) | (p.fmt << 7) | (p.fmt << 10) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
             const uint32_t k_addr = smem_u32(sK);
@@ -362,7 +372,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 for (uint32_t b = 0; b < t.nb; b++, g++) {
                     const uint32_t st = g % NST, ph = (g / NST) & 1, sb = g & 1;
                     if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
-                    if (!mbar_wait(&pv_done[sb], ((g >> 1) & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    if (!mbar_wait(kOwnP ? s_free : &pv_done[sb], kOwnP ? (g & 1) ^ 1 : ((g >> 1) & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
                     tc_fence_after();
                     const uint64_t bd0 = umma_desc(k_addr + st * kKBytes, 16, 1024);
 #pragma unroll
@@ -370,7 +380,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                         // the descriptor's address field counts 16-byte units: +2 per 16-value k-step
                         // inside a 64-value slab, one slab further every fourth step
                         const uint64_t bd = bd0 + uint64_t(((ks >> 2) * kKChunk + (ks & 3) * 32) >> 4);
-                        tc_mma_ts(tmem_s + sb * kBN, tmem_q + ks * 8, bd, idesc_s, ks > 0);
+                        tc_mma_ts(tmem_s + (kOwnP ? 0 : sb * kBN), tmem_q + ks * 8, bd, idesc_s, ks > 0);
                     }
                     tc_commit(&k_empty[st]);
                     tc_commit(&s_full[sb]);
@@ -401,7 +411,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     const uint64_t bd0 = umma_desc(v_addr + st * kKBytes, kKChunk, 1024);
 #pragma unroll
                     for (int ks = 0; ks < kBN / 16; ks++)
-                        tc_mma_ts(tmem_o, tmem_s + sb * kBN + ks * 8, bd0 + uint64_t((ks * 2048) >> 4), idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
+                        tc_mma_ts(tmem_o, (kOwnP ? tmem_p + sb * 32 : tmem_s + sb * kBN) + ks * 8, bd0 + uint64_t((ks * 2048) >> 4), idesc_o, (b > 0 || ks > 0) ? 1u : 0u);
                     tc_commit(&v_empty[st]);
                     tc_commit(&pv_done[sb]);
                     if (b + 1 == t.nb) tc_commit(o_final);
@@ -429,9 +439,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 if (!mbar_wait(&s_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
                 tc_fence_after();
                 uint32_t sr[2][32];
-                tmem_ld32(tmem_s + lane_addr + st * kBN, sr[0]);
-                tmem_ld32(tmem_s + lane_addr + st * kBN + 32, sr[1]);
+                tmem_ld32(tmem_s + lane_addr + (kOwnP ? 0 : st * kBN), sr[0]);
+                tmem_ld32(tmem_s + lane_addr + (kOwnP ? 0 : st * kBN) + 32, sr[1]);
                 tmem_wait_ld();
+                if constexpr (kOwnP) { // the scores are in registers: the S buffer is free for the next block's product
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(s_free);
+                }
 
                 // raw scores; the positive scale (in log2 units) is folded into the exponent's FFMA
                 float s[64];
@@ -473,7 +488,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     tc_fence_before();
                 }
                 const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                // P over the first 32 columns of the S buffer it came from (two values per column)
+                // P (two values per column) into its own buffer, or over the first 32 columns of the S buffer it came from
                 uint32_t pw[32];
                 float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -488,7 +503,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                         pw[k] = pack_half2(a, bb);
                     }
                 }
-                tmem_st32(tmem_s + lane_addr + st * kBN, pw);
+                if constexpr (kOwnP) { // P buffer g & 1: the P V product of two blocks ago has read it
+                    if (!mbar_wait(&pv_done[st], ph ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    tc_fence_after();
+                }
+                tmem_st32((kOwnP ? tmem_p + st * 32 : tmem_s + st * kBN) + lane_addr, pw);
                 tmem_wait_st();
                 const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                 l += sum;
