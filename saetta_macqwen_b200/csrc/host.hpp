@@ -235,6 +235,7 @@ struct PrefillArgs {
                              // that stores only its own slice of the sequence
     // a quantised cache read in place (qbits 8 or 4; k and v above are then unused): codes, scales, biases
     int qbits = 0;
+    bool narrow = false;     // 16-bit cache: the kernel with 64-key score blocks instead of the wide one (kept for comparison)
     int k_dtype = -1;        // of k when it differs from q's (binary16 keys under bfloat16 queries: q is converted on the way in)
     const void *qk = nullptr, *qv = nullptr, *qks = nullptr, *qkz = nullptr, *qvs = nullptr, *qvz = nullptr;
 };

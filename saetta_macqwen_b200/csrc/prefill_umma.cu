@@ -808,6 +808,457 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     if (warp == 13) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
+// ----------------------------------------------------------------- the wide kernel (16-bit caches)
+//
+// Same tiles, same work items, same results as prefill_kernel<0>; what differs is the shape of the score product.
+// A tcgen05.mma of 128 rows x N x 16 occupies the tensor pipe for about 55 ns whatever N is, up to 128, so the
+// scores are computed 128 keys at a time (sixteen instructions per 128 keys instead of per 64).  Tensor memory
+// has no room for that beside the 256-column O: O 256 + S 128 + P 64 leave 64 columns, so only dims 0..127 of the
+// Q tile live in tensor memory; dims 128..255 sit in shared memory (written once per tile, in the swizzled
+// K-major layout) and are the A operand of the second half of a block's score instructions.  K travels in
+// half-stages of 128 keys x 128 dims (a ring of three), V in stages of 64 keys x 256 dims as before.
+// Eight softmax warps, two per row (keys 0..63 and 64..127 of the block): they exchange their maxima through
+// shared memory, release S as soon as the scores are in registers (the next block's scores are computed during
+// this block's softmax) and write P into its own 64 columns.  Four tile I/O warps, one thread per row.  Two copying
+// threads (K; V) and two issuing threads (scores; P V).
+constexpr int kWBN = 128;                       // keys per score block
+constexpr int kWKHalf = kWBN * 128 * 2;         // bytes of a K half-stage: 128 keys x 128 dims, two slabs of [128][128 B]
+constexpr int kWKSlab = kWBN * 128;             // 16 KB
+constexpr int kWKStages = 3, kWVStages = 2;
+constexpr int kWQHi = kBM * 128 * 2;            // dims 128..255 of the Q tile: 32 KB, two slabs of [128 rows][128 B]
+constexpr int kWTmemO = 0, kWTmemQ = 256, kWTmemS = 320, kWTmemP = 448;
+constexpr int kWSmem = kWKStages * kWKHalf + kWVStages * kKBytes + kWQHi + 1024 /*align*/ + 512 /*barriers*/ +
+                       (2 * 2 + 2) * kBM * 4 /*l per half and tile, m per tile*/ + 2 * 2 * kBM * 8 /*maxima per half and parity, tagged*/;
+static_assert(kWSmem <= 227 * 1024, "shared memory of the wide prefill kernel");
+
+__global__ void __launch_bounds__(kPfThreads, 1)
+prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const PfParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *sK = smem;                              // [3][2 slabs][128 keys][128 B]
+    uint8_t *sV = sK + kWKStages * kWKHalf;          // [2][4 slabs][64 keys][128 B]
+    uint8_t *sQ = sV + kWVStages * kKBytes;          // [2 slabs][128 rows][128 B]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sQ + kWQHi);
+    uint64_t *q_full = bars + 0, *q_empty = bars + 1, *o_final = bars + 2, *o_empty = bars + 3, *k_full = bars + 4,
+             *k_empty = bars + 7, *v_full = bars + 10, *v_empty = bars + 12, *s_full = bars + 14, *s_free = bars + 15,
+             *p_full = bars + 16, *pv_done = bars + 17, *lm_full = bars + 18;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 20);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    volatile uint32_t *never_set = tmem_slot + 2;
+    float *row_l = reinterpret_cast<float *>(bars + 64); // [2 tiles][2 halves][128]
+    float *row_m = row_l + 2 * 2 * kBM;                  // [2 tiles][128]
+    volatile unsigned long long *xmax = reinterpret_cast<volatile unsigned long long *>(row_m + 2 * kBM); // [2 parities][2 halves][128]: (maximum, block number + 1)
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    xmax[threadIdx.x] = 0ull; // 2 x 2 x 128 words = the block's 512 threads: tag 0 is no block's number
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 4), mbar_init(q_empty, 1), mbar_init(o_final, 1), mbar_init(o_empty, 4);
+        for (int s = 0; s < kWKStages; s++) mbar_init(&k_full[s], 1), mbar_init(&k_empty[s], 1);
+        for (int s = 0; s < kWVStages; s++) mbar_init(&v_full[s], 1), mbar_init(&v_empty[s], 1);
+        mbar_init(s_full, 1), mbar_init(s_free, 8), mbar_init(p_full, 8), mbar_init(pv_done, 1);
+        mbar_init(&lm_full[0], 8), mbar_init(&lm_full[1], 8);
+        *abort_flag = 0;
+        *never_set = 0;
+        mbar_fence_init();
+    }
+    if (warp == 13) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_o = tmem + kWTmemO, tmem_q = tmem + kWTmemQ, tmem_s = tmem + kWTmemS, tmem_p = tmem + kWTmemP;
+    auto give_up = [&](uint32_t bit) {
+        atomicOr(p.status, bit);
+        *abort_flag = 1;
+    };
+    // a work item's keys in blocks of 128 from its first 64-key block on; the last may be half a block
+    auto wide_blocks = [](const PfTile &t) { return (t.nb + 1) >> 1; };
+
+    if (warp >= 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 12) {
+            // ------------------------------------------------------------ K copies: a half-stage = 128 keys x 128 dims
+            if (lane == 0) {
+                uint32_t hs = 0; // half-stages copied so far
+                bool ok = true;
+                PfTile t;
+                for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                    for (uint32_t w = 0; ok && w < wide_blocks(t); w++)
+                        for (uint32_t j = 0; j < 2; j++, hs++) {
+                            const uint32_t st = hs % kWKStages, ph = (hs / kWKStages) & 1;
+                            const int key0 = int(t.b_begin * kBN + w * kWBN) - int(p.key_base);
+                            if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                            mbar_expect_tx(&k_full[st], kWKHalf);
+                            for (int c = 0; c < 2; c++)
+                                tma_load_3d(sK + st * kWKHalf + c * kWKSlab, &map_k, &k_full[st], int(j) * 128 + c * 64, int(t.kv), key0);
+                        }
+                }
+                if (*abort_flag)
+                    for (uint32_t k = hs > uint32_t(kWKStages) ? hs - kWKStages : 0; k < hs; k++)
+                        mbar_wait(&k_full[k % kWKStages], (k / kWKStages) & 1, never_set, 200000u);
+            }
+        } else if (warp == 15) {
+            // ------------------------------------------------------------ V copies: a stage = 64 keys x 256 dims
+            if (lane == 0) {
+                uint32_t vs = 0;
+                bool ok = true;
+                PfTile t;
+                for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                    for (uint32_t b = 0; b < t.nb; b++, vs++) {
+                        const uint32_t st = vs % kWVStages, ph = (vs / kWVStages) & 1;
+                        const int key0 = int((t.b_begin + b) * kBN) - int(p.key_base);
+                        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { give_up(kStatusEmptyTimeout); ok = false; break; }
+                        mbar_expect_tx(&v_full[st], kKBytes);
+                        for (int c = 0; c < 4; c++) tma_load_3d(sV + st * kKBytes + c * kKChunk, &map_v, &v_full[st], c * 64, int(t.kv), key0);
+                    }
+                }
+                if (*abort_flag)
+                    for (uint32_t k = vs > uint32_t(kWVStages) ? vs - kWVStages : 0; k < vs; k++)
+                        mbar_wait(&v_full[k % kWVStages], (k / kWVStages) & 1, never_set, 200000u);
+            }
+        } else if (warp == 13) {
+            // ------------------------------------------------------------ score products: 128 rows x 128 keys x 256 dims
+            if (lane == 0) {
+                const uint32_t idesc_s = (1u << 4) | (p.fmt << 7) | (p.fmt << 10) | (uint32_t(kWBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+                const uint32_t k_addr = smem_u32(sK), q_addr = smem_u32(sQ);
+                uint32_t g = 0, hs = 0, tc = 0;
+                bool ok = true;
+                PfTile t;
+                for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                    if (!t.nb) continue;
+                    if (!mbar_wait(q_full, tc & 1, abort_flag)) { give_up(kStatusFullTimeout); break; }
+                    for (uint32_t w = 0; ok && w < wide_blocks(t); w++, g++) {
+                        if (!mbar_wait(s_free, (g & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                        for (uint32_t j = 0; j < 2; j++, hs++) {
+                            const uint32_t st = hs % kWKStages, ph = (hs / kWKStages) & 1;
+                            if (!mbar_wait(&k_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                            tc_fence_after();
+#pragma unroll
+                            for (int ks = 0; ks < 8; ks++) {
+                                // 16 dims per instruction: 32 bytes further inside a 64-dim slab, one slab on after four
+                                const uint32_t off = uint32_t((ks >> 2) * kWKSlab + (ks & 3) * 32);
+                                const uint64_t bd = umma_desc(k_addr + st * kWKHalf + off, 16, 1024);
+                                if (j == 0) tc_mma_ts(tmem_s, tmem_q + ks * 8, bd, idesc_s, ks > 0);
+                                else tc_mma(tmem_s, umma_desc(q_addr + off, 16, 1024), bd, idesc_s, 1u);
+                            }
+                            tc_commit(&k_empty[st]);
+                        }
+                        if (!ok) break;
+                        tc_commit(s_full);
+                    }
+                    if (!ok) break;
+                    tc_commit(q_empty); // every score product of this tile has been issued
+                    tc++;
+                }
+            }
+        } else {
+            // ------------------------------------------------------------ O += P V, 64 keys (one V stage) at a time
+            if (lane == 0) {
+                const uint32_t idesc_o = (1u << 4) | (p.v_fmt << 7) | (p.v_fmt << 10) | (1u << 16) | (uint32_t(kDim >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+                const uint32_t v_addr = smem_u32(sV);
+                uint32_t g = 0, vs = 0, tc = 0;
+                bool ok = true;
+                PfTile t;
+                for (uint32_t round = 0; ok && pf_tile(p, round, t); round++) {
+                    if (!t.nb) continue;
+                    for (uint32_t w = 0; ok && w < wide_blocks(t); w++, g++) {
+                        if (!mbar_wait(p_full, g & 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                        const uint32_t halves = min(2u, t.nb - 2 * w);
+                        for (uint32_t j = 0; j < halves; j++, vs++) {
+                            const uint32_t st = vs % kWVStages, ph = (vs / kWVStages) & 1;
+                            if (!mbar_wait(&v_full[st], ph, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                            if (w == 0 && j == 0 && !mbar_wait(o_empty, (tc & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                            tc_fence_after();
+                            const uint64_t bd0 = umma_desc(v_addr + st * kKBytes, kKChunk, 1024);
+#pragma unroll
+                            for (int ks = 0; ks < kBN / 16; ks++)
+                                tc_mma_ts(tmem_o, tmem_p + j * 32 + ks * 8, bd0 + uint64_t((ks * 2048) >> 4), idesc_o,
+                                          (w > 0 || j > 0 || ks > 0) ? 1u : 0u);
+                            tc_commit(&v_empty[st]);
+                        }
+                        if (!ok) break;
+                        tc_commit(pv_done);
+                        if (w + 1 == wide_blocks(t)) tc_commit(o_final);
+                    }
+                    tc++;
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------ softmax: two threads per row, 64 keys each
+        const uint32_t h = warp >> 2, quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        uint32_t g = 0, tc = 0;
+        bool ok = true;
+        PfTile t;
+        for (uint32_t round = 0; pf_tile(p, round, t); round++) {
+            if (!t.nb) continue;
+            const uint32_t tok = t.tok0 + (row >> 3);
+            const uint32_t item_end = (t.b_begin + t.nb) * kBN;
+            const uint32_t lim_hi = min(min(p.key_hi, p.pos + tok + 1), item_end); // this row sees keys [key_lo, lim_hi)
+            const uint32_t lim_tile = min(min(p.key_hi, p.pos + t.tok0 + 1), item_end); // below it no row of the tile is masked
+            float m_ref = -INFINITY, l = 0.f;
+            for (uint32_t w = 0; ok && w < wide_blocks(t); w++, g++) {
+                const uint32_t key0 = t.b_begin * kBN + w * kWBN + h * 64;
+                if (!mbar_wait(s_full, g & 1, abort_flag)) { give_up(kStatusFullTimeout); ok = false; break; }
+                tc_fence_after();
+                uint32_t sr[2][32];
+                tmem_ld32(tmem_s + lane_addr + h * 64, sr[0]);
+                tmem_ld32(tmem_s + lane_addr + h * 64 + 32, sr[1]);
+                tmem_wait_ld();
+                tc_fence_before(); // the scores are in registers: S is free for the next block's product
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free);
+
+                float s[64];
+#pragma unroll
+                for (int c = 0; c < 64; c++) s[c] = __uint_as_float(sr[c >> 5][c & 31]);
+                if (key0 < p.key_lo || key0 + 64 > lim_tile) {
+#pragma unroll
+                    for (int c = 0; c < 64; c++)
+                        if (key0 + c < p.key_lo || key0 + c >= lim_hi) s[c] = -INFINITY;
+                }
+                float m4[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+                for (int c = 4; c < 64; c++) m4[c & 3] = fmaxf(m4[c & 3], s[c]);
+                float mxl = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                // The row's other half: each thread leaves (maximum, block number + 1) as one 64-bit word and polls
+                // its partner's word of the same parity until it carries this block's number.  No barrier, so a
+                // warp that has given up cannot strand its partner; the poll is bounded like every other wait.
+                // (Two parities: the partner cannot write block g + 2 before it has read this thread's g + 1.)
+                xmax[((g & 1) * 2 + h) * kBM + row] = (static_cast<unsigned long long>(g + 1) << 32) | __float_as_uint(mxl);
+                {
+                    const volatile unsigned long long *theirs = &xmax[((g & 1) * 2 + (h ^ 1)) * kBM + row];
+                    unsigned long long wv = *theirs;
+                    unsigned long long t0 = 0;
+                    bool got = true;
+                    for (uint32_t n = 1; uint32_t(wv >> 32) != g + 1; n++) {
+                        if ((n & 63) == 0) {
+                            unsigned long long tn;
+                            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tn));
+                            if (!t0) t0 = tn;
+                            if (*abort_flag || tn - t0 > 1000000000ull) { got = false; break; }
+                        }
+                        wv = *theirs;
+                    }
+                    if (!__all_sync(0xffffffffu, got)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    mxl = fmaxf(mxl, __uint_as_float(uint32_t(wv)));
+                }
+                const float mx = mxl * p.scale_log2;
+                const bool need = mx > m_ref + kPfRescale; // the same in both halves of a row
+                float factor = 1.f;
+                if (need) {
+                    factor = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - mx);
+                    m_ref = mx;
+                    l *= factor;
+                }
+                if (w > 0 && __any_sync(0xffffffffu, need)) {
+                    // the P V products of the block before must have landed in O; each half rescales its 128 columns
+                    if (!mbar_wait(pv_done, (g & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_o + lane_addr + h * 128 + c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int k = 0; k < 32; k++) o[k] = __float_as_uint(__uint_as_float(o[k]) * factor);
+                        tmem_st32(tmem_o + lane_addr + h * 128 + c, o);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                uint32_t pw[32];
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < 32; k++) {
+                    const float a = ex2_approx(fmaf(s[2 * k], p.scale_log2, -m_use));
+                    const float bb = ex2_approx(fmaf(s[2 * k + 1], p.scale_log2, -m_use));
+                    sum4[k & 3] += a + bb;
+                    if (p.v_fmt) {
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(a, bb);
+                        pw[k] = *reinterpret_cast<uint32_t *>(&hh);
+                    } else {
+                        pw[k] = pack_half2(a, bb);
+                    }
+                }
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                // P has one buffer: the P V products of the block before have read it
+                if (!mbar_wait(pv_done, (g & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); ok = false; break; }
+                tc_fence_after();
+                tmem_st32(tmem_p + lane_addr + h * 32, pw);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
+            }
+            if (!ok) break;
+            row_l[((tc & 1) * 2 + h) * kBM + row] = l;
+            if (h == 0) row_m[(tc & 1) * kBM + row] = m_ref;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&lm_full[tc & 1]);
+            tc++;
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        // ------------------------------------------------------------ tile I/O: one thread per row
+        const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        struct RowOf {
+            uint32_t tok;
+            bool live;
+            size_t rh;
+            float *part;
+        };
+        auto row_of = [&](const PfTile &t) {
+            RowOf r;
+            r.tok = t.tok0 + (row >> 3);
+            r.live = r.tok < p.tokens;
+            r.rh = size_t(r.tok) * p.heads + t.kv * kHeadsPerKv + (row & 7);
+            r.part = p.part ? p.part + size_t(t.split) * p.part_stride : nullptr;
+            return r;
+        };
+        auto next_item = [&](uint32_t &round, PfTile &t) -> bool {
+            while (pf_tile(p, round, t)) {
+                round++;
+                if (t.nb) return true;
+                const RowOf r = row_of(t);
+                if (r.live && r.part) { // no keys: the empty partial
+                    float *dst = r.part + r.rh * kPartStride;
+                    for (uint32_t d = 0; d < uint32_t(kDim); d++) dst[d] = 0.f;
+                    dst[kPartM] = -INFINITY, dst[kPartL] = 0.f;
+                }
+            }
+            return false;
+        };
+        auto load_q = [&](const PfTile &t, uint32_t k) -> bool {
+            const RowOf r = row_of(t);
+            if (r.live && p.out) {
+                const char *gpf = reinterpret_cast<const char *>(p.q_and_gate + r.rh * 2 * kDim + kDim);
+#pragma unroll
+                for (int j = 0; j < 8; j++) prefetch_l2(gpf + j * 128);
+            }
+            const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + r.rh * kDim);
+            bool waited = false;
+#pragma unroll 1
+            for (uint32_t half = 0; half < 2; half++) {
+                uint4 qv[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) qv[j] = r.live ? qrow[half * 16 + j] : make_uint4(0u, 0u, 0u, 0u);
+                if (p.q_bf16) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        uint32_t *wq = reinterpret_cast<uint32_t *>(&qv[j]);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) wq[e] = pack_half2(__uint_as_float(wq[e] << 16), __uint_as_float(wq[e] & 0xffff0000u));
+                    }
+                }
+                if (!waited) { // the score products of the tile before no longer read the old Q
+                    if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+                    tc_fence_after();
+                    waited = true;
+                }
+                if (half == 0) { // dims 0..127 into tensor memory, two values per column
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        uint32_t wq[32];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const uint4 v = qv[c * 8 + j];
+                            wq[4 * j] = v.x, wq[4 * j + 1] = v.y, wq[4 * j + 2] = v.z, wq[4 * j + 3] = v.w;
+                        }
+                        tmem_st32(tmem_q + lane_addr + c * 32, wq);
+                    }
+                } else { // dims 128..255 into shared memory: slab = 64 dims, 16-byte chunks swizzled by the row
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const uint32_t slab = j >> 3, chunk = j & 7;
+                        *reinterpret_cast<uint4 *>(sQ + slab * (kBM * 128) + row * 128 + ((chunk ^ (row & 7)) << 4)) = qv[j];
+                    }
+                }
+            }
+            tmem_wait_st();
+            fence_async_smem(); // the tensor cores read the shared-memory half through the async proxy
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
+            return true;
+        };
+        auto epilogue = [&](const PfTile &t, uint32_t k) -> bool {
+            const RowOf r = row_of(t);
+            const bool row_live = r.live;
+            const size_t rh = r.rh;
+            float *part = r.part;
+            const bool gated = row_live && p.out;
+            if (!mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+            const float l = row_l[((k & 1) * 2) * kBM + row] + row_l[((k & 1) * 2 + 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
+            if (!mbar_wait(o_final, k & 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+            tc_fence_after();
+            const float inv_l = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+            for (uint32_t half = 0; half < 2; half++) {
+                const float *gp = p.q_and_gate + (gated ? rh * 2 * kDim + kDim + half * 128 : 0);
+                uint32_t o[4][32];
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem_o + lane_addr + half * 128 + ch * 32, o[ch]);
+                tmem_wait_ld();
+                if (half == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_empty); // O has left tensor memory: the next tile's P V products may start
+                }
+                if (row_live) {
+                    if (p.out) {
+                        float *op = p.out + rh * kDim + half * 128;
+                        Float8 gt = ld_global_v8(gp);
+#pragma unroll
+                        for (int st = 0; st < 16; st++) {
+                            Float8 gn = gt;
+                            if (st + 1 < 16) gn = ld_global_v8(gp + (st + 1) * 8);
+                            Float8 v;
+#pragma unroll
+                            for (int e = 0; e < 8; e++)
+                                v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-gt.v[e]));
+                            st_global_v8(op + st * 8, v);
+                            gt = gn;
+                        }
+                    } else {
+                        float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + half * 128);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            op[j] = make_float4(__uint_as_float(o[j >> 3][4 * (j & 7)]), __uint_as_float(o[j >> 3][4 * (j & 7) + 1]),
+                                                __uint_as_float(o[j >> 3][4 * (j & 7) + 2]), __uint_as_float(o[j >> 3][4 * (j & 7) + 3]));
+                    }
+                }
+            }
+            if (row_live && part) {
+                part[rh * kPartStride + kPartM] = m_ref;
+                part[rh * kPartStride + kPartL] = l;
+            }
+            return true;
+        };
+        uint32_t round = 0, k = 0;
+        PfTile cur, nxt;
+        bool have = next_item(round, cur);
+        if (have && !load_q(cur, 0)) have = false;
+        while (have) {
+            const bool more = next_item(round, nxt);
+            if (more && !load_q(nxt, k + 1)) break;
+            if (!epilogue(cur, k)) break;
+            cur = nxt, have = more, k++;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 13) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+
 // ----------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -831,6 +1282,7 @@ int prefill_configure(int device) {
     SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfLayout<0>::kSmem));
     SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfLayout<8>::kSmem));
     SAETTA_CUDA(cudaFuncSetAttribute(prefill_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfLayout<4>::kSmem));
+    SAETTA_CUDA(cudaFuncSetAttribute(prefill_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWSmem));
     return SAETTA_OK;
 }
 
@@ -857,7 +1309,8 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
         for (int side = 0; side < 2; side++) {
             const cuuint64_t dims[3] = {cuuint64_t(kDim), a.kv_heads, keys_total};
             const cuuint64_t strides[2] = {kDim * 2, cuuint64_t(a.kv_heads) * kDim * 2};
-            const cuuint32_t box[3] = {64, 1, kBN};
+            // the wide kernel takes the keys 128 at a time, the values 64 at a time
+            const cuuint32_t box[3] = {64, 1, cuuint32_t(side || a.narrow ? kBN : kWBN)};
             CUresult r = enc(side ? &mv : &mk, side ? dtv : dt, 3, const_cast<void *>(side ? a.v : a.k), dims, strides, box, el,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -899,7 +1352,8 @@ int launch_prefill(const PrefillArgs &a, uint32_t *status, cudaStream_t stream) 
     SAETTA_CUDA(cudaGetDevice(&dev));
     const uint32_t tiles = (a.tokens + kTokTile - 1) / kTokTile * a.kv_heads * (a.splits ? a.splits : 1u);
     const uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count(dev)));
-    if (!quant) prefill_kernel<0><<<grid, kPfThreads, PfLayout<0>::kSmem, stream>>>(mk, mv, qm, p);
+    if (!quant && !a.narrow) prefill_wide_kernel<<<grid, kPfThreads, kWSmem, stream>>>(mk, mv, p);
+    else if (!quant) prefill_kernel<0><<<grid, kPfThreads, PfLayout<0>::kSmem, stream>>>(mk, mv, qm, p);
     else if (a.qbits == 8) prefill_kernel<8><<<grid, kPfThreads, PfLayout<8>::kSmem, stream>>>(mk, mv, qm, p);
     else prefill_kernel<4><<<grid, kPfThreads, PfLayout<4>::kSmem, stream>>>(mk, mv, qm, p);
     SAETTA_CUDA(cudaGetLastError());

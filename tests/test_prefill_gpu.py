@@ -334,8 +334,9 @@ def test_quantised_cache_through_the_staging_copy(oracle, bits):
         got = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=op)
         check_rows(oracle, got, q[sl], qg[gl], kr, vr, pos, np.arange(n))
         same = run(torch, q[sl], None, None, qg[gl], pos, n, sa.BF16, quant=cache.quant(), op=in_place)
-        # both routes feed the tensor cores the same binary16 operands
-        assert np.abs(got - same).max() <= 1e-5 * max(1.0, np.abs(same).max())
+        # both routes feed the tensor cores the same binary16 operands (in blocks of 128 and of 64 keys: the
+        # rounding of P sees different running maxima)
+        assert np.abs(got - same).max() <= 2e-4 * max(1.0, np.abs(same).max())
     bare = sa.AttGemm(0, 4096, KV)
     bare.stage_quantised()
     pos, n = chunks[-1]
