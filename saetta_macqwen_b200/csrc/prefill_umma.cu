@@ -988,6 +988,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
         }
     } else if (warp < 8) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
         // ------------------------------------------------------------ softmax: two threads per row, 64 keys each
         const uint32_t h = warp >> 2, quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
@@ -1104,7 +1105,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             tc++;
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
         // ------------------------------------------------------------ tile I/O: one thread per row
         const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
