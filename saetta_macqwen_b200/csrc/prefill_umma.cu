@@ -988,7 +988,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
         }
     } else if (warp < 8) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");
         // ------------------------------------------------------------ softmax: two threads per row, 64 keys each
         const uint32_t h = warp >> 2, quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
@@ -1105,7 +1105,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             tc++;
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         // ------------------------------------------------------------ tile I/O: one thread per row
         const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
@@ -1143,44 +1143,36 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 8; j++) prefetch_l2(gpf + j * 128);
             }
+            // the whole row into registers first: none of it depends on the wait below
             const uint4 *qrow = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.q) + r.rh * kDim);
-            bool waited = false;
-#pragma unroll 1
-            for (uint32_t half = 0; half < 2; half++) {
-                uint4 qv[16];
+            uint4 qv[32];
 #pragma unroll
-                for (int j = 0; j < 16; j++) qv[j] = r.live ? qrow[half * 16 + j] : make_uint4(0u, 0u, 0u, 0u);
-                if (p.q_bf16) {
+            for (int j = 0; j < 32; j++) qv[j] = r.live ? qrow[j] : make_uint4(0u, 0u, 0u, 0u);
+            if (p.q_bf16) { // bfloat16 queries over binary16 key operands: exact unless outside binary16's range
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        uint32_t *wq = reinterpret_cast<uint32_t *>(&qv[j]);
+                for (int j = 0; j < 32; j++) {
+                    uint32_t *wq = reinterpret_cast<uint32_t *>(&qv[j]);
 #pragma unroll
-                        for (int e = 0; e < 4; e++) wq[e] = pack_half2(__uint_as_float(wq[e] << 16), __uint_as_float(wq[e] & 0xffff0000u));
-                    }
+                    for (int e = 0; e < 4; e++) wq[e] = pack_half2(__uint_as_float(wq[e] << 16), __uint_as_float(wq[e] & 0xffff0000u));
                 }
-                if (!waited) { // the score products of the tile before no longer read the old Q
-                    if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
-                    tc_fence_after();
-                    waited = true;
+            }
+            // the score products of the tile before no longer read the old Q
+            if (!mbar_wait(q_empty, (k & 1) ^ 1, abort_flag)) { give_up(kStatusMmaTimeout); return false; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; c++) { // dims 0..127 into tensor memory, two values per column
+                uint32_t wq[32];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint4 v = qv[c * 8 + j];
+                    wq[4 * j] = v.x, wq[4 * j + 1] = v.y, wq[4 * j + 2] = v.z, wq[4 * j + 3] = v.w;
                 }
-                if (half == 0) { // dims 0..127 into tensor memory, two values per column
+                tmem_st32(tmem_q + lane_addr + c * 32, wq);
+            }
 #pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        uint32_t wq[32];
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const uint4 v = qv[c * 8 + j];
-                            wq[4 * j] = v.x, wq[4 * j + 1] = v.y, wq[4 * j + 2] = v.z, wq[4 * j + 3] = v.w;
-                        }
-                        tmem_st32(tmem_q + lane_addr + c * 32, wq);
-                    }
-                } else { // dims 128..255 into shared memory: slab = 64 dims, 16-byte chunks swizzled by the row
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const uint32_t slab = j >> 3, chunk = j & 7;
-                        *reinterpret_cast<uint4 *>(sQ + slab * (kBM * 128) + row * 128 + ((chunk ^ (row & 7)) << 4)) = qv[j];
-                    }
-                }
+            for (int j = 0; j < 16; j++) { // dims 128..255 into shared memory: slab = 64 dims, 16-byte chunks swizzled by the row
+                const uint32_t slab = j >> 3, chunk = j & 7;
+                *reinterpret_cast<uint4 *>(sQ + slab * (kBM * 128) + row * 128 + ((chunk ^ (row & 7)) << 4)) = qv[16 + j];
             }
             tmem_wait_st();
             fence_async_smem(); // the tensor cores read the shared-memory half through the async proxy
@@ -1215,17 +1207,23 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 if (row_live) {
                     if (p.out) {
                         float *op = p.out + rh * kDim + half * 128;
-                        Float8 gt = ld_global_v8(gp);
+                        // the gate values four 32-byte steps ahead of their use (a thread has a whole row: one step
+                        // ahead, sixteen dependent round trips to L2 stood between O's two halves).  Releasing O
+                        // before any gate value is read -- first half out raw, gated later from its own stores --
+                        // shortened the tile change from 9 to 3 us but made the blocks after it slower, the four
+                        // epilogue warps then competing with the softmax warps: 790 against 840 TFLOP/s at position 0
+                        Float8 gt[4];
+#pragma unroll
+                        for (int a = 0; a < 4; a++) gt[a] = ld_global_v8(gp + a * 8);
 #pragma unroll
                         for (int st = 0; st < 16; st++) {
-                            Float8 gn = gt;
-                            if (st + 1 < 16) gn = ld_global_v8(gp + (st + 1) * 8);
+                            const Float8 gc = gt[st & 3];
+                            if (st + 4 < 16) gt[st & 3] = ld_global_v8(gp + (st + 4) * 8);
                             Float8 v;
 #pragma unroll
                             for (int e = 0; e < 8; e++)
-                                v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-gt.v[e]));
+                                v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-gc.v[e]));
                             st_global_v8(op + st * 8, v);
-                            gt = gn;
                         }
                     } else {
                         float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + half * 128);
