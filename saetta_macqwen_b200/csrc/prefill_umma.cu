@@ -988,15 +988,16 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
         }
     } else if (warp < 8) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 144;");
         // ------------------------------------------------------------ softmax: two threads per row, 64 keys each
         const uint32_t h = warp >> 2, quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
         uint32_t g = 0, tc = 0;
         bool ok = true;
-        PfTile t;
+        PfTile t, last;
         for (uint32_t round = 0; pf_tile(p, round, t); round++) {
             if (!t.nb) continue;
+            last = t;
             const uint32_t tok = t.tok0 + (row >> 3);
             const uint32_t item_end = (t.b_begin + t.nb) * kBN;
             const uint32_t lim_hi = min(min(p.key_hi, p.pos + tok + 1), item_end); // this row sees keys [key_lo, lim_hi)
@@ -1104,8 +1105,59 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             if (lane == 0) mbar_arrive(&lm_full[tc & 1]);
             tc++;
         }
+        // The CTA's LAST tile leaves through these eight warps, two threads per row (this half's 128 columns): nothing
+        // is left for them to do, and a tile's scaled, gated stores are bound by the loads and stores in flight,
+        // that is by the number of threads (four warps took 15-19 us for it at the end of a CTA's life).
+        if (ok && tc) {
+            const uint32_t k = tc - 1;
+            const uint32_t tok = last.tok0 + (row >> 3);
+            const bool row_live = tok < p.tokens;
+            const size_t rh = size_t(tok) * p.heads + last.kv * kHeadsPerKv + (row & 7);
+            bool fine = mbar_wait(&lm_full[k & 1], (k >> 1) & 1, abort_flag);
+            const float l = row_l[((k & 1) * 2) * kBM + row] + row_l[((k & 1) * 2 + 1) * kBM + row], m_ref = row_m[(k & 1) * kBM + row];
+            fine = fine && mbar_wait(o_final, k & 1, abort_flag);
+            if (!fine) {
+                give_up(kStatusMmaTimeout);
+            } else {
+                tc_fence_after();
+                const float inv_l = l > 0.f ? 1.f / l : 0.f;
+                uint32_t o[4][32];
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem_o + lane_addr + h * 128 + ch * 32, o[ch]);
+                tmem_wait_ld();
+                if (row_live) {
+                    if (p.out) {
+                        const float *gp = p.q_and_gate + rh * 2 * kDim + kDim + h * 128;
+                        float *op = p.out + rh * kDim + h * 128;
+                        Float8 gt[2] = {ld_global_v8(gp), ld_global_v8(gp + 8)};
+#pragma unroll
+                        for (int st = 0; st < 16; st++) {
+                            const Float8 gc = gt[st & 1];
+                            if (st + 2 < 16) gt[st & 1] = ld_global_v8(gp + (st + 2) * 8);
+                            Float8 v;
+#pragma unroll
+                            for (int e = 0; e < 8; e++)
+                                v.v[e] = __uint_as_float(o[st >> 2][8 * (st & 3) + e]) * __fdividef(inv_l, 1.f + __expf(-gc.v[e]));
+                            st_global_v8(op + st * 8, v);
+                        }
+                    } else {
+                        float *part = p.part + size_t(last.split) * p.part_stride;
+                        float4 *op = reinterpret_cast<float4 *>(part + rh * kPartStride + h * 128);
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            op[j] = make_float4(__uint_as_float(o[j >> 3][4 * (j & 7)]), __uint_as_float(o[j >> 3][4 * (j & 7) + 1]),
+                                                __uint_as_float(o[j >> 3][4 * (j & 7) + 2]), __uint_as_float(o[j >> 3][4 * (j & 7) + 3]));
+                    }
+                    if (p.part && h == 0) {
+                        float *part = p.part + size_t(last.split) * p.part_stride;
+                        part[rh * kPartStride + kPartM] = m_ref;
+                        part[rh * kPartStride + kPartL] = l;
+                    }
+                }
+            }
+        }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ------------------------------------------------------------ tile I/O: one thread per row
         const uint32_t quarter = warp & 3, row = quarter * 32 + lane;
         const uint32_t lane_addr = (quarter * 32) << 16;
@@ -1247,6 +1299,7 @@ prefill_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         while (have) {
             const bool more = next_item(round, nxt);
             if (more && !load_q(nxt, k + 1)) break;
+            if (!more) break; // the last tile leaves through the softmax warps
             if (!epilogue(cur, k)) break;
             cur = nxt, have = more, k++;
         }
