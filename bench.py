@@ -210,7 +210,7 @@ def batch_point(sa, torch, bits, warmup, stream, seqs=64, lo=8192, hi=262144, se
     return {"gbs": nbytes / ms / 1e6, "ms": ms, "tokens": int(lens.sum()), "seqs": seqs}
 
 
-def prefill_point(sa, torch, pos, tokens, warmup, stream, quant_bits=None, staged=False):
+def prefill_point(sa, torch, pos, tokens, warmup, stream, quant_bits=None, staged=False, blocks=128):
     """TFLOP/s of one causal chunk (flops = 4*H*D*(t*pos + t(t+1)/2), src/attention_prefill.rs:139-142).  A
     quantised prefix is read in place; with `staged`, through the op's 16-bit staging copy, which already holds
     the prefix, as after the chunk before (every call converts the chunk's own rows again)."""
@@ -220,6 +220,7 @@ def prefill_point(sa, torch, pos, tokens, warmup, stream, quant_bits=None, stage
     qg = torch.randn(tokens * HEADS * 2 * DIM, device="cuda")
     out = torch.zeros(tokens * HEADS * DIM, device="cuda")
     op = sa.AttGemm(dev, tokens, KV)
+    op.score_blocks(blocks)  # 16-bit caches: the kernel with 128-key score blocks (default) or the one with 64
     p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
     if quant_bits:
         cache = sa.GpuKvCache(dev, quant_bits, total)
@@ -370,6 +371,7 @@ def point_table(sa, torch, stream, s, w):
         "prefill_4k_pos32k_4bit": lambda: prefill_point(sa, torch, 32768, 4096, 2, stream, quant_bits=4),
         "prefill_4k_pos32k_8bit_staged": lambda: prefill_point(sa, torch, 32768, 4096, 2, stream, quant_bits=8, staged=True),
         "prefill_4k_pos128k_8bit_staged": lambda: prefill_point(sa, torch, 131072, 4096, 2, stream, quant_bits=8, staged=True),
+        "prefill_4k_pos128k_8bit_staged_64key": lambda: prefill_point(sa, torch, 131072, 4096, 2, stream, quant_bits=8, staged=True, blocks=64),
         "e2e_prefill_4k_8bit": lambda: e2e_prefill_point(sa, torch, 4096, 8, w, stream),
     }
 

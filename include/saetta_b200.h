@@ -433,6 +433,11 @@ int saetta_att_gemm_invalidate(saetta_att_gemm *op);
  * prefixes (every row is converted once instead of once per query tile), for 2 KB
  * of device memory per key and side. */
 int saetta_att_gemm_stage_quantised(saetta_att_gemm *op, int on);
+/* Which kernel serves a 16-bit cache (and the staging copy): score blocks of 128 keys
+ * (the default; about a tenth faster over long prefixes) or of 64 keys (the kernel the
+ * quantised in-place route is built on).  Same results to rounding; no counterpart in
+ * the reference.  keys: 64 or 128. */
+int saetta_att_gemm_score_blocks(saetta_att_gemm *op, int keys);
 /* AttGemm::encode: with keys_q/values_q non-NULL the cache is read from those
  * 8/4-bit rows (see saetta_att_gemm_stage_quantised) and keys_dev/values_dev are
  * ignored. */

@@ -152,6 +152,7 @@ SYMBOLS = {
     "saetta_att_gemm_reserve": (_I, [_P, _Z]),
     "saetta_att_gemm_invalidate": (_I, [_P]),
     "saetta_att_gemm_stage_quantised": (_I, [_P, _I]),
+    "saetta_att_gemm_score_blocks": (_I, [_P, _I]),
     "saetta_att_gemm_partial_shard": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, FlashParams, _Z, _Z, _Z, _P]),
     "saetta_att_gemm_encode": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, FlashParams, _P]),
     "saetta_att_gemm_partial": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, FlashParams, _Z, _Z, _P]),
@@ -665,6 +666,10 @@ class AttGemm:
 
     def invalidate(self):
         _check(lib().saetta_att_gemm_invalidate(self.h))
+
+    def score_blocks(self, keys):
+        """16-bit caches: score blocks of 128 keys (default) or 64 (the older kernel)."""
+        _check(lib().saetta_att_gemm_score_blocks(self.h, keys))
 
     def stage_quantised(self, on=True):
         """Read 8/4-bit caches through the op's 16-bit staging copy (kv_stage) instead of in place."""

@@ -942,6 +942,13 @@ int saetta_att_gemm_stage_quantised(saetta_att_gemm *op, int on) {
     return SAETTA_OK;
 }
 
+int saetta_att_gemm_score_blocks(saetta_att_gemm *op, int keys) {
+    if (!op) return fail(SAETTA_ERR_BAD_ARG, "AttGemm: null handle");
+    if (keys != 64 && keys != 128) return fail(SAETTA_ERR_BAD_ARG, "AttGemm: score blocks of 64 or 128 keys");
+    op->narrow = keys == 64;
+    return SAETTA_OK;
+}
+
 static int prefill_check(const void *q, int dtype, const saetta_flash_params &p) {
     if (!q) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: q is null");
     if (dtype != SAETTA_F16 && dtype != SAETTA_BF16) return fail(SAETTA_ERR_BAD_ARG, "prefill attention: dtype");
@@ -1034,6 +1041,7 @@ static int att_gemm_run(saetta_att_gemm *op, const void *q, int dtype, const voi
                   uint32_t(key_lo), uint32_t(key_hi), p.scale};
     a.key_base = uint32_t(key_base);
     a.k_dtype = k_dtype;
+    a.narrow = op->narrow;
     if (in_place) {
         // 8/4-bit rows are read where they are, per key block (kernels/attention_rows_q.metal:16-31): no
         // 16-bit copy of the cache, nothing to reserve

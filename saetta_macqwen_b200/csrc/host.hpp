@@ -80,6 +80,7 @@ struct saetta_att_gemm {
     void *stage_k = nullptr, *stage_v = nullptr;
     size_t stage_tokens = 0; // rows each copy has room for
     bool stage_quant = false; // read 8/4-bit caches through the 16-bit copy instead of in place
+    bool narrow = false;      // 16-bit caches: score blocks of 64 keys (the older kernel) instead of 128
     struct Staged {
         const void *src = nullptr; // the buffer the rows came from (identity of the cache side)
         int dtype = 0;

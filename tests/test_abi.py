@@ -85,6 +85,7 @@ def test_null_arguments_are_refused_before_any_device_work(lib):
     assert lib.saetta_peer_slice(None, 8, C.byref(z), C.byref(z)) == sa.BAD_ARG
     assert lib.saetta_peer_group_reset(None, 0, None) == sa.BAD_ARG
     assert lib.saetta_att_gemm_stage_quantised(None, 1) == sa.BAD_ARG
+    assert lib.saetta_att_gemm_score_blocks(None, 64) == sa.BAD_ARG
     assert lib.saetta_decode_publish_cache(None, 1, None, None, None, 0, None, None) == sa.BAD_ARG
     assert lib.saetta_decode_exchange_cache(None, 1, None, None, None, 0, None, None, None, None) == sa.BAD_ARG
     assert lib.saetta_decode_batch_publish(None, 1, None, None, None, None, None) == sa.BAD_ARG

@@ -30,8 +30,11 @@ def run(torch, q, k, v, qg, pos, tokens, dtype, quant=None, op=None):
     return out.cpu().numpy().reshape(tokens, HEADS, DIM)
 
 
+@pytest.mark.parametrize("blocks", [128, 64])
 @pytest.mark.parametrize("pos,tokens", [(0, 1), (0, 7), (5, 8), (70, 100), (1000, 64), (0, 300), (4093, 37)])
-def test_matches_cpu_on_reference_shapes(oracle, pos, tokens):
+def test_matches_cpu_on_reference_shapes(oracle, pos, tokens, blocks):
+    """The reference's own shapes (tests/attention_prefill.rs) through both kernels for 16-bit caches: score
+    blocks of 128 keys (the default) and of 64."""
     import torch
 
     capacity = (pos + tokens + 63) // 64 * 64 + 64
@@ -39,10 +42,15 @@ def test_matches_cpu_on_reference_shapes(oracle, pos, tokens):
     k = oracle.round_f16(oracle.spread(capacity * ROW, 2))
     v = oracle.round_f16(oracle.spread(capacity * ROW, 3))
     qg = ((np.arange(tokens * HEADS * 2 * DIM) % 7) - 3).astype(np.float32)
-    got = run(torch, q, k, v, qg, pos, tokens, sa.F16)
+    op = sa.AttGemm(0, 4096, KV)
+    op.score_blocks(blocks)
+    got = run(torch, q, k, v, qg, pos, tokens, sa.F16, op=op)
     want = oracle.attention_rows(q, qg, k, v, [pos + i + 1 for i in range(tokens)], threads=8)
     assert np.isfinite(got).all()
     assert max_abs(got, want) < 2e-3 and rel_rms(got, want) < 1e-3, (pos, tokens, max_abs(got, want), rel_rms(got, want))
+    if blocks == 64:
+        with pytest.raises(sa.SaettaError):
+            op.score_blocks(96)
 
 
 @pytest.mark.parametrize("pos,tokens", [(0, 1), (0, 7), (5, 8), (70, 100), (1000, 64), (0, 300), (4093, 37)])
