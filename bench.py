@@ -508,10 +508,11 @@ def strong_decode(sa, torch, dist, group_of, rank, world, dev, stream, warmup):
             "ctx_total": CTX, "ctx_per_gpu": n, "layers": LAYERS}
 
 
-def sharded_prefill(sa, torch, dist, group_of, rank, world, dev, stream, warmup, pos=131072, tokens=4096, bits=8):
+def sharded_prefill(sa, torch, dist, group_of, rank, world, dev, stream, warmup, pos=131072, tokens=4096, bits=8, staged=False):
     """Config 4 over N GPUs: a 4096-token chunk at 131072 over an 8-bit cache whose rows are split over the
     ranks by sequence (every rank STORES only its slice); partial over the rank's keys, row-sliced exchange,
-    every rank finalises its slice of the chunk's rows."""
+    every rank finalises its slice of the chunk's rows.  The slice is read in place, or (`staged`) through the op's
+    binary16 copy of it, which holds the slice from the chunk before."""
     from saetta_macqwen_b200 import shard
     total = pos + tokens
     lo, hi = shard.shard_ranges(total, world)[rank]
@@ -523,6 +524,7 @@ def sharded_prefill(sa, torch, dist, group_of, rank, world, dev, stream, warmup,
     qg = torch.randn(tokens * HEADS * 2 * DIM, device="cuda", generator=g)
     out = torch.zeros(tokens * HEADS * DIM, device="cuda")
     op = sa.AttGemm(dev, tokens, KV)
+    op.stage_quantised(staged)
     op.reserve(hi - lo)
     group = group_of(tokens)
     p = sa.FlashParams(HEADS, KV, pos, tokens, 1.0 / 16.0)
@@ -794,6 +796,7 @@ def main():
         if args.points != "none":
             for name, fn in [("strong_256k_8bit", lambda: strong_decode(sa, torch, dist, group_of, rank, world, dev, stream, 3)),
                              ("prefill_4k_pos128k_8bit", lambda: sharded_prefill(sa, torch, dist, group_of, rank, world, dev, stream, 2)),
+                             ("prefill_4k_pos128k_8bit_staged", lambda: sharded_prefill(sa, torch, dist, group_of, rank, world, dev, stream, 2, staged=True)),
                              ("batch64_ragged_8bit", lambda: sharded_batch(sa, torch, dist, group_of, rank, world, dev, stream, 3, 8)),
                              ("batch64_ragged_4bit", lambda: sharded_batch(sa, torch, dist, group_of, rank, world, dev, stream, 3, 4))]:
                 try:

@@ -361,8 +361,8 @@ def test_quantised_cache_through_the_staging_copy(oracle, bits):
         sa._check(sa.lib().saetta_att_gemm_stage_quantised(None, 1))
 
 
-@pytest.mark.parametrize("quant_bits", [None, 8])
-def test_shards_that_store_only_their_slice(oracle, quant_bits):
+@pytest.mark.parametrize("quant_bits,staged", [(None, False), (8, False), (8, True)])
+def test_shards_that_store_only_their_slice(oracle, quant_bits, staged):
     """Split-KV prefill where every shard STORES only its own keys: row 0 of shard r's cache is the key at
     global position cuts[r].  The shards' partials merge to the oracle's result over the whole sequence."""
     import torch
@@ -378,6 +378,7 @@ def test_shards_that_store_only_their_slice(oracle, quant_bits):
     for r in range(len(cuts) - 1):
         lo, hi = cuts[r], cuts[r + 1]
         op = sa.AttGemm(0, 4096, KV)
+        op.stage_quantised(staged)  # the slice through the op's binary16 copy of it, or in place
         if quant_bits:
             c = sa.GpuKvCache(0, quant_bits, hi - lo)
             c.store_at(dev(k[lo * ROW:hi * ROW]), dev(v[lo * ROW:hi * ROW]), 0, hi - lo)
